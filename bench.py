@@ -1,0 +1,293 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: top-k sparse MLA forward on the DeepSeek-V3.2 prefill shape
+(S_q = S_kv = 4096, h = 128, d_qk = 576, d_v = 512, topk = 2048 causal, -1 padded).
+
+    python bench.py --gpus N --steps K --warmup W            # this repo's CUDA path
+    python bench.py --impl reference ...                      # the CPU restatement, host cores
+
+One "step" is one forward over one batch of synthetic, seed-generated input.  With N > 1 every
+rank runs a full-size batch of its own query tokens against the replicated latent KV (tokens
+are independent units, so there is no data-path collective: weak scaling) and the line reports
+total FLOP/s over all ranks divided by the slowest rank's device time.  Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "sparse_mla_fwd_tflops"
+UNIT = "TFLOP/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"bf16_tflops": float(d["bf16_tflops"]), "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu_index), "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append((time.time(), ln.strip()))
+
+    def stop(self, t_begin: float, t_end: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        rows = [ln for (ts, ln) in self.lines if t_begin - 0.05 <= ts <= t_end + 0.15] or [ln for _, ln in self.lines]
+        for ln in rows:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline_mla(n_tokens: int, reps: int = 1):
+    """Times the CPU oracle on a bounded, evenly spaced sample of the cfg2 query tokens."""
+    from flagtree_b200 import workloads as W
+    from oracle.sparse_mla_ref import sparse_mla_fwd_ref
+    c = W.mla_cfg2(device="cpu", s_q=4096, s_kv=4096, h=128, topk=2048) if n_tokens > 0 else None
+    sel = torch.linspace(0, 4095, n_tokens).round().long()
+    q, idx = c.q[sel].contiguous(), c.indices[sel].contiguous()
+    flops = 2 * (576 + 512) * 128 * int((idx >= 0).sum())
+    torch.set_num_threads(os.cpu_count() or 1)
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        sparse_mla_fwd_ref(q, c.kv, idx, c.sm_scale, chunk=8)
+        best = min(best, time.perf_counter() - t0)
+    return {"value": flops / best / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n_tokens} of 4096 query tokens of the cfg2 prefill batch, evenly spaced (h=128, topk<=2048), "
+                      f"fp32 torch restatement, best of {reps}; {best:.2f} s",
+            "seconds": best, "flops": flops}
+
+
+def run_reference(args, rank, world):
+    """CPU arm: the restatement of the reference's torch idiom on the box's host cores."""
+    if rank != 0:
+        return
+    n_tok = args.ref_tokens
+    times = []
+    res = None
+    for i in range(args.warmup + args.steps):
+        res = cpu_baseline_mla(n_tok, reps=1)
+        if i >= args.warmup:
+            times.append(res["seconds"])
+    t = sum(times) / len(times)
+    val = res["flops"] / t / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "mla_cfg2_prefill_sq4096_skv4096_h128_topk2048_causal", "sample_tokens": n_tok},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": res["cores"], "kind": "port", "sample": res["sample"]},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--ref-tokens", type=int, default=512, help="query tokens per step of the CPU arm")
+    ap.add_argument("--cpu-tokens", type=int, default=2048, help="query tokens of the cpu_baseline sample")
+    ap.add_argument("--s-q", type=int, default=4096, help="query tokens per rank (default = full cfg2)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return 0
+
+    if args.warmup < 3:
+        args.warmup = 3
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the native arm has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+
+    from flagtree_b200 import sparse_mla_fwd
+    from flagtree_b200 import workloads as W
+
+    case = W.mla_cfg2(device=dev, s_q=args.s_q, s_kv=4096, h=128, topk=2048, rank=rank)
+    flops_rank = case.flops
+    out = torch.empty(case.q.shape[0], 128, 512, dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(case.q.shape[0], 128, dtype=torch.float32, device=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step():
+        sparse_mla_fwd(case.q, case.kv, case.indices, case.sm_scale, out=out, lse=lse)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    barrier()
+    t_begin = time.time()
+    evs[0].record()
+    for i in range(args.steps):
+        step()
+        evs[i + 1].record()
+    barrier()
+    t_end = time.time()
+    total_ms = evs[0].elapsed_time(evs[-1])
+    per_launch_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+
+    t = torch.tensor([total_ms, float(flops_rank)], dtype=torch.float64, device=dev)
+    if dist is not None:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        total_ms_max, flops_all = float(tmax[0]), float(tsum[1])
+    else:
+        total_ms_max, flops_all = total_ms, float(flops_rank)
+    ms_per_step = total_ms_max / args.steps
+    value = flops_all / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end-to-end through the public API with host buffers (pinned), copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        hq = case.q.cpu().pin_memory()
+        hkv = case.kv.cpu().pin_memory()
+        hidx = case.indices.cpu().pin_memory()
+        hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        hlse = torch.empty(lse.shape, dtype=lse.dtype).pin_memory()
+        dq, dkv, didx = torch.empty_like(case.q), torch.empty_like(case.kv), torch.empty_like(case.indices)
+
+        def e2e_step():
+            dq.copy_(hq, non_blocking=True)
+            dkv.copy_(hkv, non_blocking=True)
+            didx.copy_(hidx, non_blocking=True)
+            sparse_mla_fwd(dq, dkv, didx, case.sm_scale, out=out, lse=lse)
+            hout.copy_(out, non_blocking=True)
+            hlse.copy_(lse, non_blocking=True)
+
+        n_e2e = max(3, min(args.steps, 8))
+        e2e_step()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ms = float(te[0]) / n_e2e
+        h2d = hq.numel() * 2 + hkv.numel() * 2 + hidx.numel() * 4
+        d2h = hout.numel() * 2 + hlse.numel() * 4
+        e2e = {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e}
+
+    if rank == 0:
+        peaks = load_peaks()
+        avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
+        achieved = flops_rank / (avg_launch_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"]
+        prof_traffic = None
+        tpath = os.path.join(ROOT, "profiles", "sparse_mla_traffic.json")
+        if os.path.exists(tpath):
+            try:
+                with open(tpath) as f:
+                    prof_traffic = json.load(f).get("dram_bytes_per_launch_cfg2")
+            except Exception:
+                prof_traffic = None
+        roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "traffic": prof_traffic, "peak_source": f"bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json",
+                    "kernel": "sparse_mla_fwd_kernel", "flops_per_launch": flops_rank, "avg_launch_ms": avg_launch_ms}
+        cpu_b = None
+        if not args.no_cpu_baseline:
+            cpu_b = cpu_baseline_mla(args.cpu_tokens, reps=2)
+            cpu_b.pop("seconds"); cpu_b.pop("flops")
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "mla_cfg2_prefill_sq4096_skv4096_h128_topk2048_causal", "s_q_per_gpu": args.s_q,
+                       "sharding": "query tokens per rank, latent KV replicated, no collective",
+                       "l2": "inputs larger than L2 (q 604 MB per step)", "sm_scale": case.sm_scale,
+                       "flops_per_gpu_step": flops_rank},
+            "roofline": roofline, "cpu_baseline": cpu_b, "e2e": e2e, "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

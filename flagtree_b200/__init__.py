@@ -1,0 +1,8 @@
+"""B200-native (sm_100a) kernels for FlagTree's sparse-MLA forward and GEMM + reduce-scatter.
+
+The product is the C-ABI library `libflagtree_b200.so` (include/flagtree_b200.h); this package
+is the thin Python mirror of the reference's operator wrappers on top of it.
+"""
+from .ops import decode_attention_fwd, sparse_mla_fwd, sparse_mla_fwd_paged  # noqa: F401
+
+__all__ = ["sparse_mla_fwd", "sparse_mla_fwd_paged", "decode_attention_fwd"]

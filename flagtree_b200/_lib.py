@@ -1,0 +1,85 @@
+"""ctypes binding of libflagtree_b200.so.  Loading fails loudly: there is no CPU fallback."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libflagtree_b200.so")
+
+FTB_OK, FTB_ERR_INVALID, FTB_ERR_CUDA, FTB_ERR_TIMEOUT, FTB_ERR_BAD_INDEX, FTB_ERR_UNSUPPORTED = range(6)
+STATUS_NAMES = {0: "OK", 1: "INVALID", 2: "CUDA", 3: "TIMEOUT", 4: "BAD_INDEX", 5: "UNSUPPORTED"}
+
+
+class SparseMlaArgs(C.Structure):
+    """Mirror of `ftb_sparse_mla_args` (include/flagtree_b200.h)."""
+    _fields_ = [
+        ("q", C.c_void_p), ("kv", C.c_void_p), ("indices", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+        ("s_q", C.c_int32), ("h", C.c_int32), ("s_kv", C.c_int32), ("topk", C.c_int32),
+        ("q_stride_token", C.c_int64), ("q_stride_head", C.c_int64),
+        ("kv_stride_row", C.c_int64),
+        ("idx_stride_token", C.c_int64),
+        ("out_stride_token", C.c_int64), ("out_stride_head", C.c_int64),
+        ("lse_stride_token", C.c_int64),
+        ("sm_scale", C.c_float), ("lse_base2", C.c_int32), ("algo_id", C.c_int32),
+        ("status", C.c_void_p),
+        ("kv_is_fp8", C.c_int32),
+        ("kv_scale", C.c_void_p), ("block_table", C.c_void_p), ("context_lens", C.c_void_p),
+        ("page_size", C.c_int32), ("q_per_seq", C.c_int32),
+        ("block_table_stride", C.c_int64),
+        ("dbg_scores", C.c_void_p),
+    ]
+
+
+_lib = None
+_lock = threading.Lock()
+
+
+def load() -> C.CDLL:
+    """Load the shared library once.  Raises RuntimeError when it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise RuntimeError(
+                    f"{LIB_PATH} is missing: build it with `python -m flagtree_b200.build` "
+                    "(nvcc, sm_100a). flagtree_b200 has no CPU or PyTorch fallback.")
+            lib = C.CDLL(LIB_PATH)
+            lib.ftb_abi_version.restype = C.c_int
+            lib.ftb_last_error_string.restype = C.c_char_p
+            for name in declared_symbols():
+                if not hasattr(lib, name):
+                    raise RuntimeError(f"{LIB_PATH} does not export {name}; rebuild the library")
+            lib.ftb_sparse_mla_fwd.argtypes = [C.POINTER(SparseMlaArgs), C.c_void_p]
+            lib.ftb_sparse_mla_fwd.restype = C.c_int
+            if lib.ftb_sizeof_sparse_mla_args() != C.sizeof(SparseMlaArgs):
+                raise RuntimeError("ftb_sparse_mla_args layout differs between the header and the Python mirror")
+            _lib = lib
+    return _lib
+
+
+def declared_symbols():
+    """Names of every function `include/flagtree_b200.h` declares (parsed from the header)."""
+    import re
+    hdr = os.path.join(_PKG, "..", "include", "flagtree_b200.h")
+    with open(hdr) as f:
+        text = f.read()
+    return sorted(set(re.findall(r"FTB_API\s+[\w\s\*]+?\b(ftb_\w+)\s*\(", text)))
+
+
+def last_error() -> str:
+    s = load().ftb_last_error_string()
+    return s.decode() if s else ""
+
+
+def check(rc: int, what: str) -> None:
+    """Map a C-ABI status to the exception types the reference's wrappers raise."""
+    if rc == FTB_OK:
+        return
+    msg = f"{what}: {STATUS_NAMES.get(rc, rc)}: {last_error()}"
+    if rc in (FTB_ERR_INVALID, FTB_ERR_UNSUPPORTED):
+        raise ValueError(msg)
+    raise RuntimeError(msg)

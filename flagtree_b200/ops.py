@@ -1,0 +1,176 @@
+"""Python call surface of the hot path: same call shapes as the reference's kernel wrappers.
+
+Every function here only validates arguments, allocates outputs with torch and forwards plain
+pointers to the C ABI (include/flagtree_b200.h).  There is no PyTorch or CPU fallback: if the
+shared library is missing the call raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+D_QK = 576
+D_V = 512
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            # The reference's launcher raises ValueError for host tensors
+            # (third_party/nvidia/backend/driver.py:259-264).
+            raise ValueError("Pointer argument cannot be accessed from the device: expected CUDA tensors")
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _check_status(status: Optional[torch.Tensor], what: str):
+    if status is None:
+        return
+    code = int(status.item())
+    if code != 0:
+        raise RuntimeError(f"{what}: device status {_lib.STATUS_NAMES.get(code, code)}")
+
+
+def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
+                   sm_scale: Optional[float] = None, d_v: int = D_V, *, lse_base2: bool = False,
+                   out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                   check: bool = False, _dbg_scores: Optional[torch.Tensor] = None
+                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Top-k sparse MLA forward.
+
+    q [S_q, h, 576] bf16, kv [S_kv, 576] (or [S_kv, 1, 576]) bf16, indices [S_q, topk] int32 with
+    -1 padding.  Returns (out [S_q, h, 512] bf16, lse [S_q, h] fp32, natural log).  Takes over
+    the reference's decode_attention_fwd launch pair
+    (third_party/mthreads/python/test/wmma/test_accuracy_musa_vllm_mla.py:571-620) with the
+    token table as `indices`.  `sm_scale` defaults to 576**-0.5 (:640 of the same file).
+    `check=True` reads back the device status word (one host sync) and raises on a bad index
+    or a device-side timeout.
+    """
+    _require_cuda(q, kv, indices)
+    if kv.dim() == 3:
+        assert kv.shape[1] == 1, "latent KV has a single shared head"
+        kv = kv[:, 0, :]
+    assert q.dim() == 3 and kv.dim() == 2 and indices.dim() == 2, "expected q[S_q,h,576], kv[S_kv,576], indices[S_q,topk]"
+    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16, "q and kv must be bf16"
+    assert indices.dtype == torch.int32, "indices must be int32"
+    assert q.shape[2] == D_QK and kv.shape[1] == D_QK, "q/k head dim must be 576 (512 latent + 64 rope)"
+    assert d_v == D_V, "v head dim must be 512"
+    assert indices.shape[0] == q.shape[0]
+    assert q.stride(2) == 1 and kv.stride(1) == 1 and indices.stride(1) == 1, "innermost dimension must be contiguous"
+    s_q, h, _ = q.shape
+    if sm_scale is None:
+        sm_scale = D_QK ** -0.5
+    if out is None:
+        out = torch.empty(s_q, h, D_V, dtype=torch.bfloat16, device=q.device)
+    if lse is None:
+        lse = torch.empty(s_q, h, dtype=torch.float32, device=q.device)
+    assert out.shape == (s_q, h, D_V) and out.dtype == torch.bfloat16 and out.stride(2) == 1
+    assert lse.shape == (s_q, h) and lse.dtype == torch.float32 and lse.stride(1) == 1
+    status = torch.zeros(1, dtype=torch.int32, device=q.device) if check else None
+    lib = _lib.load()
+    for h0 in range(0, h, 128):      # more than 128 heads: one launch per block of 128 heads
+        h1 = min(h, h0 + 128)
+        qs, os_, ls = q[:, h0:h1], out[:, h0:h1], lse[:, h0:h1]
+        a = _lib.SparseMlaArgs()
+        a.q, a.kv, a.indices = qs.data_ptr(), kv.data_ptr(), indices.data_ptr()
+        a.out, a.lse = os_.data_ptr(), ls.data_ptr()
+        a.s_q, a.h, a.s_kv, a.topk = s_q, h1 - h0, kv.shape[0], indices.shape[1]
+        a.q_stride_token, a.q_stride_head = qs.stride(0), qs.stride(1)
+        a.kv_stride_row = kv.stride(0)
+        a.idx_stride_token = indices.stride(0)
+        a.out_stride_token, a.out_stride_head = os_.stride(0), os_.stride(1)
+        a.lse_stride_token = ls.stride(0)
+        a.sm_scale, a.lse_base2, a.algo_id = float(sm_scale), int(lse_base2), 0
+        a.status = status.data_ptr() if status is not None else None
+        a.kv_is_fp8 = 0
+        a.dbg_scores = _dbg_scores.data_ptr() if _dbg_scores is not None else None
+        with torch.cuda.device(q.device):
+            rc = lib.ftb_sparse_mla_fwd(C.byref(a), C.c_void_p(_stream_ptr(q.device)))
+        _lib.check(rc, "sparse_mla_fwd")
+    _check_status(status, "sparse_mla_fwd")
+    return out, lse
+
+
+def sparse_mla_fwd_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Tensor,
+                         block_table: torch.Tensor, context_lens: torch.Tensor, indices: torch.Tensor,
+                         sm_scale: Optional[float] = None, d_v: int = D_V, page_size: int = 64, *,
+                         lse_base2: bool = False, check: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sparse MLA decode over a paged FP8 (e4m3) latent cache with one fp32 scale per page.
+
+    q [B, n_q, h, 576] bf16; kv_cache [num_pages, page_size, 576] e4m3 (uint8 or float8_e4m3fn);
+    kv_scale [num_pages] fp32 (value = fp8 * scale); block_table [B, max_pages] int32;
+    context_lens [B] int32; indices [B, n_q, topk] int32 LOGICAL positions (-1 = padding).
+    Physical row = block_table[b, p // page] * page + p % page, the addressing rule of
+    test_accuracy_musa_vllm_mla.py:278-283.  Returns (out [B,n_q,h,512] bf16, lse [B,n_q,h] fp32).
+    """
+    _require_cuda(q, kv_cache, kv_scale, block_table, context_lens, indices)
+    assert q.dim() == 4 and indices.dim() == 3 and kv_cache.dim() == 3
+    assert q.dtype == torch.bfloat16
+    assert kv_cache.dtype in (torch.uint8, torch.float8_e4m3fn), "kv_cache must hold e4m3 bytes"
+    assert kv_cache.shape[1] == page_size and kv_cache.shape[2] == D_QK and kv_cache.is_contiguous()
+    assert kv_scale.dtype == torch.float32 and kv_scale.numel() == kv_cache.shape[0] and kv_scale.is_contiguous()
+    assert block_table.dtype == torch.int32 and context_lens.dtype == torch.int32 and indices.dtype == torch.int32
+    assert block_table.stride(1) == 1 and context_lens.is_contiguous()
+    assert d_v == D_V and q.shape[3] == D_QK
+    b, n_q, h, _ = q.shape
+    assert h <= 128, "at most 128 heads per call in the paged form"
+    assert indices.shape[:2] == (b, n_q) and block_table.shape[0] == b and context_lens.shape[0] == b
+    q2 = q.reshape(b * n_q, h, D_QK)
+    idx2 = indices.reshape(b * n_q, indices.shape[2])
+    assert q2.stride(2) == 1 and idx2.stride(1) == 1
+    if sm_scale is None:
+        sm_scale = D_QK ** -0.5
+    out = torch.empty(b * n_q, h, D_V, dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty(b * n_q, h, dtype=torch.float32, device=q.device)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device) if check else None
+    a = _lib.SparseMlaArgs()
+    a.q, a.kv, a.indices, a.out, a.lse = q2.data_ptr(), kv_cache.data_ptr(), idx2.data_ptr(), out.data_ptr(), lse.data_ptr()
+    a.s_q, a.h, a.s_kv, a.topk = b * n_q, h, kv_cache.shape[0] * page_size, idx2.shape[1]
+    a.q_stride_token, a.q_stride_head = q2.stride(0), q2.stride(1)
+    a.kv_stride_row = D_QK
+    a.idx_stride_token = idx2.stride(0)
+    a.out_stride_token, a.out_stride_head = out.stride(0), out.stride(1)
+    a.lse_stride_token = lse.stride(0)
+    a.sm_scale, a.lse_base2, a.algo_id = float(sm_scale), int(lse_base2), 0
+    a.status = status.data_ptr() if status is not None else None
+    a.kv_is_fp8 = 1
+    a.kv_scale, a.block_table, a.context_lens = kv_scale.data_ptr(), block_table.data_ptr(), context_lens.data_ptr()
+    a.page_size, a.q_per_seq, a.block_table_stride = page_size, n_q, block_table.stride(0)
+    a.dbg_scores = None
+    with torch.cuda.device(q.device):
+        rc = _lib.load().ftb_sparse_mla_fwd(C.byref(a), C.c_void_p(_stream_ptr(q.device)))
+    _lib.check(rc, "sparse_mla_fwd_paged")
+    _check_status(status, "sparse_mla_fwd_paged")
+    return out.view(b, n_q, h, D_V), lse.view(b, n_q, h)
+
+
+def decode_attention_fwd(q, k_buffer, v_buffer, o, req_to_token, b_seq_len, attn_logits=None,
+                         num_kv_splits=None, sm_scale=None, page_size=1, logit_cap=0.0, en_wmma=False):
+    """Drop-in for the reference's `decode_attention_fwd` (test_accuracy_musa_vllm_mla.py:571-584)
+    for the MLA shape (one shared latent head, Lk = 576, Lv = 512, page_size = 1): writes into `o`.
+
+    `req_to_token [B, max_len]` is the token table and `b_seq_len [B]` the number of leading
+    valid entries.  `attn_logits` and `num_kv_splits` are accepted and ignored (kv splitting is
+    internal); when both are given the reference's shape assertion (:585) is kept.
+    """
+    if attn_logits is not None and num_kv_splits is not None:
+        assert num_kv_splits == attn_logits.shape[2]
+    assert page_size == 1, "the dense form takes a token table (page size 1); use sparse_mla_fwd_paged for pages"
+    assert logit_cap == 0.0, "logit soft-capping is not part of the sparse MLA path"
+    assert k_buffer.shape[-2] == 1 and k_buffer.shape[-1] == D_QK, "MLA form: one latent head of 576 dims"
+    kv = k_buffer.reshape(-1, D_QK)
+    assert v_buffer.shape[-1] == D_V
+    topk = req_to_token.shape[1]
+    pos = torch.arange(topk, device=req_to_token.device, dtype=torch.int32)
+    idx = torch.where(pos[None, :] < b_seq_len[:, None].to(torch.int32), req_to_token.to(torch.int32),
+                      torch.full((1, 1), -1, dtype=torch.int32, device=req_to_token.device))
+    if sm_scale is None:
+        sm_scale = D_QK ** -0.5
+    sparse_mla_fwd(q, kv, idx.contiguous(), sm_scale, out=o)
+    return o

@@ -78,19 +78,18 @@ def causal_topk_indices(s_q: int, topk: int, g: torch.Generator, device, t0: int
 
 
 def mla_cfg2(device="cpu", s_q: int = 4096, s_kv: int = 4096, h: int = 128, topk: int = 2048,
-             rank: int = 0, world: int = 1) -> SparseMlaCase:
+             rank: int = 0) -> SparseMlaCase:
     """Prefill, DeepSeek-V3.2 shape: causal top-k with -1 padding.
 
-    With world > 1 the KV is replicated (same seed on every rank) and rank r holds query
-    tokens [r*s_q/world, (r+1)*s_q/world).
+    The latent KV is the same on every rank (it is replicated in a token-sharded run); `rank`
+    only changes the seed of the query tokens and of their index lists, so each rank gets an
+    independent batch of the same shape.
     """
-    assert s_q % world == 0
     g = _gen(1000 * 2, device)
     kv = torch.randn(s_kv, D_QK, generator=g, device=device).to(torch.bfloat16)
-    q_all_rows = s_q // world
     gq = _gen(1000 * 2 + 1 + rank, device)
-    q = torch.randn(q_all_rows, h, D_QK, generator=gq, device=device).to(torch.bfloat16)
-    idx = causal_topk_indices(q_all_rows, topk, gq, device, t0=rank * q_all_rows)
+    q = torch.randn(s_q, h, D_QK, generator=gq, device=device).to(torch.bfloat16)
+    idx = causal_topk_indices(s_q, topk, gq, device)
     idx = torch.where(idx >= s_kv, torch.full_like(idx, -1), idx)
     return SparseMlaCase(q, kv, idx, SM_SCALE_CFG,
                          f"mla_cfg2_prefill_sq{s_q}_skv{s_kv}_h{h}_topk{topk}")

@@ -94,10 +94,24 @@ def run_reference(mod, q, k_buffer, v_buffer, req_to_tokens, b_seqlen, sm_scale,
     return o, lse, att
 
 
+def _randn_bf16_exact_fp16(shape, g):
+    """N(0,1) values that are exactly representable in BOTH bf16 and fp16, returned as fp16.
+
+    The interpreter run needs fp16; the CUDA kernels take bf16.  Rounding to bf16 first and
+    flushing magnitudes below the fp16 normal range makes the two casts exact, so GPU parity
+    tests can feed the kernels the very same numbers.
+    """
+    x = torch.randn(*shape, generator=g).to(torch.bfloat16).to(torch.float32)
+    x = torch.where(x.abs() < 2.0 ** -14, torch.zeros_like(x), x)
+    y = x.to(torch.float16)
+    assert torch.equal(y.to(torch.float32), x) and torch.equal(x.to(torch.bfloat16).to(torch.float32), x)
+    return y
+
+
 def case_topk(mod, seed, s_q, h, s_kv, topk, splits, ragged):
     g = torch.Generator().manual_seed(seed)
-    q = torch.randn(s_q, h, 576, generator=g).to(torch.float16)
-    kv = torch.randn(s_kv, 576, generator=g).to(torch.float16)
+    q = _randn_bf16_exact_fp16((s_q, h, 576), g)
+    kv = _randn_bf16_exact_fp16((s_kv, 576), g)
     idx = torch.stack([torch.randperm(s_kv, generator=g)[:topk] for _ in range(s_q)]).to(torch.int32)
     if ragged:
         n_valid = torch.randint(1, topk + 1, (s_q,), generator=g).to(torch.int32)
@@ -117,8 +131,8 @@ def case_topk(mod, seed, s_q, h, s_kv, topk, splits, ragged):
 
 def case_paged(mod, seed, batch, h, n_pages, page, seq_len, splits):
     g = torch.Generator().manual_seed(seed)
-    q = torch.randn(batch, h, 576, generator=g).to(torch.float16)
-    cache = torch.randn(n_pages, page, 1, 576, generator=g).to(torch.float16)
+    q = _randn_bf16_exact_fp16((batch, h, 576), g)
+    cache = _randn_bf16_exact_fp16((n_pages, page, 1, 576), g)
     pages_per = (seq_len + page - 1) // page
     table = torch.stack([torch.randperm(n_pages, generator=g)[:pages_per] for _ in range(batch)]).to(torch.int32)
     lens = torch.full((batch,), seq_len, dtype=torch.int32)

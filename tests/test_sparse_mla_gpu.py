@@ -1,0 +1,217 @@
+"""GPU parity tests of the sparse MLA forward: the CUDA path (through the C ABI) against the CPU
+oracle on identical seeded inputs.  Tolerances are the benchmark contract's: bf16 output max-abs
+error <= 2e-2, LSE relative error <= 1e-3 (relative to max(|lse|, 1))."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_DIR, LSE_RTOL, OUT_ATOL
+
+pytestmark = pytest.mark.gpu
+
+if torch.cuda.is_available():
+    from flagtree_b200 import decode_attention_fwd, sparse_mla_fwd, sparse_mla_fwd_paged
+    from flagtree_b200 import workloads as W
+from oracle.sparse_mla_ref import sparse_mla_fwd_paged_ref, sparse_mla_fwd_ref
+
+DEV = "cuda:0"
+
+
+def _errors(out, lse, ref_out, ref_lse):
+    out = out.float().cpu()
+    lse = lse.float().cpu()
+    e_out = (out - ref_out).abs().max().item() if out.numel() else 0.0
+    fin = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse), fin), "finite/-inf pattern of LSE differs"
+    if (~fin).any():
+        assert (lse[~fin] == ref_lse[~fin]).all()
+    e_lse = ((lse[fin] - ref_lse[fin]).abs() / ref_lse[fin].abs().clamp(min=1.0)).max().item() if fin.any() else 0.0
+    return e_out, e_lse
+
+
+def _check(q, kv, idx, sm_scale, name=""):
+    out, lse = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), sm_scale, check=True)
+    torch.cuda.synchronize()
+    ref_out, ref_lse = sparse_mla_fwd_ref(q, kv, idx, sm_scale)
+    e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
+    print(f"[{name}] out max-abs err {e_out:.3e}  lse rel err {e_lse:.3e}")
+    assert torch.isfinite(out.float()).all()
+    assert e_out <= OUT_ATOL, (name, e_out)
+    assert e_lse <= LSE_RTOL, (name, e_lse)
+    return out, lse
+
+
+def test_scores_tap_matches_qk():
+    """Raw Q.K^T scores of the first tiles (debug tap) against a direct fp32 product."""
+    g = torch.Generator().manual_seed(1)
+    s_q, h, s_kv, topk = 2, 128, 300, 128
+    q = torch.randn(s_q, h, 576, generator=g).bfloat16()
+    kv = torch.randn(s_kv, 576, generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(s_kv, generator=g)[:topk] for _ in range(s_q)]).int()
+    dbg = torch.zeros(s_q, 128, topk, dtype=torch.float32, device=DEV)
+    sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), 0.05, check=True, _dbg_scores=dbg)
+    torch.cuda.synchronize()
+    ref = torch.einsum("thd,tkd->thk", q.float(), kv.float()[idx.long()])
+    err = (dbg.cpu() - ref).abs().max().item()
+    print("scores tap max-abs err", err)
+    assert err < 1e-2 * ref.abs().max().item()
+
+
+GOLDEN = sorted(glob.glob(os.path.join(GOLDEN_DIR, "mla_topk_*.npz")))
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
+def test_golden_vectors_from_reference_kernel(path):
+    d = np.load(path)
+    q = torch.from_numpy(d["q"]).to(torch.bfloat16)       # exact: fixtures hold bf16-representable values
+    kv = torch.from_numpy(d["kv"]).to(torch.bfloat16)
+    assert torch.equal(q.float(), torch.from_numpy(d["q"]).float())
+    idx = torch.from_numpy(d["indices"])
+    out, lse = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), float(d["sm_scale"]), check=True)
+    e_out, e_lse = _errors(out, lse, torch.from_numpy(d["out"]).float(), torch.from_numpy(d["lse"]).float())
+    print(f"[golden {os.path.basename(path)}] out {e_out:.3e} lse {e_lse:.3e}")
+    assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+
+
+def test_cfg1_cpu_runnable_case_full():
+    c = W.mla_cfg1()
+    _check(c.q, c.kv, c.indices, c.sm_scale, c.name)
+
+
+@pytest.mark.parametrize("h", [1, 16, 64, 128])
+@pytest.mark.parametrize("topk", [1, 37, 64, 200])
+def test_head_counts_and_ragged_topk(h, topk):
+    g = torch.Generator().manual_seed(100 + h + topk)
+    s_q, s_kv = 5, 333
+    q = torch.randn(s_q, h, 576, generator=g).bfloat16()
+    kv = torch.randn(s_kv, 576, generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(s_kv, generator=g)[:topk] for _ in range(s_q)]).int()
+    _check(q, kv, idx, 576 ** -0.5, f"h{h}_topk{topk}")
+
+
+def test_padding_patterns():
+    """Trailing -1 padding, a token with no valid entry, one valid entry, and -1 in the middle."""
+    g = torch.Generator().manual_seed(7)
+    s_q, h, s_kv, topk = 6, 128, 500, 192
+    q = torch.randn(s_q, h, 576, generator=g).bfloat16()
+    kv = torch.randn(s_kv, 576, generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(s_kv, generator=g)[:topk] for _ in range(s_q)]).int()
+    idx[0, 100:] = -1
+    idx[1, :] = -1
+    idx[2, 1:] = -1
+    idx[3, 10:70] = -1            # a hole spanning a tile boundary
+    idx[4, 0:64] = -1             # a fully masked first tile
+    out, lse = _check(q, kv, idx, 0.07, "padding")
+    assert (out[1] == 0).all() and torch.isinf(lse[1]).all()
+    # single selected row: the output is that row's first 512 values exactly (weight 1.0)
+    assert torch.equal(out[2].cpu(), kv[idx[2, 0].item(), :512].expand(h, 512))
+
+
+def test_causal_prefill_shape_scaled_down():
+    c = W.mla_cfg2(s_q=192, s_kv=192, h=128, topk=128)
+    _check(c.q, c.kv, c.indices, c.sm_scale, c.name)
+
+
+def test_large_scores_are_stable():
+    g = torch.Generator().manual_seed(3)
+    q = (torch.randn(3, 128, 576, generator=g) * 4).bfloat16()
+    kv = (torch.randn(256, 576, generator=g) * 4).bfloat16()
+    idx = torch.stack([torch.randperm(256, generator=g)[:128] for _ in range(3)]).int()
+    _check(q, kv, idx, 1.0, "large_scores")
+
+
+def test_order_invariance_determinism_and_token_sharding():
+    c = W.mla_cfg2(device=DEV, s_q=512, s_kv=512, h=128, topk=256)
+    out, lse = sparse_mla_fwd(c.q, c.kv, c.indices, c.sm_scale, check=True)
+    out2, lse2 = sparse_mla_fwd(c.q, c.kv, c.indices, c.sm_scale, check=True)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2), "two runs differ"
+    # sharding query tokens across ranks must give bit-identical rows
+    for lo, hi in ((0, 128), (128, 512)):
+        o_s, l_s = sparse_mla_fwd(c.q[lo:hi], c.kv, c.indices[lo:hi], c.sm_scale, check=True)
+        assert torch.equal(o_s, out[lo:hi]) and torch.equal(l_s, lse[lo:hi])
+    # sharding heads: bit-identical columns
+    o_h, l_h = sparse_mla_fwd(c.q[:, 16:32].contiguous(), c.kv, c.indices, c.sm_scale, check=True)
+    assert torch.equal(o_h, out[:, 16:32]) and torch.equal(l_h, lse[:, 16:32])
+    # permuting a token's index list changes only the summation order
+    perm = torch.randperm(256, device=DEV)
+    o_p, l_p = sparse_mla_fwd(c.q, c.kv, c.indices[:, perm].contiguous(), c.sm_scale, check=True)
+    assert (o_p.float() - out.float()).abs().max().item() <= OUT_ATOL
+    assert ((l_p - lse).abs() / lse.abs().clamp(min=1)).max().item() <= LSE_RTOL
+
+
+def test_full_size_prefill_sampled_tokens():
+    """cfg2 at full size (S_q = S_kv = 4096, h = 128, topk = 2048): every output is produced on the
+    GPU; a seeded sample of tokens is compared with the CPU oracle, LSE of all tokens is checked
+    for finiteness, and the all-tokens checksum is compared between two runs."""
+    c = W.mla_cfg2(device=DEV)
+    out, lse = sparse_mla_fwd(c.q, c.kv, c.indices, c.sm_scale, check=True)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    g = torch.Generator().manual_seed(5)
+    sample = torch.cat([torch.tensor([0, 1, 63, 64, 2047, 2048, 4095]), torch.randint(0, 4096, (9,), generator=g)])
+    ref_out, ref_lse = sparse_mla_fwd_ref(c.q[sample].cpu(), c.kv.cpu(), c.indices[sample].cpu(), c.sm_scale, chunk=4)
+    e_out, e_lse = _errors(out[sample], lse[sample], ref_out, ref_lse)
+    print(f"[cfg2 full, {len(sample)} sampled tokens] out {e_out:.3e} lse {e_lse:.3e}")
+    assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+    out2, _ = sparse_mla_fwd(c.q, c.kv, c.indices, c.sm_scale)
+    assert torch.equal(out, out2)
+
+
+def test_more_than_128_heads_and_strided_views():
+    g = torch.Generator().manual_seed(11)
+    q_big = torch.randn(3, 160, 640, generator=g).bfloat16()
+    kv_big = torch.randn(100, 1, 640, generator=g).bfloat16()
+    q, kv = q_big[:, :, :576], kv_big[:, :, :576]           # non-contiguous rows
+    idx = torch.stack([torch.randperm(100, generator=g)[:70] for _ in range(3)]).int()
+    out, lse = sparse_mla_fwd(q.to(DEV)[:, :, :], kv.to(DEV), idx.to(DEV), 0.05, check=True)
+    ref_out, ref_lse = sparse_mla_fwd_ref(q, kv[:, 0], idx, 0.05)
+    e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
+    assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+
+
+def test_bad_index_is_reported_not_read():
+    g = torch.Generator().manual_seed(2)
+    q = torch.randn(1, 16, 576, generator=g).bfloat16().to(DEV)
+    kv = torch.randn(32, 576, generator=g).bfloat16().to(DEV)
+    idx = torch.tensor([[0, 1, 999999, 3]], dtype=torch.int32, device=DEV)
+    with pytest.raises(RuntimeError, match="BAD_INDEX"):
+        sparse_mla_fwd(q, kv, idx, 0.1, check=True)
+
+
+def test_decode_attention_fwd_shim_matches_reference_signature():
+    d = np.load(os.path.join(GOLDEN_DIR, "mla_topk_ragged_sq6_h16_topk96.npz"))
+    q = torch.from_numpy(d["q"]).to(torch.bfloat16).to(DEV)
+    kv = torch.from_numpy(d["kv"]).to(torch.bfloat16).to(DEV)
+    idx = torch.from_numpy(d["indices"]).to(DEV)
+    n_valid = (idx >= 0).sum(dim=1).int()
+    o = torch.zeros(q.shape[0], q.shape[1], 512, dtype=torch.bfloat16, device=DEV)
+    attn_logits = torch.empty(q.shape[0], q.shape[1], 4, 513, device=DEV)
+    decode_attention_fwd(q, kv.view(-1, 1, 576), kv.view(-1, 1, 576)[..., :512], o, idx.clamp(min=0), n_valid,
+                         attn_logits, 4, float(d["sm_scale"]))
+    assert (o.float().cpu() - torch.from_numpy(d["out"]).float()).abs().max().item() <= OUT_ATOL
+
+
+def test_paged_fp8_decode_scaled_down():
+    c = W.mla_cfg3(batch=4, n_q=2, h=128, topk=256, len_lo=300, len_hi=1500)
+    out, lse = sparse_mla_fwd_paged(c.q.to(DEV), c.kv_cache.to(DEV), c.kv_scale.to(DEV), c.block_table.to(DEV),
+                                    c.context_lens.to(DEV), c.indices.to(DEV), c.sm_scale, page_size=c.page_size,
+                                    check=True)
+    ref_out, ref_lse = sparse_mla_fwd_paged_ref(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens,
+                                                c.indices, c.sm_scale, page_size=c.page_size)
+    e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
+    print(f"[paged fp8] out {e_out:.3e} lse {e_lse:.3e}")
+    assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+
+
+def test_paged_fp8_short_context_and_padding():
+    c = W.mla_cfg3(batch=3, n_q=2, h=16, topk=128, len_lo=20, len_hi=100)   # topk > context: -1 padded
+    out, lse = sparse_mla_fwd_paged(c.q.to(DEV), c.kv_cache.to(DEV), c.kv_scale.to(DEV), c.block_table.to(DEV),
+                                    c.context_lens.to(DEV), c.indices.to(DEV), c.sm_scale, page_size=c.page_size,
+                                    check=True)
+    ref_out, ref_lse = sparse_mla_fwd_paged_ref(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens,
+                                                c.indices, c.sm_scale, page_size=c.page_size)
+    e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
+    assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
