@@ -117,10 +117,13 @@ def test_causal_prefill_shape_scaled_down():
 
 def test_large_scores_are_stable():
     g = torch.Generator().manual_seed(3)
-    q = (torch.randn(3, 128, 576, generator=g) * 4).bfloat16()
-    kv = (torch.randn(256, 576, generator=g) * 4).bfloat16()
+    # scores with a standard deviation near 100: the softmax is close to one-hot and the running
+    # maximum moves by large steps between tiles (kv stays N(0,1) so that the absolute output
+    # tolerance keeps its meaning)
+    q = (torch.randn(3, 128, 576, generator=g) * 8).bfloat16()
+    kv = torch.randn(256, 576, generator=g).bfloat16()
     idx = torch.stack([torch.randperm(256, generator=g)[:128] for _ in range(3)]).int()
-    _check(q, kv, idx, 1.0, "large_scores")
+    _check(q, kv, idx, 0.5, "large_scores")
 
 
 def test_order_invariance_determinism_and_token_sharding():
