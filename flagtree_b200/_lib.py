@@ -32,6 +32,14 @@ class SparseMlaArgs(C.Structure):
     ]
 
 
+class GemmArgs(C.Structure):
+    """Mirror of `ftb_gemm_args`."""
+    _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p),
+                ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+                ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64),
+                ("status", C.c_void_p)]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -57,6 +65,19 @@ def load() -> C.CDLL:
             lib.ftb_sparse_mla_fwd.restype = C.c_int
             if lib.ftb_sizeof_sparse_mla_args() != C.sizeof(SparseMlaArgs):
                 raise RuntimeError("ftb_sparse_mla_args layout differs between the header and the Python mirror")
+            if lib.ftb_sizeof_gemm_args() != C.sizeof(GemmArgs):
+                raise RuntimeError("ftb_gemm_args layout differs between the header and the Python mirror")
+            lib.ftb_gemm_bf16.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+            lib.ftb_gemm_rs_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+            lib.ftb_gemm_rs_ctx_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int,
+                                                   C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
+            lib.ftb_gemm_rs_ctx_destroy.argtypes = [C.c_void_p]
+            lib.ftb_gemm_rs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
+                                        C.c_int64, C.c_void_p, C.c_void_p]
+            lib.ftb_ipc_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_uint8)]
+            lib.ftb_ipc_open.argtypes = [C.POINTER(C.c_uint8), C.POINTER(C.c_void_p)]
+            lib.ftb_ipc_close.argtypes = [C.c_void_p]
+            lib.ftb_ipc_free.argtypes = [C.c_void_p]
             _lib = lib
     return _lib
 

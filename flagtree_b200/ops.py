@@ -174,3 +174,110 @@ def decode_attention_fwd(q, k_buffer, v_buffer, o, req_to_token, b_seq_len, attn
         sm_scale = D_QK ** -0.5
     sparse_mla_fwd(q, kv, idx.contiguous(), sm_scale, out=o)
     return o
+
+
+# ------------------------------------------------------------------------------------- GEMM
+def matmul(a: torch.Tensor, b: torch.Tensor, acc_dtype=None, input_precision=None, fp8_fast_accum=True,
+           output_dtype=None, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A @ B for bf16 operands with fp32 accumulation; same call shape as the reference's
+    `triton.ops.matmul` (python/triton/ops/matmul.py:231-236).  Non-contiguous inputs are copied as
+    the reference does (:165-168); the shape check is the reference's assertion (:170)."""
+    _require_cuda(a, b)
+    if a.stride(0) > 1 and a.stride(1) > 1:
+        a = a.contiguous()
+    if b.stride(0) > 1 and b.stride(1) > 1:
+        b = b.contiguous()
+    assert a.shape[1] == b.shape[0], "incompatible dimensions"
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "bf16 operands only"
+    assert acc_dtype in (None, torch.float32), "bf16 inputs accumulate in fp32"
+    assert output_dtype in (None, torch.bfloat16)
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    m, k = a.shape
+    n = b.shape[1]
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    _gemm_into(a, b, out)
+    return out
+
+
+def _gemm_into(a, b, c, status=None):
+    g = _lib.GemmArgs()
+    g.a, g.b, g.c = a.data_ptr(), b.data_ptr(), c.data_ptr()
+    g.m, g.n, g.k = a.shape[0], b.shape[1], a.shape[1]
+    g.lda, g.ldb, g.ldc = a.stride(0), b.stride(0), c.stride(0)
+    g.status = status.data_ptr() if status is not None else None
+    with torch.cuda.device(a.device):
+        rc = _lib.load().ftb_gemm_bf16(C.byref(g), C.c_void_p(_stream_ptr(a.device)))
+    _lib.check(rc, "matmul")
+
+
+class GemmRsContext:
+    """Workspace of one (M, N, group) GEMM + reduce-scatter shape: peer-mapped receive slots and flags.
+
+    Creation is collective over `group`.  One call may be in flight per context.
+    """
+
+    def __init__(self, m: int, n: int, group=None, device: Optional[torch.device] = None, provider: str = "auto"):
+        import torch.distributed as dist
+        from .symm import SymmetricBuffer
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.tp = dist.get_world_size(group)
+        self.m, self.n = m, n
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        lib = _lib.load()
+        rb, fb = C.c_int64(), C.c_int64()
+        _lib.check(lib.ftb_gemm_rs_workspace_bytes(m, n, self.tp, C.byref(rb), C.byref(fb)), "gemm_rs workspace")
+        with torch.cuda.device(self.device):
+            self.recv = SymmetricBuffer(rb.value, group, self.device, provider)
+            self.flags = SymmetricBuffer(fb.value, group, self.device, provider)
+            recv_ptrs = (C.c_void_p * self.tp)(*self.recv.ptrs)
+            flag_ptrs = (C.c_void_p * self.tp)(*self.flags.ptrs)
+            ctx = C.c_void_p()
+            _lib.check(lib.ftb_gemm_rs_ctx_create(C.byref(ctx), self.rank, self.tp, m, n, recv_ptrs, flag_ptrs),
+                       "gemm_rs ctx_create")
+        self._ctx = ctx
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(a, b)
+        assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+        assert a.shape[0] == self.m and b.shape[1] == self.n and a.shape[1] == b.shape[0], "incompatible dimensions"
+        assert a.stride(1) == 1 and b.stride(1) == 1
+        if out is None:
+            out = torch.empty(self.m // self.tp, self.n, dtype=torch.bfloat16, device=a.device)
+        assert out.shape == (self.m // self.tp, self.n) and out.stride(1) == 1
+        with torch.cuda.device(a.device):
+            rc = _lib.load().ftb_gemm_rs(self._ctx, a.data_ptr(), b.data_ptr(), out.data_ptr(), a.shape[1],
+                                         a.stride(0), b.stride(0), out.stride(0), self.status.data_ptr(),
+                                         C.c_void_p(_stream_ptr(a.device)))
+        _lib.check(rc, "gemm_rs")
+        return out
+
+    def check(self):
+        _check_status(self.status, "gemm_rs")
+
+    def close(self):
+        if self._ctx is not None:
+            torch.cuda.synchronize(self.device)
+            _lib.load().ftb_gemm_rs_ctx_destroy(self._ctx)
+            self._ctx = None
+            self.recv.close()
+            self.flags.close()
+
+
+_RS_CONTEXTS = {}
+
+
+def gemm_rs(a: torch.Tensor, b: torch.Tensor, group=None, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Row-parallel GEMM fused with reduce-scatter: rank r passes A_r [M, K/tp] and B_r [K/tp, N] and gets
+    rows [r*M/tp, (r+1)*M/tp) of sum_r A_r @ B_r as bf16.  Collective over `group`; the workspace of each
+    (M, N, group) is created on first use and cached."""
+    key = (a.shape[0], b.shape[1], id(group), a.device.index)
+    ctx = _RS_CONTEXTS.get(key)
+    if ctx is None:
+        ctx = _RS_CONTEXTS[key] = GemmRsContext(a.shape[0], b.shape[1], group, a.device)
+    return ctx(a, b, out)

@@ -84,6 +84,57 @@ FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* args, void* stream);
 /* sizeof(ftb_sparse_mla_args) as compiled into the library (for bindings to check their mirror). */
 FTB_API int ftb_sizeof_sparse_mla_args(void);
 
+/* ------------------------------------------------------------------------------------------
+ * Dense GEMM  C[M,N] = A[M,K] . B[K,N]  (bf16 in, fp32 accumulate, bf16 out; row-major).
+ *
+ * Takes the place of the Triton kernel behind the reference's matmul op,
+ *   python/triton/ops/matmul.py:92-151 (_kernel) launched from :218-227, at the `spec("matmul_kernel",
+ *   grid, a, b, c, M, N, K, ...)` backend hook of :218: it writes into the caller-allocated `c`.
+ * fp32 accumulation for bf16 inputs follows matmul.py:184-190.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ftb_gemm_args {
+  const void* a;   /* bf16 [m, k], lda */
+  const void* b;   /* bf16 [k, n], ldb */
+  void* c;         /* bf16 [m, n], ldc */
+  int32_t m, n, k;
+  int64_t lda, ldb, ldc;
+  int32_t* status; /* optional device status word */
+} ftb_gemm_args;
+
+FTB_API int ftb_gemm_bf16(const ftb_gemm_args* args, void* stream);
+FTB_API int ftb_sizeof_gemm_args(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Row-parallel GEMM fused with reduce-scatter (tensor parallel size tp, one rank per GPU).
+ *
+ * Rank r holds A_r [M, K/tp] and B_r [K/tp, N]; C = sum_r A_r.B_r; rank r receives rows
+ * [r*M/tp, (r+1)*M/tp) of C as bf16.  The reference has no collective of any kind (no call site of
+ * a reduce-scatter exists in it); the GEMM core replaces python/triton/ops/matmul.py:92-151 and the
+ * persistent tile loop of python/test/unit/hopper/test_persistent_warp_specialized_gemm.py:38-125,
+ * and the cross-rank sum follows the definition "sum over ranks in rank order, fp32, scatter along M".
+ *
+ * Workspace: every rank provides a receive buffer (recv_bytes) and a flag buffer (flag_bytes), both
+ * zero-initialised and mapped into every peer (CUDA IPC, cuMem export, or a symmetric-memory
+ * allocator); `recv_ptrs[i]` / `flag_ptrs[i]` are THIS process's device pointers to rank i's buffers
+ * (host arrays of tp pointers).  One call may be in flight per context; calls must be issued in the
+ * same order on every rank.  Device-side waits are bounded (FTB_ERR_TIMEOUT in the status word).
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ftb_gemm_rs_ctx ftb_gemm_rs_ctx;
+FTB_API int ftb_gemm_rs_workspace_bytes(int m, int n, int tp, int64_t* recv_bytes, int64_t* flag_bytes);
+FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** ctx, int rank, int tp, int m, int n,
+                                   void* const* recv_ptrs, void* const* flag_ptrs);
+FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* ctx);
+/* a [m, k_local] bf16, b [k_local, n] bf16, out [m/tp, n] bf16 (this rank's shard). */
+FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* ctx, const void* a, const void* b, void* out, int k_local,
+                        int64_t lda, int64_t ldb, int64_t ldo, int32_t* status, void* stream);
+
+/* CUDA IPC helpers for callers without a symmetric-memory allocator: allocate a zeroed device buffer
+ * and export a 64-byte handle; open a peer's handle (enables peer access lazily); close; free. */
+FTB_API int ftb_ipc_alloc(int64_t bytes, void** ptr, uint8_t handle[64]);
+FTB_API int ftb_ipc_open(const uint8_t handle[64], void** ptr);
+FTB_API int ftb_ipc_close(void* ptr);
+FTB_API int ftb_ipc_free(void* ptr);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,56 @@
+"""Worker of the multi-GPU GEMM + reduce-scatter test: one process per GPU (torchrun).  Every rank
+builds all ranks' seeded inputs, so each can check its own shard against the CPU oracle."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from flagtree_b200 import GemmRsContext  # noqa: E402
+from flagtree_b200 import workloads as W  # noqa: E402
+from oracle.gemm_rs_ref import gemm_rs_ref  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    provider = os.environ.get("FTB_SYMM_PROVIDER", "auto")
+    ok = True
+    for (m, n, k_total) in [(world * 128, 256, world * 64), (world * 256, 1024, world * 320), (world * 1024, 7168, world * 2304 // 4)]:
+        cases = [W.gemm_cfg4(tp=world, rank=r, m=m, n=n, k_total=k_total) for r in range(world)]
+        ref = gemm_rs_ref([c.a for c in cases], [c.b for c in cases])[rank]
+        ctx = GemmRsContext(m, n, None, dev, provider)
+        a, b = cases[rank].a.to(dev), cases[rank].b.to(dev)
+        outs = []
+        for it in range(3):                      # repeated calls reuse the slots (epoch handling)
+            outs.append(ctx(a, b).clone())
+        torch.cuda.synchronize()
+        ctx.check()
+        nccl_in = (a.float() @ b.float())
+        nccl_out = torch.empty(m // world, n, dtype=torch.float32, device=dev)
+        dist.reduce_scatter_tensor(nccl_out, nccl_in)
+        err = (outs[0].float().cpu() - ref).abs().max().item()
+        scale = ref.abs().max().item()
+        err_nccl = (outs[0].float() - nccl_out).abs().max().item()
+        same = all(torch.equal(outs[0], o) for o in outs[1:])
+        print(f"[rank {rank}] m={m} n={n} k={k_total} provider={ctx.recv.provider}: err {err:.3e} scale {scale:.3e} "
+              f"vs-nccl {err_nccl:.3e} repeat-identical {same}", flush=True)
+        # partials are rounded to bf16 before the cross-rank sum: world roundings of 2^-9 each
+        tol = (world + 1) * 2 ** -9 * scale
+        ok = ok and err <= tol and err_nccl <= tol and same
+        ctx.close()
+        dist.barrier()
+    t = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    sys.exit(0 if int(t.item()) == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()

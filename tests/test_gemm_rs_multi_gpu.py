@@ -1,0 +1,25 @@
+"""GEMM + reduce-scatter on 2 or more GPUs (skipped on a single-GPU box): child processes under torchrun."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(world, provider):
+    env = dict(os.environ, FTB_SYMM_PROVIDER=provider, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(ROOT, "tests", "_gemm_rs_worker.py")]
+    r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
+    print(r.stdout[-4000:])
+    assert r.returncode == 0
+
+
+@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
+@pytest.mark.parametrize("provider", ["auto", "cuda_ipc"])
+def test_gemm_rs_matches_oracle(provider):
+    _run(min(torch.cuda.device_count(), 8), provider)

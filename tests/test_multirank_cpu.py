@@ -1,0 +1,92 @@
+"""Host-side multi-rank logic on CPU (gloo, world_size 2): handle exchange of the symmetric workspace,
+token sharding of the sparse MLA batch, and the reduce-scatter sharding convention of the oracle."""
+import os
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from flagtree_b200 import workloads as W
+
+
+def _worker(rank, world, port, fn_name, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        globals()[fn_name](rank, world)
+        q.put((rank, "ok"))
+    except Exception as e:   # noqa: BLE001
+        q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def _spawn(fn_name, world=2, port=29611):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, fn_name, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(r[1] == "ok" for r in res), res
+
+
+def _case_symmetric_exchange(rank, world):
+    from flagtree_b200.symm import SymmetricBuffer
+    opened = []
+
+    def alloc(nbytes):
+        return 1000 * (rank + 1), f"handle-of-{rank}-{nbytes}".encode()
+
+    def open_(handle):
+        opened.append(handle)
+        owner = int(handle.decode().split("-")[2])
+        return 1000 * (owner + 1) + 7          # a "mapped" address, distinct from the owner's own
+
+    buf = SymmetricBuffer(4096, None, None, _alloc=alloc, _open=open_)
+    assert buf.world == world and buf.local_ptr == 1000 * (rank + 1)
+    for r in range(world):
+        assert buf.ptrs[r] == (1000 * (r + 1) if r == rank else 1000 * (r + 1) + 7)
+    assert len(opened) == world - 1 and all(h.endswith(b"-4096") for h in opened)
+
+
+def _case_mla_token_sharding(rank, world):
+    from oracle.sparse_mla_ref import sparse_mla_fwd_ref
+    c = W.mla_cfg2(s_q=48, s_kv=48, h=4, topk=16)
+    lo, hi = W.shard_bounds(48, world, rank)
+    out, lse = sparse_mla_fwd_ref(c.q[lo:hi], c.kv, c.indices[lo:hi], c.sm_scale)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (lo, hi, out, lse))
+    full_out, full_lse = sparse_mla_fwd_ref(c.q, c.kv, c.indices, c.sm_scale)
+    covered = 0
+    for lo_r, hi_r, o_r, l_r in gathered:
+        assert torch.equal(o_r, full_out[lo_r:hi_r]) and torch.equal(l_r, full_lse[lo_r:hi_r])
+        covered += hi_r - lo_r
+    assert covered == 48
+
+
+def _case_reduce_scatter_convention(rank, world):
+    from oracle.gemm_rs_ref import gemm_rs_ref
+    cases = [W.gemm_cfg4(tp=world, rank=r, m=world * 8, n=16, k_total=world * 24) for r in range(world)]
+    ref = gemm_rs_ref([c.a for c in cases], [c.b for c in cases])[rank]
+    part = cases[rank].a.float() @ cases[rank].b.float()
+    out = torch.empty(8, 16)
+    dist.reduce_scatter_tensor(out, part)
+    assert torch.allclose(out, ref, rtol=1e-6, atol=1e-8)
+
+
+@pytest.mark.parametrize("fn,port", [("_case_symmetric_exchange", 29611), ("_case_mla_token_sharding", 29612),
+                                     ("_case_reduce_scatter_convention", 29613)])
+def test_two_ranks_gloo(fn, port):
+    _spawn(fn, 2, port)
+
+
+def test_shard_bounds_cover_everything():
+    for n in (0, 1, 7, 64, 4096):
+        for world in (1, 2, 3, 8):
+            spans = [W.shard_bounds(n, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(spans[i][1] == spans[i + 1][0] for i in range(world - 1))
