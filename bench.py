@@ -111,6 +111,68 @@ def cpu_baseline_mla(n_tokens: int, reps: int = 1):
             "seconds": best, "flops": flops}
 
 
+def bench_gemm_rs(args, dev, rank, world, dist, peaks):
+    """Second hot path: row-parallel bf16 GEMM fused with reduce-scatter at tp = number of GPUs, per-rank
+    shape of cfg4 (A [8192 x 2304], B [2304 x 7168]; K grows with tp).  tp = 1 is the plain GEMM.  Each
+    timed iteration is bracketed by its own CUDA events with an L2 flush (256 MB write) in between."""
+    from flagtree_b200 import GemmRsContext, matmul
+    from flagtree_b200 import workloads as W
+    m, n, k_loc = 8192, 7168, 2304
+    case = W.gemm_cfg4(device=dev, tp=world, rank=rank, m=m, n=n, k_total=k_loc * world)
+    flops = case.flops
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    c_full = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    iters = max(5, min(args.steps, 20))
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.fill_(1)
+            if dist is not None:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        ts.sort()
+        t = torch.tensor([ts[len(ts) // 2]], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    t_gemm = timed(lambda: matmul(case.a, case.b, out=c_full))
+    res = {"workload": f"gemm_rs_cfg4_per_rank_m{m}_n{n}_klocal{k_loc}_tp{world}", "tp": world, "dtype": "bf16",
+           "flops_per_gpu": flops, "gemm_only_ms": t_gemm, "gemm_only_tflops_per_gpu": flops / t_gemm / 1e9,
+           "l2": "256 MB flush write between timed iterations", "iters": iters, "timing": "median per rank, max over ranks"}
+    if world > 1:
+        ctx = GemmRsContext(m, n, None, dev)
+        out = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)
+        t_fused = timed(lambda: ctx(case.a, case.b, out))
+        ctx.check()
+        nccl_out = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)
+
+        def nccl_path():
+            matmul(case.a, case.b, out=c_full)
+            dist.reduce_scatter_tensor(nccl_out, c_full)
+
+        t_nccl = timed(nccl_path)
+        pushed = (world - 1) / world * m * n * 2
+        res.update({"fused_ms": t_fused, "tflops_per_gpu": flops / t_fused / 1e9,
+                    "frac_of_peak": flops / t_fused / 1e9 / peaks["bf16_tflops"],
+                    "exposed_comm": t_fused / t_gemm - 1.0, "gemm_plus_nccl_rs_ms": t_nccl,
+                    "pushed_bytes_per_gpu": pushed, "nvlink_floor_ms": pushed / 770e9 * 1e3,
+                    "symm_provider": ctx.recv.provider})
+        ctx.close()
+    else:
+        res.update({"tflops_per_gpu": flops / t_gemm / 1e9, "frac_of_peak": flops / t_gemm / 1e9 / peaks["bf16_tflops"]})
+    return res
+
+
 def run_reference(args, rank, world):
     """CPU arm: the restatement of the reference's torch idiom on the box's host cores."""
     if rank != 0:
@@ -146,6 +208,7 @@ def main():
     ap.add_argument("--s-q", type=int, default=4096, help="query tokens per rank (default = full cfg2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM + reduce-scatter section")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -252,6 +315,10 @@ def main():
         e2e = {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e}
 
+    gemm_rs = None
+    if not args.no_gemm:
+        gemm_rs = bench_gemm_rs(args, dev, rank, world, dist, load_peaks())
+
     if rank == 0:
         peaks = load_peaks()
         avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
@@ -281,6 +348,7 @@ def main():
                        "l2": "inputs larger than L2 (q 604 MB per step)", "sm_scale": case.sm_scale,
                        "flops_per_gpu_step": flops_rank},
             "roofline": roofline, "cpu_baseline": cpu_b, "e2e": e2e, "gpu_launches": args.steps,
+            "gemm_rs": gemm_rs,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
