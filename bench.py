@@ -123,6 +123,7 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     c_full = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
     iters = max(5, min(args.steps, 20))
+    sync_word = torch.zeros(1, device=dev)
 
     def timed(fn):
         for _ in range(3):
@@ -134,6 +135,8 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
                 dist.barrier()
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if dist is not None:
+                dist.all_reduce(sync_word)      # aligns the ranks' streams on the device before the start event
             e0.record()
             fn()
             e1.record()

@@ -1,7 +1,9 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a: C[M,N] = A[M,K] . B[K,N], bf16 in, fp32
-// accumulate in TMEM, bf16 out -- and the same kernel with a reduce-scatter epilogue that stores every
-// finished tile straight into the receive slot of the rank that owns those rows (peer memory over
-// NVLink, plain st.global; no multicast load anywhere), followed by a fixed-order fp32 reduction.
+// accumulate in TMEM, bf16 out -- and the same kernel with a reduce-scatter epilogue: a finished tile
+// whose rows belong to another rank is stored (TMA store from a staging box, never a multicast load)
+// straight into that rank's receive slot in peer memory over NVLink and a per-(source, row block)
+// counter is released; tiles of this rank's own rows are computed last and their epilogue adds the
+// partials the other ranks have pushed (fixed order, fp32) before writing the bf16 shard.
 //
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM), warps 2-5 = epilogue.
 // Tile 128 x 256, K step 64, 4 shared-memory stages of 48 KB, two 256-column TMEM accumulators so the
@@ -25,7 +27,8 @@ constexpr int A_BYTES = BM * BK * 2;                 // 16384
 constexpr int B_BLOCK_BYTES = BK * 128;              // 8192: 64 k-rows x 64 columns
 constexpr int B_BYTES = (BN / 64) * B_BLOCK_BYTES;   // 32768
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 49152
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int STAGING_BYTES = 4 /*warps*/ * 2 /*buffers*/ * 4096;   // [32 rows x 128 B] boxes for TMA stores
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr int THREADS = 192;
 constexpr int MAX_TP = 8;
 
@@ -40,7 +43,16 @@ struct Params {
   __nv_bfloat16* recv[MAX_TP];       // base of dst's receive buffer [tp][shard_rows][n] (peer-mapped)
   unsigned int* flags[MAX_TP];       // base of dst's flag array [tp][blocks_per_shard] then done[tp]
   unsigned int epoch;                // this call's sequence number (>= 1)
+  unsigned int flag_target;          // value every (src, row block) counter reaches in this call
+  __nv_bfloat16* out;                // this rank's shard [shard_rows, n]
+  long long ldo;
+  unsigned int* counter;             // CTA completion counter (device, zero between calls)
   int* status;
+};
+
+// One tensor map per destination rank: that rank's receive slot for THIS rank, [shard_rows, n] bf16.
+struct OutMaps {
+  CUtensorMap m[MAX_TP];
 };
 
 struct Bars {
@@ -80,13 +92,25 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src),
+               "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_pending4() { asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ OutMaps tm_out, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - raw_addr);
-  Bars* bars = reinterpret_cast<Bars*>(sm + STAGES * STAGE_BYTES);
+  Bars* bars = reinterpret_cast<Bars*>(sm + STAGES * STAGE_BYTES + STAGING_BYTES);
+  const uint32_t staging = base + STAGES * STAGE_BYTES;
   volatile int* abort_flag = &bars->abort_flag;
 
   const int tid = threadIdx.x;
@@ -169,22 +193,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2-5)
     const int lg = warp & 3;                         // TMEM lane group this warp may read
-    uint32_t local = 0;
+    const uint32_t stg = staging + lg * 8192;        // this warp's two 4 KB staging boxes
+    uint32_t local = 0, box_it = 0;
+    unsigned int* pending_flag = nullptr;            // lane 0: counter of the last remote tile, not yet released
     for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++local) {
       int m_blk, n_blk, dst;
       tile_coords(p, t, m_blk, n_blk, dst);
       const uint32_t acc = local & 1u;
-      __nv_bfloat16* out_base;
-      long long ld;
-      int row_local;
       const int row = m_blk * BM + lg * 32 + lane;
-      if (p.tp <= 1) {
-        out_base = p.c;
-        ld = p.ldc;
-        row_local = row;
-      } else {
-        // slot `rank` of dst's receive buffer; before the first store make sure dst has finished
-        // reducing the previous call (its done[] word, written by dst into this rank's memory).
+      const bool remote = p.tp > 1 && dst != p.rank;
+      if (remote) {
+        // Before the first store into dst's receive slot make sure dst has consumed the previous
+        // call's data (its done[] word, written by dst into this rank's flag buffer).
         if (lane == 0) {
           const unsigned int* done = p.flags[p.rank] + p.tp * p.blocks_per_shard + dst;
           if (ld_acquire_sys(done) + 1u < p.epoch && !*abort_flag) {
@@ -196,45 +216,145 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
         __syncwarp();
-        out_base = p.recv[dst] + static_cast<long long>(p.rank) * p.shard_rows * p.n;
-        ld = p.n;
-        row_local = row - dst * p.shard_rows;
-      }
-      mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
-      tc_fence_after();
-      const bool row_ok = row < p.m;
-      __nv_bfloat16* orow = out_base + static_cast<long long>(row_local) * ld + n_blk * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld32(tmem_addr(tmem, lg * 32, acc * BN + c0), v);
-        tmem_wait_ld();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            const int col = n_blk * BN + c0 + j;
-            if (col < p.n) {   // n is a multiple of 8
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-              o.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-              o.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-              o.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-              *reinterpret_cast<uint4*>(orow + c0 + j) = o;
+      } else if (p.tp > 1) {
+        // Own rows: every other rank's partial tile must have landed in this rank's receive slots.
+        if (lane == 0) {
+          // Never enter this wait while holding back a release of our own (peers wait for it too).
+          if (pending_flag != nullptr) {
+            bulk_wait_all();
+            fence_proxy_async_smem();
+            __threadfence_system();
+            red_release_sys_add(pending_flag, 1u);
+            pending_flag = nullptr;
+          }
+          const int blk = m_blk - dst * p.blocks_per_shard;
+          for (int src = 0; src < p.tp; ++src) {
+            if (src == p.rank) continue;
+            const unsigned int* f = p.flags[p.rank] + src * p.blocks_per_shard + blk;
+            if (ld_acquire_sys(f) < p.flag_target && !*abort_flag) {
+              const long long t0 = clock64();
+              while (ld_acquire_sys(f) < p.flag_target) {
+                if (*abort_flag) break;
+                if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; break; }
+              }
             }
           }
         }
+        __syncwarp();
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
-      if (p.tp > 1) {
-        // Publish: this warp's 32 rows of the tile are stored.  The owner counts 4 arrivals per tile.
-        __threadfence_system();
+      mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
+      tc_fence_after();
+
+      if (remote) {
+        // bf16 partial tile -> swizzled staging box -> TMA store into the owner's receive slot.
+        const int y = (m_blk - dst * p.blocks_per_shard) * BM + lg * 32;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 64, ++box_it) {
+          const uint32_t buf = stg + (box_it & 1u) * 4096;
+          if (lane == 0) bulk_wait_read1();          // the store that last used this buffer has read it
+          __syncwarp();
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t v[32];
+            tmem_ld32(tmem_addr(tmem, lg * 32, acc * BN + c0 + hh * 32), v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int ch = hh * 4 + (j >> 3);
+              const uint32_t d = buf + lane * 128 + ((ch ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d),
+                           "r"(pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]))),
+                           "r"(pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]))),
+                           "r"(pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]))),
+                           "r"(pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])))
+                           : "memory");
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tm_out.m[dst], buf, n_blk * BN + c0, y);
+            bulk_commit();
+          }
+        }
+        tc_fence_before();
         __syncwarp();
         if (lane == 0) {
+          mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+          // Publish the PREVIOUS remote tile of this warp: its 4 store groups are older than the 4
+          // just committed, so "at most 4 groups pending" means they have completed.  The owner
+          // counts 4 arrivals (warps) per tile.
+          if (pending_flag != nullptr) {
+            bulk_wait_pending4();
+            fence_proxy_async_smem();
+            __threadfence_system();
+            red_release_sys_add(pending_flag, 1u);
+          }
           const int blk = m_blk - dst * p.blocks_per_shard;
-          red_release_sys_add(p.flags[dst] + p.rank * p.blocks_per_shard + blk, 1u);
+          pending_flag = p.flags[dst] + p.rank * p.blocks_per_shard + blk;
         }
+        __syncwarp();
+      } else {
+        __nv_bfloat16* orow;
+        const __nv_bfloat16* rrow = nullptr;
+        long long slot = 0;
+        if (p.tp <= 1) {
+          orow = p.c + static_cast<long long>(row) * p.ldc + n_blk * BN;
+        } else {
+          const int rl = row - dst * p.shard_rows;
+          orow = p.out + static_cast<long long>(rl) * p.ldo + n_blk * BN;
+          rrow = p.recv[p.rank] + static_cast<long long>(rl) * p.n + n_blk * BN;
+          slot = static_cast<long long>(p.shard_rows) * p.n;
+        }
+        const bool row_ok = row < p.m;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_addr(tmem, lg * 32, acc * BN + c0), v);
+          tmem_wait_ld();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int col = n_blk * BN + c0 + j;
+              if (col < p.n) {   // n is a multiple of 8
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[j + e]);
+                if (rrow != nullptr) {
+                  // fixed-order cross-rank sum: own fp32 accumulator, then sources 0..tp-1
+                  for (int src = 0; src < p.tp; ++src) {
+                    if (src == p.rank) continue;
+                    const uint4 w = *reinterpret_cast<const uint4*>(rrow + src * slot + c0 + j);
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 ff = __bfloat1622float2(h2[e]);
+                      f[2 * e] += ff.x;
+                      f[2 * e + 1] += ff.y;
+                    }
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]);
+                o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]);
+                o.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(orow + c0 + j) = o;
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+      }
+    }
+    if (lane == 0) {
+      bulk_wait_all();
+      if (pending_flag != nullptr) {
+        fence_proxy_async_smem();
+        __threadfence_system();
+        red_release_sys_add(pending_flag, 1u);
       }
     }
   }
@@ -246,67 +366,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     tmem_dealloc(tmem, 512);
   }
   if (tid == 0 && p.status != nullptr && bars->abort_flag) atomicCAS(p.status, 0, FTB_ERR_TIMEOUT);
-}
-
-// Owner-side reduction: out[row, :] = sum over src (fixed order 0..tp-1, fp32) of recv[src][row, :].
-// One CTA per (row block of 128, column slab); waits (bounded) until every source has published all
-// tiles of the row block for this epoch.
-__global__ void __launch_bounds__(256)
-reduce_scatter_sum_kernel(const __nv_bfloat16* __restrict__ recv, unsigned int* flags, __nv_bfloat16* __restrict__ out,
-                          long long ldo, int tp, int rank, int shard_rows, int n, int blocks_per_shard,
-                          unsigned int target, unsigned int epoch, unsigned int* const* peer_flags, unsigned int* counter,
-                          int* status) {
-  __shared__ int s_abort;
-  const int blk = blockIdx.y;
-  if (threadIdx.x == 0) {
-    int ab = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
-    for (int src = 0; src < tp && !ab; ++src) {
-      const unsigned int* f = flags + src * blocks_per_shard + blk;
-      const long long t0 = clock64();
-      while (gemm::ld_acquire_sys(f) < target) {
-        if (clock64() - t0 > kWaitLimitCycles) { ab = 1; break; }
-      }
-    }
-    s_abort = ab;
-    if (ab && status != nullptr) atomicCAS(status, 0, FTB_ERR_TIMEOUT);
-  }
-  __syncthreads();
-  if (!s_abort) {
-    const int vec_per_row = n / 8;
-    const int rows = min(128, shard_rows - blk * 128);
-    const long long slot = static_cast<long long>(shard_rows) * n;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows * vec_per_row; i += gridDim.x * blockDim.x) {
-      const int r = blk * 128 + i / vec_per_row;
-      const int c = (i % vec_per_row) * 8;
-      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      for (int src = 0; src < tp; ++src) {
-        const uint4 v = *reinterpret_cast<const uint4*>(recv + src * slot + static_cast<long long>(r) * n + c);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = __bfloat1622float2(h[j]);
-          acc[2 * j] += f.x;
-          acc[2 * j + 1] += f.y;
-        }
-      }
-      uint4 o;
-      o.x = pack_bf16x2(acc[0], acc[1]);
-      o.y = pack_bf16x2(acc[2], acc[3]);
-      o.z = pack_bf16x2(acc[4], acc[5]);
-      o.w = pack_bf16x2(acc[6], acc[7]);
-      *reinterpret_cast<uint4*>(out + static_cast<long long>(r) * ldo + c) = o;
-    }
-  }
-  // The last CTA to finish tells every peer that this rank's receive slots may be overwritten.
-  __syncthreads();
-  if (threadIdx.x == 0) {
+  if (tid == 0 && p.tp > 1) {
+    // The last CTA to finish tells every peer that this rank's receive slots may be overwritten.
     __threadfence();
-    const unsigned int total = gridDim.x * gridDim.y;
-    const unsigned int prev = atomicAdd(counter, 1u);
-    if (prev == total - 1) {
-      *counter = 0;
-      for (int peer = 0; peer < tp; ++peer)
-        gemm::st_release_sys(peer_flags[peer] + tp * blocks_per_shard + rank, epoch);
+    const unsigned int prev = atomicAdd(p.counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *p.counter = 0;
+      for (int peer = 0; peer < p.tp; ++peer)
+        st_release_sys(p.flags[peer] + p.tp * p.blocks_per_shard + p.rank, p.epoch);
     }
   }
 }
@@ -318,7 +385,7 @@ reduce_scatter_sum_kernel(const __nv_bfloat16* __restrict__ recv, unsigned int* 
 using namespace ftb;
 
 static int launch_gemm(const void* a, const void* b, int m, int n, int k, long long lda, long long ldb,
-                       gemm::Params& p, cudaStream_t st) {
+                       gemm::Params& p, const gemm::OutMaps& maps, cudaStream_t st) {
   if (m <= 0 || n <= 0 || k <= 0) { set_last_error("gemm: bad sizes m=%d n=%d k=%d", m, n, k); return FTB_ERR_INVALID; }
   if ((n % 8) || (k % 8) || (lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(a) & 15) ||
       (reinterpret_cast<uintptr_t>(b) & 15)) {
@@ -341,7 +408,7 @@ static int launch_gemm(const void* a, const void* b, int m, int n, int k, long l
   const int grid = p.n_tiles < sms ? p.n_tiles : sms;
   cudaError_t e = cudaFuncSetAttribute(gemm::gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES);
   if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm)");
-  gemm::gemm_bf16_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, st>>>(tm_a, tm_b, p);
+  gemm::gemm_bf16_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, st>>>(tm_a, tm_b, maps, p);
   return check_cuda(cudaGetLastError(), "gemm launch");
 }
 
@@ -357,16 +424,17 @@ extern "C" FTB_API int ftb_gemm_bf16(const ftb_gemm_args* g, void* stream) {
   p.ldc = g->ldc;
   p.tp = 1;
   p.status = g->status;
-  return launch_gemm(g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, p, reinterpret_cast<cudaStream_t>(stream));
+  static gemm::OutMaps no_maps;   // unused when tp == 1
+  return launch_gemm(g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, p, no_maps, reinterpret_cast<cudaStream_t>(stream));
 }
 
 struct ftb_gemm_rs_ctx {
   int rank, tp, m, n, shard_rows, blocks_per_shard;
   void* recv[gemm::MAX_TP];
   unsigned int* flags[gemm::MAX_TP];
-  unsigned int** d_peer_flags;   // device copy of flags[]
   unsigned int* d_counter;
   unsigned int epoch;
+  gemm::OutMaps maps;            // TMA store maps: receive slot of this rank on every peer
 };
 
 extern "C" FTB_API int ftb_gemm_rs_workspace_bytes(int m, int n, int tp, int64_t* recv_bytes, int64_t* flag_bytes) {
@@ -397,9 +465,16 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
     c->recv[i] = recv_ptrs[i];
     c->flags[i] = reinterpret_cast<unsigned int*>(flag_ptrs[i]);
   }
-  cudaError_t e = cudaMalloc(&c->d_peer_flags, sizeof(unsigned int*) * gemm::MAX_TP);
-  if (e == cudaSuccess) e = cudaMalloc(&c->d_counter, sizeof(unsigned int));
-  if (e == cudaSuccess) e = cudaMemcpy(c->d_peer_flags, c->flags, sizeof(unsigned int*) * tp, cudaMemcpyHostToDevice);
+  memset(&c->maps, 0, sizeof(c->maps));
+  for (int i = 0; i < tp; ++i) {
+    const char* slot = reinterpret_cast<const char*>(c->recv[i]) + static_cast<size_t>(rank) * c->shard_rows * n * 2;
+    if (!make_tmap_2d(&c->maps.m[i], slot, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c->shard_rows, n, n, 32, 64)) {
+      delete c;
+      set_last_error("ftb_gemm_rs_ctx_create: cuTensorMapEncodeTiled failed for the receive slot of rank %d", i);
+      return FTB_ERR_CUDA;
+    }
+  }
+  cudaError_t e = cudaMalloc(&c->d_counter, sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMemset(c->d_counter, 0, sizeof(unsigned int));
   if (e != cudaSuccess) { delete c; return check_cuda(e, "ftb_gemm_rs_ctx_create"); }
   *out = c;
@@ -408,7 +483,6 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
 
 extern "C" FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* c) {
   if (!c) return FTB_OK;
-  cudaFree(c->d_peer_flags);
   cudaFree(c->d_counter);
   delete c;
   return FTB_OK;
@@ -428,16 +502,13 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
     p.flags[i] = c->flags[i];
   }
   p.epoch = c->epoch;
-  p.status = status;
-  int rc = launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
-  if (rc != FTB_OK) return rc;
   const int n_blocks = (c->n + gemm::BN - 1) / gemm::BN;
-  const unsigned int target = c->epoch * static_cast<unsigned int>(n_blocks) * 4u;   // 4 epilogue warps per tile
-  dim3 grid(16, c->blocks_per_shard);
-  gemm::reduce_scatter_sum_kernel<<<grid, 256, 0, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(c->recv[c->rank]), c->flags[c->rank], reinterpret_cast<__nv_bfloat16*>(out), ldo,
-      c->tp, c->rank, c->shard_rows, c->n, c->blocks_per_shard, target, c->epoch, c->d_peer_flags, c->d_counter, status);
-  return check_cuda(cudaGetLastError(), "reduce_scatter_sum launch");
+  p.flag_target = c->epoch * static_cast<unsigned int>(n_blocks) * 4u;   // 4 epilogue warps per tile
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.counter = c->d_counter;
+  p.status = status;
+  return launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, c->maps, st);
 }
 
 // ---- CUDA IPC helpers for callers that do not have a symmetric-memory allocator of their own.
