@@ -144,6 +144,8 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
             ts.append(e0.elapsed_time(e1))
         ts.sort()
         t = torch.tensor([ts[len(ts) // 2]], dtype=torch.float64, device=dev)
+        if os.environ.get("FTB_BENCH_PER_RANK"):
+            print(f"[rank {rank}] median {float(t[0]):.4f} ms", file=sys.stderr, flush=True)
         if dist is not None:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])

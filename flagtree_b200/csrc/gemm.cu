@@ -1,7 +1,7 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a: C[M,N] = A[M,K] . B[K,N], bf16 in, fp32
 // accumulate in TMEM, bf16 out -- and the same kernel with a reduce-scatter epilogue: a finished tile
-// whose rows belong to another rank is stored (TMA store from a staging box, never a multicast load)
-// straight into that rank's receive slot in peer memory over NVLink and a per-(source, row block)
+// whose rows belong to another rank is stored (bulk shared->global copies of contiguous 4 KB boxes, never a
+// multicast load) straight into that rank's receive slot in peer memory over NVLink and a per-(source, row block)
 // counter is released; tiles of this rank's own rows are computed last and their epilogue adds the
 // partials the other ranks have pushed (fixed order, fp32) before writing the bf16 shard.
 //
@@ -10,6 +10,7 @@
 // epilogue of tile i overlaps the MMAs of tile i+1.
 //   A stage: [128 rows x 128 B] K-major, 128B swizzle (one TMA box)
 //   B stage: 4 blocks of [64 k-rows x 128 B] (64 N columns each), used as the MN-major operand.
+#include <cstdlib>
 #include <cstring>
 
 #include "sm100.cuh"
@@ -22,13 +23,21 @@ int check_cuda(cudaError_t e, const char* what);
 
 namespace gemm {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int MAX_STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;                 // 16384
 constexpr int B_BLOCK_BYTES = BK * 128;              // 8192: 64 k-rows x 64 columns
-constexpr int B_BYTES = (BN / 64) * B_BLOCK_BYTES;   // 32768
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 49152
-constexpr int STAGING_BYTES = 4 /*warps*/ * 2 /*buffers*/ * 4096;   // [32 rows x 128 B] boxes for TMA stores
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int STAGING_BYTES = 4 /*warps*/ * 2 /*buffers*/ * 4096;   // [32 rows x 128 B] boxes for bulk stores
+// NCTA = 1: one CTA per 128 x 256 tile, it loads all of B (4 blocks), 4 stages of 48 KB.
+// NCTA = 2: a CTA pair per 256 x 256 tile (cta_group::2 MMA); each CTA loads its 128 rows of A and
+//           its 128 columns of B (2 blocks), 6 stages of 32 KB: a third less L2->SM traffic per flop.
+template <int NCTA> struct Cfg {
+  static constexpr int B_BLOCKS = (BN / 64) / NCTA;
+  static constexpr int B_BYTES = B_BLOCKS * B_BLOCK_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = NCTA == 1 ? 4 : 6;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
 constexpr int THREADS = 192;
 constexpr int MAX_TP = 8;
 
@@ -48,36 +57,39 @@ struct Params {
   long long ldo;
   unsigned int* counter;             // CTA completion counter (device, zero between calls)
   int* status;
+  int dbg;                           // timing experiments only (env FTB_GEMM_RS_DEBUG): 1 no remote stores,
+                                     // 2 no reads of received partials, 4 no flag waits; results are wrong
 };
 
-// One tensor map per destination rank: that rank's receive slot for THIS rank, [shard_rows, n] bf16.
-struct OutMaps {
-  CUtensorMap m[MAX_TP];
-};
 
 struct Bars {
-  unsigned long long full[STAGES];
-  unsigned long long empty[STAGES];
+  unsigned long long full[MAX_STAGES];
+  unsigned long long empty[MAX_STAGES];
   unsigned long long acc_full[2];
   unsigned long long acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-__device__ __forceinline__ void tile_coords(const Params& p, int t, int& m_blk, int& n_blk, int& dst) {
+// Tile t of a CTA group (NCTA CTAs, each owning one 128-row block of the group tile) -> the 128-row
+// block of CTA `cta`, the 256-column block, and the rank that owns those rows.
+template <int NCTA>
+__device__ __forceinline__ void tile_coords(const Params& p, int t, int cta, int& m_blk, int& n_blk, int& dst) {
   if (p.tp <= 1) {
-    m_blk = t / p.n_blocks;
-    n_blk = t - m_blk * p.n_blocks;
+    const int mg = t / p.n_blocks;
+    n_blk = t - mg * p.n_blocks;
+    m_blk = mg * NCTA + cta;
     dst = 0;
     return;
   }
-  const int per_shard = p.blocks_per_shard * p.n_blocks;
+  const int groups_per_shard = p.blocks_per_shard / NCTA;
+  const int per_shard = groups_per_shard * p.n_blocks;
   const int ord = t / per_shard;                     // remote shards first, own shard last
   dst = (p.rank + 1 + ord) % p.tp;
   const int r = t - ord * per_shard;
-  const int mb = r / p.n_blocks;
-  n_blk = r - mb * p.n_blocks;
-  m_blk = dst * p.blocks_per_shard + mb;
+  const int mg = r / p.n_blocks;
+  n_blk = r - mg * p.n_blocks;
+  m_blk = dst * p.blocks_per_shard + mg * NCTA + cta;
 }
 
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
@@ -92,19 +104,120 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src),
-               "r"(x), "r"(y)
-               : "memory");
+// 4 KB contiguous shared -> global copy (the destination may be peer memory).
+__device__ __forceinline__ void bulk_store_4k(void* dst, uint32_t src) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], 4096;" ::"l"(dst), "r"(src) : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_pending4() { asm volatile("cp.async.bulk.wait_group 4;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// Epilogue of a tile whose rows this rank owns: out = own fp32 accumulator + partials of the other
+// ranks (ascending rank order, fp32), as bf16.  The partials are fetched with two 16-column slices in
+// flight per thread (NSRC x 2 16-byte loads each) and the first slice is requested before the
+// accumulator is complete, so the load latency overlaps the MMAs.  NSRC = tp - 1 (0 = generic path).
+template <int NSRC>
+__device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long long slot,
+                                                  __nv_bfloat16* orow, int n_blk, uint32_t full_bar, uint32_t parity,
+                                                  uint32_t tacc, volatile int* abort_flag, bool skip_reads) {
+  constexpr int NS = NSRC > 0 ? NSRC : 1;
+  // Receive slots are stored as contiguous 4 KB boxes of [32 rows x 64 columns] in the staging
+  // (128B-swizzled) order; `rrow` points at this thread's row inside box column 0 of its row group.
+  const __nv_bfloat16* rrow = p.recv[p.rank] + static_cast<long long>(rl >> 5) * (p.n >> 6) * 2048 + (rl & 31) * 64;
+  const int sw = rl & 7;
+  auto box_off = [&](int col) -> long long {   // element offset of 8 columns starting at absolute column `col`
+    return static_cast<long long>(col >> 6) * 2048 + ((((col & 63) >> 3) ^ sw) << 3);
+  };
+  const __nv_bfloat16* src_ptr[NS];
+  if constexpr (NSRC > 0) {
+#pragma unroll
+    for (int i = 0; i < NSRC; ++i) src_ptr[i] = rrow + (i + (i >= p.rank ? 1 : 0)) * slot;   // ascending, skipping self
+  }
+  uint4 bufA[NS][2], bufB[NS][2];
+  auto fetch = [&](uint4 (&buf)[NS][2], int col) {
+    if constexpr (NSRC > 0) {
+      if (!skip_reads && n_blk * BN + col < p.n) {
+#pragma unroll
+        for (int i = 0; i < NSRC; ++i) {
+          buf[i][0] = *reinterpret_cast<const uint4*>(src_ptr[i] + box_off(n_blk * BN + col));
+          buf[i][1] = *reinterpret_cast<const uint4*>(src_ptr[i] + box_off(n_blk * BN + col + 8));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NSRC; ++i) buf[i][0] = buf[i][1] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  auto finish = [&](const uint32_t* v, uint4 (&buf)[NS][2], int col) {
+    float f[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) f[e] = __uint_as_float(v[e]);
+    if constexpr (NSRC > 0) {
+#pragma unroll
+      for (int i = 0; i < NSRC; ++i) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&buf[i][h]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 ff = __bfloat1622float2(h2[e]);
+            f[h * 8 + 2 * e] += ff.x;
+            f[h * 8 + 2 * e + 1] += ff.y;
+          }
+        }
+      }
+    } else if (!skip_reads && n_blk * BN + col < p.n) {
+      for (int src = 0; src < p.tp; ++src) {
+        if (src == p.rank) continue;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint4 w = *reinterpret_cast<const uint4*>(rrow + src * slot + box_off(n_blk * BN + col + h * 8));
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 ff = __bfloat1622float2(h2[e]);
+            f[h * 8 + 2 * e] += ff.x;
+            f[h * 8 + 2 * e + 1] += ff.y;
+          }
+        }
+      }
+    }
+    if (n_blk * BN + col < p.n) {   // n is a multiple of 8 (and row blocks are full in this mode)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (n_blk * BN + col + h * 8 < p.n) {
+          uint4 o;
+          o.x = pack_bf16x2(f[h * 8], f[h * 8 + 1]);
+          o.y = pack_bf16x2(f[h * 8 + 2], f[h * 8 + 3]);
+          o.z = pack_bf16x2(f[h * 8 + 4], f[h * 8 + 5]);
+          o.w = pack_bf16x2(f[h * 8 + 6], f[h * 8 + 7]);
+          *reinterpret_cast<uint4*>(orow + col + h * 8) = o;
+        }
+      }
+    }
+  };
+  fetch(bufA, 0);
+  mbar_wait(full_bar, parity, abort_flag);
+  tc_fence_after();
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    fetch(bufB, c0 + 16);
+    uint32_t v[32];
+    tmem_ld32(tacc + c0, v);
+    tmem_wait_ld();
+    finish(v, bufA, c0);
+    if (c0 + 32 < BN) fetch(bufA, c0 + 32);
+    finish(v + 16, bufB, c0 + 16);
+  }
+}
+
+template <int NCTA>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                 const __grid_constant__ OutMaps tm_out, const Params p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
+  using C = Cfg<NCTA>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int STAGE_BYTES = C::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -117,6 +230,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int kb_total = (p.k + BK - 1) / BK;
+  const int cta = NCTA == 1 ? 0 : static_cast<int>(cluster_ctarank());   // position inside the CTA pair
+  const int group = blockIdx.x / NCTA;
+  const int n_groups = gridDim.x / NCTA;
 
   if (tid == 0) {
     bars->abort_flag = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
@@ -126,50 +242,69 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&bars->acc_full[a]), 1);
-      mbar_init(smem_u32(&bars->acc_empty[a]), 4);   // one arrival per epilogue warp
+      mbar_init(smem_u32(&bars->acc_empty[a]), 4 * NCTA);   // one arrival per epilogue warp of the group
     }
     fence_mbar_init();
     tma_prefetch_desc(&tm_a);
     tma_prefetch_desc(&tm_b);
   }
   __syncthreads();
+  // The status word is read before any CTA of this launch can have written it only if an EARLIER
+  // launch failed, so both CTAs of a pair take the same branch here.
   if (bars->abort_flag) return;
   if (warp == 1) {
-    tmem_alloc(smem_u32(&bars->tmem_base), 512);
-    tmem_relinquish();
+    if constexpr (NCTA == 1) {
+      tmem_alloc(smem_u32(&bars->tmem_base), 512);
+      tmem_relinquish();
+    } else {
+      tmem_alloc_pair(smem_u32(&bars->tmem_base), 512);
+      tmem_relinquish_pair();
+    }
     tc_fence_before();
   }
   __syncthreads();
+  if constexpr (NCTA == 2) cluster_sync_all();   // peer barriers are initialised before anyone signals them
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ TMA producer (every CTA)
     if (lane == 0) {
       uint32_t it = 0;
-      for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x) {
+      for (int t = group; t < p.n_tiles; t += n_groups) {
         int m_blk, n_blk, dst;
-        tile_coords(p, t, m_blk, n_blk, dst);
+        tile_coords<NCTA>(p, t, cta, m_blk, n_blk, dst);
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag);
-          const uint32_t full = smem_u32(&bars->full[s]);
-          mbar_arrive_expect_tx(full, STAGE_BYTES);
           const uint32_t a_dst = base + s * STAGE_BYTES;
-          tma_load_2d(a_dst, &tm_a, full, kb * BK, m_blk * BM);
+          if constexpr (NCTA == 1) {
+            const uint32_t full = smem_u32(&bars->full[s]);
+            mbar_arrive_expect_tx(full, STAGE_BYTES);
+            tma_load_2d(a_dst, &tm_a, full, kb * BK, m_blk * BM);
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_2d(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full, n_blk * BN + j * 64, kb * BK);
+            for (int j = 0; j < C::B_BLOCKS; ++j)
+              tma_load_2d(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full, n_blk * BN + j * 64, kb * BK);
+          } else {
+            // Both CTAs' loads are counted on the even CTA's barrier; that CTA announces the total.
+            const uint32_t full0 = mapa_shared(smem_u32(&bars->full[s]), 0);
+            if (cta == 0) mbar_arrive_expect_tx(smem_u32(&bars->full[s]), 2 * STAGE_BYTES);
+            tma_load_2d_pair(a_dst, &tm_a, full0, kb * BK, m_blk * BM);
+#pragma unroll
+            for (int j = 0; j < C::B_BLOCKS; ++j)
+              tma_load_2d_pair(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full0,
+                               n_blk * BN + (cta * C::B_BLOCKS + j) * 64, kb * BK);
+          }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, BM, BN, 0, 1);
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && cta == 0) {
+      constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, BM * NCTA, BN, 0, 1);
       uint32_t it = 0, local = 0;
-      for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++local) {
+      for (int t = group; t < p.n_tiles; t += n_groups, ++local) {
         const uint32_t acc = local & 1u;
         mbar_wait(smem_u32(&bars->acc_empty[acc]), ((local >> 1) & 1u) ^ 1u, abort_flag);
         tc_fence_after();
@@ -183,11 +318,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t ad = smem_desc_sw128(a_s + k * 32, 16, 1024);
             const uint64_t bd = smem_desc_sw128(b_s + k * 2048, B_BLOCK_BYTES, 1024);
-            umma_f16_ss(tmem + acc * BN, ad, bd, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (NCTA == 1) umma_f16_ss(tmem + acc * BN, ad, bd, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_f16_ss_pair(tmem + acc * BN, ad, bd, kIdesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(smem_u32(&bars->empty[s]));     // stage free once these MMAs have read it
+          // stage free (in every CTA of the group) once these MMAs have read it
+          if constexpr (NCTA == 1) {
+            umma_commit(smem_u32(&bars->empty[s]));
+          } else {
+            umma_commit_pair(mapa_shared(smem_u32(&bars->empty[s]), 0));
+            umma_commit_pair(mapa_shared(smem_u32(&bars->empty[s]), 1));
+          }
         }
-        umma_commit(smem_u32(&bars->acc_full[acc]));
+        if constexpr (NCTA == 1) {
+          umma_commit(smem_u32(&bars->acc_full[acc]));
+        } else {
+          umma_commit_pair(mapa_shared(smem_u32(&bars->acc_full[acc]), 0));
+          umma_commit_pair(mapa_shared(smem_u32(&bars->acc_full[acc]), 1));
+        }
       }
     }
   } else {
@@ -196,9 +343,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t stg = staging + lg * 8192;        // this warp's two 4 KB staging boxes
     uint32_t local = 0, box_it = 0;
     unsigned int* pending_flag = nullptr;            // lane 0: counter of the last remote tile, not yet released
-    for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x, ++local) {
+    long long t_prev_tile = 0;                       // when this warp started draining its previous remote tile
+    // the accumulator-free barrier the MMA issuer waits on lives in the even CTA
+    const uint32_t acc_empty_addr[2] = {
+        NCTA == 1 ? smem_u32(&bars->acc_empty[0]) : mapa_shared(smem_u32(&bars->acc_empty[0]), 0),
+        NCTA == 1 ? smem_u32(&bars->acc_empty[1]) : mapa_shared(smem_u32(&bars->acc_empty[1]), 0)};
+    auto release_acc = [&](uint32_t a) {
+      if constexpr (NCTA == 1) mbar_arrive(acc_empty_addr[a]);
+      else mbar_arrive_cluster(acc_empty_addr[a]);
+    };
+    for (int t = group; t < p.n_tiles; t += n_groups, ++local) {
       int m_blk, n_blk, dst;
-      tile_coords(p, t, m_blk, n_blk, dst);
+      tile_coords<NCTA>(p, t, cta, m_blk, n_blk, dst);
       const uint32_t acc = local & 1u;
       const int row = m_blk * BM + lg * 32 + lane;
       const bool remote = p.tp > 1 && dst != p.rank;
@@ -218,7 +374,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();
       } else if (p.tp > 1) {
         // Own rows: every other rank's partial tile must have landed in this rank's receive slots.
-        if (lane == 0) {
+        if (lane == 0 && !(p.dbg & 4)) {
           // Never enter this wait while holding back a release of our own (peers wait for it too).
           if (pending_flag != nullptr) {
             bulk_wait_all();
@@ -242,45 +398,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         __syncwarp();
       }
-      mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
-      tc_fence_after();
-
       if (remote) {
-        // bf16 partial tile -> swizzled staging box -> TMA store into the owner's receive slot.
-        const int y = (m_blk - dst * p.blocks_per_shard) * BM + lg * 32;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 64, ++box_it) {
-          const uint32_t buf = stg + (box_it & 1u) * 4096;
-          if (lane == 0) bulk_wait_read1();          // the store that last used this buffer has read it
-          __syncwarp();
+        mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
+        tc_fence_after();
+        // Drain the accumulator into registers as packed bf16 and hand the TMEM buffer back at once,
+        // so that a slow link only delays this warp's stores, not the MMAs of the next tiles.
+        uint32_t pk[BN / 2];
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            uint32_t v[32];
-            tmem_ld32(tmem_addr(tmem, lg * 32, acc * BN + c0 + hh * 32), v);
-            tmem_wait_ld();
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tmem_addr(tmem, lg * 32, acc * BN + c * 32), v);
+          tmem_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              const int ch = hh * 4 + (j >> 3);
-              const uint32_t d = buf + lane * 128 + ((ch ^ (lane & 7)) << 4);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d),
-                           "r"(pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]))),
-                           "r"(pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]))),
-                           "r"(pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]))),
-                           "r"(pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7])))
-                           : "memory");
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tm_out.m[dst], buf, n_blk * BN + c0, y);
-            bulk_commit();
-          }
+          for (int j = 0; j < 16; ++j) pk[c * 16 + j] = pack_bf16x2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
         }
         tc_fence_before();
         __syncwarp();
+        if (lane == 0) release_acc(acc);
+        // packed registers -> swizzled staging box -> bulk store into the owner's receive slot.
+        // The four boxes are paced over most of a tile time: 148 SMs finishing tiles together would
+        // otherwise hit the link in one burst and stall behind it.
+        const long long t_now = clock64();
+        const long long tile_cycles = static_cast<long long>(kb_total) * 900;   // estimate of one tile's MMA time
+        t_prev_tile = t_now;
+        const long long pace = (p.dbg & 128) ? 0 : (tile_cycles * ((p.dbg >> 8) & 15)) / 32;
+        const int y = (m_blk - dst * p.blocks_per_shard) * BM + lg * 32;
+#pragma unroll
+        for (int bx = 0; bx < BN / 64; ++bx, ++box_it) {
+          const uint32_t buf = stg + (box_it & 1u) * 4096;
+          if (lane == 0) {
+            bulk_wait_read1();          // the store that last used this buffer has read it
+            if (pace > 0) {
+              const long long due = t_now + (bx * 4 + lg) * (pace / 4);   // warps interleave as well
+              while (clock64() < due && !*abort_flag) { __nanosleep(200); }
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint32_t d = buf + lane * 128 + ((ch ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d), "r"(pk[bx * 32 + ch * 4]),
+                         "r"(pk[bx * 32 + ch * 4 + 1]), "r"(pk[bx * 32 + ch * 4 + 2]), "r"(pk[bx * 32 + ch * 4 + 3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (!(p.dbg & 1) && !((p.dbg & 64) && p.rank != 0) && !((p.dbg & 2048) && (bx & 1)) && !((p.dbg & 4096) && (bx != 0)) && n_blk * BN + bx * 64 < p.n) {
+            __nv_bfloat16* box = p.recv[(p.dbg & 16) ? p.rank : dst] + static_cast<long long>(p.rank) * p.shard_rows * p.n +
+                                 (static_cast<long long>(y >> 5) * (p.n >> 6) + (n_blk * (BN / 64) + bx)) * 2048;
+            if (p.dbg & 8) {
+              // experiment: coalesced st.global of the staged box (512 contiguous bytes per warp store)
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                uint4 w;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                             : "r"(buf + k * 512 + lane * 16));
+                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(box) + k * 512 + lane * 16) = w;
+              }
+            } else if (lane == 0) {
+              bulk_store_4k(box, buf);
+              bulk_commit();
+            }
+          }
+        }
         if (lane == 0) {
-          mbar_arrive(smem_u32(&bars->acc_empty[acc]));
           // Publish the PREVIOUS remote tile of this warp: its 4 store groups are older than the 4
           // just committed, so "at most 4 groups pending" means they have completed.  The owner
           // counts 4 arrivals (warps) per tile.
@@ -293,19 +474,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           const int blk = m_blk - dst * p.blocks_per_shard;
           pending_flag = p.flags[dst] + p.rank * p.blocks_per_shard + blk;
         }
+        if ((p.dbg & 8) && !(p.dbg & 32)) __threadfence_system();   // experiment path: every lane's own stores
         __syncwarp();
-      } else {
-        __nv_bfloat16* orow;
-        const __nv_bfloat16* rrow = nullptr;
-        long long slot = 0;
-        if (p.tp <= 1) {
-          orow = p.c + static_cast<long long>(row) * p.ldc + n_blk * BN;
-        } else {
-          const int rl = row - dst * p.shard_rows;
-          orow = p.out + static_cast<long long>(rl) * p.ldo + n_blk * BN;
-          rrow = p.recv[p.rank] + static_cast<long long>(rl) * p.n + n_blk * BN;
-          slot = static_cast<long long>(p.shard_rows) * p.n;
+      } else if (p.tp > 1) {
+        const int rl = row - dst * p.shard_rows;
+        __nv_bfloat16* orow = p.out + static_cast<long long>(rl) * p.ldo + n_blk * BN;
+        const long long slot = static_cast<long long>(p.shard_rows) * p.n;
+        const uint32_t full_bar = smem_u32(&bars->acc_full[acc]);
+        const uint32_t par = (local >> 1) & 1u;
+        const uint32_t tacc = tmem_addr(tmem, lg * 32, acc * BN);
+        const bool skip = (p.dbg & 2) != 0;
+        switch (p.tp) {
+          case 2: own_tile_epilogue<1>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
+          case 4: own_tile_epilogue<3>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
+          case 8: own_tile_epilogue<7>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
+          default: own_tile_epilogue<0>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
         }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) release_acc(acc);
+      } else {
+        mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
+        tc_fence_after();
+        __nv_bfloat16* orow = p.c + static_cast<long long>(row) * p.ldc + n_blk * BN;
         const bool row_ok = row < p.m;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -317,28 +508,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             for (int j = 0; j < 32; j += 8) {
               const int col = n_blk * BN + c0 + j;
               if (col < p.n) {   // n is a multiple of 8
-                float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[j + e]);
-                if (rrow != nullptr) {
-                  // fixed-order cross-rank sum: own fp32 accumulator, then sources 0..tp-1
-                  for (int src = 0; src < p.tp; ++src) {
-                    if (src == p.rank) continue;
-                    const uint4 w = *reinterpret_cast<const uint4*>(rrow + src * slot + c0 + j);
-                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                      const float2 ff = __bfloat1622float2(h2[e]);
-                      f[2 * e] += ff.x;
-                      f[2 * e + 1] += ff.y;
-                    }
-                  }
-                }
                 uint4 o;
-                o.x = pack_bf16x2(f[0], f[1]);
-                o.y = pack_bf16x2(f[2], f[3]);
-                o.z = pack_bf16x2(f[4], f[5]);
-                o.w = pack_bf16x2(f[6], f[7]);
+                o.x = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                o.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                o.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                o.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
                 *reinterpret_cast<uint4*>(orow + c0 + j) = o;
               }
             }
@@ -346,7 +520,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[acc]));
+        if (lane == 0) release_acc(acc);
       }
     }
     if (lane == 0) {
@@ -361,16 +535,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
+  if constexpr (NCTA == 2) cluster_sync_all();   // no CTA leaves while its peer may still signal or read it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem, 512);
+    if constexpr (NCTA == 1) tmem_dealloc(tmem, 512);
+    else tmem_dealloc_pair(tmem, 512);
   }
   if (tid == 0 && p.status != nullptr && bars->abort_flag) atomicCAS(p.status, 0, FTB_ERR_TIMEOUT);
   if (tid == 0 && p.tp > 1) {
     // The last CTA to finish tells every peer that this rank's receive slots may be overwritten.
     __threadfence();
     const unsigned int prev = atomicAdd(p.counter, 1u);
-    if (prev == gridDim.x - 1) {
+    if (prev == gridDim.x - 1) {   // every CTA of the launch has arrived
       *p.counter = 0;
       for (int peer = 0; peer < p.tp; ++peer)
         st_release_sys(p.flags[peer] + p.tp * p.blocks_per_shard + p.rank, p.epoch);
@@ -385,7 +561,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 using namespace ftb;
 
 static int launch_gemm(const void* a, const void* b, int m, int n, int k, long long lda, long long ldb,
-                       gemm::Params& p, const gemm::OutMaps& maps, cudaStream_t st) {
+                       gemm::Params& p, cudaStream_t st) {
   if (m <= 0 || n <= 0 || k <= 0) { set_last_error("gemm: bad sizes m=%d n=%d k=%d", m, n, k); return FTB_ERR_INVALID; }
   if ((n % 8) || (k % 8) || (lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(a) & 15) ||
       (reinterpret_cast<uintptr_t>(b) & 15)) {
@@ -401,14 +577,42 @@ static int launch_gemm(const void* a, const void* b, int m, int n, int k, long l
   p.m = m; p.n = n; p.k = k;
   p.m_blocks = (m + gemm::BM - 1) / gemm::BM;
   p.n_blocks = (n + gemm::BN - 1) / gemm::BN;
-  p.n_tiles = p.m_blocks * p.n_blocks;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // CTA pairs when there are at least two row blocks per owner (and the caller did not opt out).
+  static const int force = getenv("FTB_GEMM_NCTA") ? atoi(getenv("FTB_GEMM_NCTA")) : 0;
+  int ncta = (p.tp > 1 ? (p.blocks_per_shard % 2 == 0) : (p.m_blocks >= 2)) ? 2 : 1;
+  if (force == 1 || force == 2) ncta = (force == 2 && p.tp > 1 && (p.blocks_per_shard % 2)) ? 1 : force;
+  cudaError_t e;
+  if (ncta == 2) {
+    p.n_tiles = ((p.m_blocks + 1) / 2) * p.n_blocks;
+    e = cudaFuncSetAttribute(gemm::gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::Cfg<2>::SMEM_BYTES);
+    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm pair)");
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.blockDim = dim3(gemm::THREADS);
+    cfg.dynamicSmemBytes = gemm::Cfg<2>::SMEM_BYTES;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(2);
+    int max_clusters = 0;
+    e = cudaOccupancyMaxActiveClusters(&max_clusters, gemm::gemm_bf16_kernel<2>, &cfg);
+    if (e != cudaSuccess || max_clusters <= 0) { cudaGetLastError(); max_clusters = sms / 2; }
+    const int groups = p.n_tiles < max_clusters ? p.n_tiles : max_clusters;
+    cfg.gridDim = dim3(2 * groups);
+    e = cudaLaunchKernelEx(&cfg, gemm::gemm_bf16_kernel<2>, tm_a, tm_b, p);
+    return check_cuda(e, "gemm pair launch");
+  }
+  p.n_tiles = p.m_blocks * p.n_blocks;
   const int grid = p.n_tiles < sms ? p.n_tiles : sms;
-  cudaError_t e = cudaFuncSetAttribute(gemm::gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES);
+  e = cudaFuncSetAttribute(gemm::gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::Cfg<1>::SMEM_BYTES);
   if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm)");
-  gemm::gemm_bf16_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, st>>>(tm_a, tm_b, maps, p);
+  gemm::gemm_bf16_kernel<1><<<grid, gemm::THREADS, gemm::Cfg<1>::SMEM_BYTES, st>>>(tm_a, tm_b, p);
   return check_cuda(cudaGetLastError(), "gemm launch");
 }
 
@@ -424,8 +628,7 @@ extern "C" FTB_API int ftb_gemm_bf16(const ftb_gemm_args* g, void* stream) {
   p.ldc = g->ldc;
   p.tp = 1;
   p.status = g->status;
-  static gemm::OutMaps no_maps;   // unused when tp == 1
-  return launch_gemm(g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, p, no_maps, reinterpret_cast<cudaStream_t>(stream));
+  return launch_gemm(g->a, g->b, g->m, g->n, g->k, g->lda, g->ldb, p, reinterpret_cast<cudaStream_t>(stream));
 }
 
 struct ftb_gemm_rs_ctx {
@@ -434,12 +637,11 @@ struct ftb_gemm_rs_ctx {
   unsigned int* flags[gemm::MAX_TP];
   unsigned int* d_counter;
   unsigned int epoch;
-  gemm::OutMaps maps;            // TMA store maps: receive slot of this rank on every peer
 };
 
 extern "C" FTB_API int ftb_gemm_rs_workspace_bytes(int m, int n, int tp, int64_t* recv_bytes, int64_t* flag_bytes) {
-  if (m <= 0 || n <= 0 || tp <= 0 || tp > gemm::MAX_TP || (m % (tp * gemm::BM)) || (n % 8) || !recv_bytes || !flag_bytes) {
-    set_last_error("ftb_gemm_rs_workspace_bytes: need 1 <= tp <= 8, m a multiple of tp*128, n a multiple of 8");
+  if (m <= 0 || n <= 0 || tp <= 0 || tp > gemm::MAX_TP || (m % (tp * gemm::BM)) || (n % 64) || !recv_bytes || !flag_bytes) {
+    set_last_error("ftb_gemm_rs_workspace_bytes: need 1 <= tp <= 8, m a multiple of tp*128, n a multiple of 64");
     return FTB_ERR_INVALID;
   }
   *recv_bytes = static_cast<int64_t>(m) * n * 2;                       // tp slots of [m/tp, n] bf16
@@ -464,15 +666,6 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
     if (!recv_ptrs[i] || !flag_ptrs[i]) { delete c; set_last_error("ftb_gemm_rs_ctx_create: null peer pointer"); return FTB_ERR_INVALID; }
     c->recv[i] = recv_ptrs[i];
     c->flags[i] = reinterpret_cast<unsigned int*>(flag_ptrs[i]);
-  }
-  memset(&c->maps, 0, sizeof(c->maps));
-  for (int i = 0; i < tp; ++i) {
-    const char* slot = reinterpret_cast<const char*>(c->recv[i]) + static_cast<size_t>(rank) * c->shard_rows * n * 2;
-    if (!make_tmap_2d(&c->maps.m[i], slot, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, c->shard_rows, n, n, 32, 64)) {
-      delete c;
-      set_last_error("ftb_gemm_rs_ctx_create: cuTensorMapEncodeTiled failed for the receive slot of rank %d", i);
-      return FTB_ERR_CUDA;
-    }
   }
   cudaError_t e = cudaMalloc(&c->d_counter, sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMemset(c->d_counter, 0, sizeof(unsigned int));
@@ -508,7 +701,8 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
   p.ldo = ldo;
   p.counter = c->d_counter;
   p.status = status;
-  return launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, c->maps, st);
+  if (const char* d = getenv("FTB_GEMM_RS_DEBUG")) p.dbg = atoi(d);
+  return launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
 }
 
 // ---- CUDA IPC helpers for callers that do not have a symmetric-memory allocator of their own.
