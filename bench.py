@@ -155,7 +155,7 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
            "flops_per_gpu": flops, "gemm_only_ms": t_gemm, "gemm_only_tflops_per_gpu": flops / t_gemm / 1e9,
            "l2": "256 MB flush write between timed iterations", "iters": iters, "timing": "median per rank, max over ranks"}
     if world > 1:
-        ctx = GemmRsContext(m, n, None, dev)
+        ctx = GemmRsContext(m, n, None, dev, "auto", os.environ.get("FTB_RS_PROTOCOL", "auto"))
         out = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)
         t_fused = timed(lambda: ctx(case.a, case.b, out))
         ctx.check()
@@ -171,7 +171,7 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
                     "frac_of_peak": flops / t_fused / 1e9 / peaks["bf16_tflops"],
                     "exposed_comm": t_fused / t_gemm - 1.0, "gemm_plus_nccl_rs_ms": t_nccl,
                     "pushed_bytes_per_gpu": pushed, "nvlink_floor_ms": pushed / 770e9 * 1e3,
-                    "symm_provider": ctx.recv.provider})
+                    "symm_provider": ctx.recv.provider, "protocol": ctx.protocol})
         ctx.close()
     else:
         res.update({"tflops_per_gpu": flops / t_gemm / 1e9, "frac_of_peak": flops / t_gemm / 1e9 / peaks["bf16_tflops"]})

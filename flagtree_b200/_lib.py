@@ -72,6 +72,7 @@ def load() -> C.CDLL:
             lib.ftb_gemm_rs_ctx_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int,
                                                    C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
             lib.ftb_gemm_rs_ctx_destroy.argtypes = [C.c_void_p]
+            lib.ftb_gemm_rs_ctx_set_multicast.argtypes = [C.c_void_p, C.c_void_p]
             lib.ftb_gemm_rs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
                                         C.c_int64, C.c_void_p, C.c_void_p]
             lib.ftb_ipc_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_uint8)]

@@ -5,6 +5,13 @@
 // counter is released; tiles of this rank's own rows are computed last and their epilogue adds the
 // partials the other ranks have pushed (fixed order, fp32) before writing the bf16 shard.
 //
+// Reduce-scatter by pull (used when the workspace has an NVSwitch multicast mapping): every rank writes
+// its bf16 partial tiles into its OWN symmetric buffer, row blocks are visited in the same order on every
+// rank, and when a row block is complete on a rank it raises one flag on the block's owner.  Four extra
+// "reducer" warps per CTA wait for a row block's flags from all ranks and fetch the cross-rank sum with
+// multimem.ld_reduce (in-switch reduction, fp32 accumulation): the owner's link carries 1/tp of the
+// bytes and no SM ever pushes bulk data, so the MMA pipeline is not disturbed.
+//
 // Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM), warps 2-5 = epilogue.
 // Tile 128 x 256, K step 64, 4 shared-memory stages of 48 KB, two 256-column TMEM accumulators so the
 // epilogue of tile i overlaps the MMAs of tile i+1.
@@ -39,6 +46,7 @@ template <int NCTA> struct Cfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 constexpr int THREADS = 192;
+constexpr int THREADS_PULL = 320;      // + 4 reducer warps
 constexpr int MAX_TP = 8;
 
 struct Params {
@@ -57,8 +65,9 @@ struct Params {
   long long ldo;
   unsigned int* counter;             // CTA completion counter (device, zero between calls)
   int* status;
-  int dbg;                           // timing experiments only (env FTB_GEMM_RS_DEBUG): 1 no remote stores,
-                                     // 2 no reads of received partials, 4 no flag waits; results are wrong
+  // pull mode
+  const __nv_bfloat16* mc_part;      // multicast address of the ranks' partial buffers [m, n] (NULL = push mode)
+  unsigned int* blk_counter;         // per 128-row block: epilogue-warp arrivals, monotonic over calls
 };
 
 
@@ -73,8 +82,20 @@ struct Bars {
 
 // Tile t of a CTA group (NCTA CTAs, each owning one 128-row block of the group tile) -> the 128-row
 // block of CTA `cta`, the 256-column block, and the rank that owns those rows.
-template <int NCTA>
+template <int NCTA, bool PULL = false>
 __device__ __forceinline__ void tile_coords(const Params& p, int t, int cta, int& m_blk, int& n_blk, int& dst) {
+  if constexpr (PULL) {
+    // row-block group j of every shard (shards staggered by rank), then group j+1 ...: row block j of
+    // every owner is complete on all ranks after phase j, so owners can fetch while phase j+1 runs.
+    const int per_phase = p.tp * p.n_blocks;
+    const int jg = t / per_phase;
+    const int r = t - jg * per_phase;
+    const int so = r / p.n_blocks;
+    n_blk = r - so * p.n_blocks;
+    dst = (so + p.rank) % p.tp;
+    m_blk = dst * p.blocks_per_shard + jg * NCTA + cta;
+    return;
+  }
   if (p.tp <= 1) {
     const int mg = t / p.n_blocks;
     n_blk = t - mg * p.n_blocks;
@@ -212,8 +233,16 @@ __device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long 
   }
 }
 
-template <int NCTA>
-__global__ void __launch_bounds__(THREADS, 1)
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr));
+  return v;
+}
+
+template <int NCTA, bool PULL>
+__global__ void __launch_bounds__(PULL ? THREADS_PULL : THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
   using C = Cfg<NCTA>;
   constexpr int STAGES = C::STAGES;
@@ -273,7 +302,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       uint32_t it = 0;
       for (int t = group; t < p.n_tiles; t += n_groups) {
         int m_blk, n_blk, dst;
-        tile_coords<NCTA>(p, t, cta, m_blk, n_blk, dst);
+        tile_coords<NCTA, PULL>(p, t, cta, m_blk, n_blk, dst);
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -337,13 +366,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2-5)
     const int lg = warp & 3;                         // TMEM lane group this warp may read
     const uint32_t stg = staging + lg * 8192;        // this warp's two 4 KB staging boxes
     uint32_t local = 0, box_it = 0;
     unsigned int* pending_flag = nullptr;            // lane 0: counter of the last remote tile, not yet released
-    long long t_prev_tile = 0;                       // when this warp started draining its previous remote tile
     // the accumulator-free barrier the MMA issuer waits on lives in the even CTA
     const uint32_t acc_empty_addr[2] = {
         NCTA == 1 ? smem_u32(&bars->acc_empty[0]) : mapa_shared(smem_u32(&bars->acc_empty[0]), 0),
@@ -354,11 +382,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     };
     for (int t = group; t < p.n_tiles; t += n_groups, ++local) {
       int m_blk, n_blk, dst;
-      tile_coords<NCTA>(p, t, cta, m_blk, n_blk, dst);
+      tile_coords<NCTA, PULL>(p, t, cta, m_blk, n_blk, dst);
       const uint32_t acc = local & 1u;
       const int row = m_blk * BM + lg * 32 + lane;
-      const bool remote = p.tp > 1 && dst != p.rank;
-      if (remote) {
+      const bool remote = !PULL && p.tp > 1 && dst != p.rank;
+      if constexpr (PULL) {
+        // Before overwriting a row block of the partial buffer make sure its owner has fetched the
+        // previous call's sum (the owner's done[] word in this rank's flag buffer).
+        if (lane == 0) {
+          const unsigned int* done = p.flags[p.rank] + p.tp * p.blocks_per_shard + dst;
+          if (ld_acquire_sys(done) + 1u < p.epoch && !*abort_flag) {
+            const long long t0 = clock64();
+            while (ld_acquire_sys(done) + 1u < p.epoch) {
+              if (*abort_flag) break;
+              if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; break; }
+            }
+          }
+        }
+        __syncwarp();
+      } else if (remote) {
         // Before the first store into dst's receive slot make sure dst has consumed the previous
         // call's data (its done[] word, written by dst into this rank's flag buffer).
         if (lane == 0) {
@@ -372,9 +414,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
         __syncwarp();
-      } else if (p.tp > 1) {
+      } else if (!PULL && p.tp > 1) {
         // Own rows: every other rank's partial tile must have landed in this rank's receive slots.
-        if (lane == 0 && !(p.dbg & 4)) {
+        if (lane == 0) {
           // Never enter this wait while holding back a release of our own (peers wait for it too).
           if (pending_flag != nullptr) {
             bulk_wait_all();
@@ -398,7 +440,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         __syncwarp();
       }
-      if (remote) {
+      if constexpr (PULL) {
+        // partial tile -> this rank's own symmetric buffer (row-major [m, n] bf16), then count the row block
+        mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
+        tc_fence_after();
+        __nv_bfloat16* orow = p.recv[p.rank] + static_cast<long long>(row) * p.n + n_blk * BN;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld32(tmem_addr(tmem, lg * 32, acc * BN + c0), v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            if (n_blk * BN + c0 + j < p.n) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+              *reinterpret_cast<uint4*>(orow + c0 + j) = o;
+            }
+          }
+        }
+        tc_fence_before();
+        __threadfence_system();        // this lane's stores are visible to peers before the count below
+        __syncwarp();
+        if (lane == 0) {
+          release_acc(acc);
+          const unsigned int cnt = atomicAdd(p.blk_counter + m_blk, 1u) + 1u;
+          if (cnt == p.flag_target) {
+            // last warp of the row block on this rank: tell the owner (one 4-byte remote store)
+            __threadfence_system();
+            const int blk = m_blk - dst * p.blocks_per_shard;
+            st_release_sys(p.flags[dst] + p.rank * p.blocks_per_shard + blk, p.epoch);
+          }
+        }
+        __syncwarp();
+      } else if (remote) {
         mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
         tc_fence_after();
         // Drain the accumulator into registers as packed bf16 and hand the TMEM buffer back at once,
@@ -416,23 +494,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();
         if (lane == 0) release_acc(acc);
         // packed registers -> swizzled staging box -> bulk store into the owner's receive slot.
-        // The four boxes are paced over most of a tile time: 148 SMs finishing tiles together would
-        // otherwise hit the link in one burst and stall behind it.
-        const long long t_now = clock64();
-        const long long tile_cycles = static_cast<long long>(kb_total) * 900;   // estimate of one tile's MMA time
-        t_prev_tile = t_now;
-        const long long pace = (p.dbg & 128) ? 0 : (tile_cycles * ((p.dbg >> 8) & 15)) / 32;
         const int y = (m_blk - dst * p.blocks_per_shard) * BM + lg * 32;
 #pragma unroll
         for (int bx = 0; bx < BN / 64; ++bx, ++box_it) {
           const uint32_t buf = stg + (box_it & 1u) * 4096;
-          if (lane == 0) {
-            bulk_wait_read1();          // the store that last used this buffer has read it
-            if (pace > 0) {
-              const long long due = t_now + (bx * 4 + lg) * (pace / 4);   // warps interleave as well
-              while (clock64() < due && !*abort_flag) { __nanosleep(200); }
-            }
-          }
+          if (lane == 0) bulk_wait_read1();          // the store that last used this buffer has read it
           __syncwarp();
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
@@ -443,22 +509,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (!(p.dbg & 1) && !((p.dbg & 64) && p.rank != 0) && !((p.dbg & 2048) && (bx & 1)) && !((p.dbg & 4096) && (bx != 0)) && n_blk * BN + bx * 64 < p.n) {
-            __nv_bfloat16* box = p.recv[(p.dbg & 16) ? p.rank : dst] + static_cast<long long>(p.rank) * p.shard_rows * p.n +
+          if (lane == 0 && n_blk * BN + bx * 64 < p.n) {
+            __nv_bfloat16* box = p.recv[dst] + static_cast<long long>(p.rank) * p.shard_rows * p.n +
                                  (static_cast<long long>(y >> 5) * (p.n >> 6) + (n_blk * (BN / 64) + bx)) * 2048;
-            if (p.dbg & 8) {
-              // experiment: coalesced st.global of the staged box (512 contiguous bytes per warp store)
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                uint4 w;
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
-                             : "r"(buf + k * 512 + lane * 16));
-                *reinterpret_cast<uint4*>(reinterpret_cast<char*>(box) + k * 512 + lane * 16) = w;
-              }
-            } else if (lane == 0) {
-              bulk_store_4k(box, buf);
-              bulk_commit();
-            }
+            bulk_store_4k(box, buf);
+            bulk_commit();
           }
         }
         if (lane == 0) {
@@ -474,16 +529,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           const int blk = m_blk - dst * p.blocks_per_shard;
           pending_flag = p.flags[dst] + p.rank * p.blocks_per_shard + blk;
         }
-        if ((p.dbg & 8) && !(p.dbg & 32)) __threadfence_system();   // experiment path: every lane's own stores
         __syncwarp();
-      } else if (p.tp > 1) {
+      } else if (!PULL && p.tp > 1) {
         const int rl = row - dst * p.shard_rows;
         __nv_bfloat16* orow = p.out + static_cast<long long>(rl) * p.ldo + n_blk * BN;
         const long long slot = static_cast<long long>(p.shard_rows) * p.n;
         const uint32_t full_bar = smem_u32(&bars->acc_full[acc]);
         const uint32_t par = (local >> 1) & 1u;
         const uint32_t tacc = tmem_addr(tmem, lg * 32, acc * BN);
-        const bool skip = (p.dbg & 2) != 0;
+        const bool skip = false;
         switch (p.tp) {
           case 2: own_tile_epilogue<1>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
           case 4: own_tile_epilogue<3>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
@@ -493,7 +547,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         tc_fence_before();
         __syncwarp();
         if (lane == 0) release_acc(acc);
-      } else {
+      } else if (!PULL) {
         mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
         tc_fence_after();
         __nv_bfloat16* orow = p.c + static_cast<long long>(row) * p.ldc + n_blk * BN;
@@ -531,6 +585,52 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         red_release_sys_add(pending_flag, 1u);
       }
     }
+  } else {
+    // ------------------------------------------------------------------ reducers (warps 6-9, pull mode)
+    if constexpr (PULL) {
+      const int rt = tid - 192;                      // 0..127
+      const int vec_per_row = p.n >> 3;
+      const int vec_per_blk = BM * vec_per_row;
+      for (int j = 0; j < p.blocks_per_shard; ++j) {
+        if (lane == 0) {
+          for (int src = 0; src < p.tp; ++src) {
+            const unsigned int* f = p.flags[p.rank] + src * p.blocks_per_shard + j;
+            if (ld_acquire_sys(f) < p.epoch && !*abort_flag) {
+              const long long t0 = clock64();
+              while (ld_acquire_sys(f) < p.epoch) {
+                if (*abort_flag) break;
+                if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; break; }
+                __nanosleep(100);
+              }
+            }
+          }
+        }
+        __syncwarp();
+        if (*abort_flag) break;
+        const long long row0 = static_cast<long long>(p.rank) * p.shard_rows + j * BM;
+        const __nv_bfloat16* src_blk = p.mc_part + row0 * p.n;
+        __nv_bfloat16* out_blk = p.out + static_cast<long long>(j) * BM * p.ldo;
+        // 16 fetches in flight per thread: the sums come back over NVLink with microseconds of latency
+        const int stride = gridDim.x * 128;
+        for (int i0 = blockIdx.x * 128 + rt; i0 < vec_per_blk; i0 += 16 * stride) {
+          uint4 v[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int i = i0 + u * stride;
+            if (i < vec_per_blk) v[u] = multimem_ld_reduce_bf16x8(src_blk + static_cast<long long>(i) * 8);
+          }
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+            const int i = i0 + u * stride;
+            if (i < vec_per_blk) {
+              const int r = i / vec_per_row;
+              const int c = (i - r * vec_per_row) * 8;
+              *reinterpret_cast<uint4*>(out_blk + static_cast<long long>(r) * p.ldo + c) = v[u];
+            }
+          }
+        }
+      }
+    }
   }
 
   tc_fence_before();
@@ -560,6 +660,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 // ------------------------------------------------------------------------------------- host side
 using namespace ftb;
 
+template <int NCTA, bool PULL>
+static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const gemm::Params& p, int sms, cudaStream_t st) {
+  auto kern = gemm::gemm_bf16_kernel<NCTA, PULL>;
+  constexpr int smem = gemm::Cfg<NCTA>::SMEM_BYTES;
+  constexpr int threads = PULL ? gemm::THREADS_PULL : gemm::THREADS;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm)");
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = NCTA; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int max_groups = sms / NCTA;
+  if (NCTA == 2) {
+    cfg.gridDim = dim3(2);
+    int mc = 0;
+    e = cudaOccupancyMaxActiveClusters(&mc, kern, &cfg);
+    if (e == cudaSuccess && mc > 0) max_groups = mc; else cudaGetLastError();
+  }
+  // pull mode: every CTA must be resident at once (reducer warps wait on other CTAs' tiles): the
+  // grid never exceeds one CTA per SM, which this kernel's shared-memory footprint already enforces.
+  const int groups = p.n_tiles < max_groups ? p.n_tiles : max_groups;
+  cfg.gridDim = dim3(NCTA * groups);
+  e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, p);
+  return check_cuda(e, "gemm launch");
+}
+
 static int launch_gemm(const void* a, const void* b, int m, int n, int k, long long lda, long long ldb,
                        gemm::Params& p, cudaStream_t st) {
   if (m <= 0 || n <= 0 || k <= 0) { set_last_error("gemm: bad sizes m=%d n=%d k=%d", m, n, k); return FTB_ERR_INVALID; }
@@ -584,36 +716,10 @@ static int launch_gemm(const void* a, const void* b, int m, int n, int k, long l
   static const int force = getenv("FTB_GEMM_NCTA") ? atoi(getenv("FTB_GEMM_NCTA")) : 0;
   int ncta = (p.tp > 1 ? (p.blocks_per_shard % 2 == 0) : (p.m_blocks >= 2)) ? 2 : 1;
   if (force == 1 || force == 2) ncta = (force == 2 && p.tp > 1 && (p.blocks_per_shard % 2)) ? 1 : force;
-  cudaError_t e;
-  if (ncta == 2) {
-    p.n_tiles = ((p.m_blocks + 1) / 2) * p.n_blocks;
-    e = cudaFuncSetAttribute(gemm::gemm_bf16_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::Cfg<2>::SMEM_BYTES);
-    if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm pair)");
-    cudaLaunchConfig_t cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.blockDim = dim3(gemm::THREADS);
-    cfg.dynamicSmemBytes = gemm::Cfg<2>::SMEM_BYTES;
-    cfg.stream = st;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cfg.gridDim = dim3(2);
-    int max_clusters = 0;
-    e = cudaOccupancyMaxActiveClusters(&max_clusters, gemm::gemm_bf16_kernel<2>, &cfg);
-    if (e != cudaSuccess || max_clusters <= 0) { cudaGetLastError(); max_clusters = sms / 2; }
-    const int groups = p.n_tiles < max_clusters ? p.n_tiles : max_clusters;
-    cfg.gridDim = dim3(2 * groups);
-    e = cudaLaunchKernelEx(&cfg, gemm::gemm_bf16_kernel<2>, tm_a, tm_b, p);
-    return check_cuda(e, "gemm pair launch");
-  }
-  p.n_tiles = p.m_blocks * p.n_blocks;
-  const int grid = p.n_tiles < sms ? p.n_tiles : sms;
-  e = cudaFuncSetAttribute(gemm::gemm_bf16_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::Cfg<1>::SMEM_BYTES);
-  if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm)");
-  gemm::gemm_bf16_kernel<1><<<grid, gemm::THREADS, gemm::Cfg<1>::SMEM_BYTES, st>>>(tm_a, tm_b, p);
-  return check_cuda(cudaGetLastError(), "gemm launch");
+  const bool pull = p.tp > 1 && p.mc_part != nullptr;
+  p.n_tiles = ((p.m_blocks + ncta - 1) / ncta) * p.n_blocks;
+  if (ncta == 2) return pull ? launch_variant<2, true>(tm_a, tm_b, p, sms, st) : launch_variant<2, false>(tm_a, tm_b, p, sms, st);
+  return pull ? launch_variant<1, true>(tm_a, tm_b, p, sms, st) : launch_variant<1, false>(tm_a, tm_b, p, sms, st);
 }
 
 extern "C" FTB_API int ftb_gemm_bf16(const ftb_gemm_args* g, void* stream) {
@@ -636,6 +742,8 @@ struct ftb_gemm_rs_ctx {
   void* recv[gemm::MAX_TP];
   unsigned int* flags[gemm::MAX_TP];
   unsigned int* d_counter;
+  unsigned int* d_blk_counter;   // pull mode: arrivals per 128-row block
+  void* mc_recv;                 // multicast address of the receive/partial buffers (NULL = push mode)
   unsigned int epoch;
 };
 
@@ -667,16 +775,29 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
     c->recv[i] = recv_ptrs[i];
     c->flags[i] = reinterpret_cast<unsigned int*>(flag_ptrs[i]);
   }
+  c->mc_recv = nullptr;
+  c->d_blk_counter = nullptr;
+  const int m_blocks = m / gemm::BM;
   cudaError_t e = cudaMalloc(&c->d_counter, sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMemset(c->d_counter, 0, sizeof(unsigned int));
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_blk_counter, sizeof(unsigned int) * m_blocks);
+  if (e == cudaSuccess) e = cudaMemset(c->d_blk_counter, 0, sizeof(unsigned int) * m_blocks);
   if (e != cudaSuccess) { delete c; return check_cuda(e, "ftb_gemm_rs_ctx_create"); }
   *out = c;
+  return FTB_OK;
+}
+
+extern "C" FTB_API int ftb_gemm_rs_ctx_set_multicast(ftb_gemm_rs_ctx* c, void* mc_recv_ptr) {
+  if (!c) { set_last_error("ftb_gemm_rs_ctx_set_multicast: null context"); return FTB_ERR_INVALID; }
+  if (c->epoch != 0) { set_last_error("ftb_gemm_rs_ctx_set_multicast: must be called before the first ftb_gemm_rs"); return FTB_ERR_INVALID; }
+  c->mc_recv = mc_recv_ptr;
   return FTB_OK;
 }
 
 extern "C" FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* c) {
   if (!c) return FTB_OK;
   cudaFree(c->d_counter);
+  cudaFree(c->d_blk_counter);
   delete c;
   return FTB_OK;
 }
@@ -701,7 +822,8 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
   p.ldo = ldo;
   p.counter = c->d_counter;
   p.status = status;
-  if (const char* d = getenv("FTB_GEMM_RS_DEBUG")) p.dbg = atoi(d);
+  p.mc_part = reinterpret_cast<const __nv_bfloat16*>(c->mc_recv);
+  p.blk_counter = c->d_blk_counter;
   return launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
 }
 

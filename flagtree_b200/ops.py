@@ -220,7 +220,8 @@ class GemmRsContext:
     Creation is collective over `group`.  One call may be in flight per context.
     """
 
-    def __init__(self, m: int, n: int, group=None, device: Optional[torch.device] = None, provider: str = "auto"):
+    def __init__(self, m: int, n: int, group=None, device: Optional[torch.device] = None, provider: str = "auto",
+                 protocol: str = "auto"):
         import torch.distributed as dist
         from .symm import SymmetricBuffer
         self.group = group
@@ -240,6 +241,15 @@ class GemmRsContext:
             _lib.check(lib.ftb_gemm_rs_ctx_create(C.byref(ctx), self.rank, self.tp, m, n, recv_ptrs, flag_ptrs),
                        "gemm_rs ctx_create")
         self._ctx = ctx
+        # Pull protocol (in-switch reduction) when every rank obtained a multicast mapping, else push.
+        import torch.distributed as dist
+        have_mc = torch.tensor([1 if (self.recv.mc_ptr and protocol in ("auto", "pull")) else 0], device=self.device)
+        dist.all_reduce(have_mc, op=dist.ReduceOp.MIN, group=group)
+        self.protocol = "pull" if int(have_mc.item()) == 1 else "push"
+        if protocol == "pull" and self.protocol != "pull":
+            raise RuntimeError("gemm_rs: protocol='pull' needs an NVSwitch multicast mapping on every rank")
+        if self.protocol == "pull":
+            _lib.check(lib.ftb_gemm_rs_ctx_set_multicast(ctx, C.c_void_p(self.recv.mc_ptr)), "gemm_rs set_multicast")
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -34,6 +34,7 @@ class SymmetricBuffer:
         self.world = dist.get_world_size(group)
         self.nbytes = int(nbytes)
         self.ptrs: List[int] = []
+        self.mc_ptr: int = 0            # NVSwitch multicast address of all ranks' buffers (0 = none)
         self._keep = None
         self._opened: List[int] = []
         self._owned: Optional[int] = None
@@ -71,6 +72,10 @@ class SymmetricBuffer:
         ptrs = list(hdl.buffer_ptrs)
         assert len(ptrs) == self.world and ptrs[self.rank] == t.data_ptr()
         self.ptrs = [int(p) for p in ptrs]
+        try:
+            self.mc_ptr = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        except Exception:               # noqa: BLE001 - multicast is optional
+            self.mc_ptr = 0
         self._keep = (t, hdl)
 
     def _init_ipc(self):

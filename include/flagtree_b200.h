@@ -123,6 +123,11 @@ typedef struct ftb_gemm_rs_ctx ftb_gemm_rs_ctx;
 FTB_API int ftb_gemm_rs_workspace_bytes(int m, int n, int tp, int64_t* recv_bytes, int64_t* flag_bytes);
 FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** ctx, int rank, int tp, int m, int n,
                                    void* const* recv_ptrs, void* const* flag_ptrs);
+/* Optional: `mc_recv_ptr` is an NVSwitch multicast mapping of all ranks' receive buffers (same size and
+ * layout on every rank).  When set (before the first call, on every rank) the reduce-scatter is done
+ * by pull: partial tiles stay in the producing rank's buffer and each owner fetches the cross-rank sum
+ * with in-switch reduction (multimem.ld_reduce, fp32 accumulate).  NULL keeps the push protocol. */
+FTB_API int ftb_gemm_rs_ctx_set_multicast(ftb_gemm_rs_ctx* ctx, void* mc_recv_ptr);
 FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* ctx);
 /* a [m, k_local] bf16, b [k_local, n] bf16, out [m/tp, n] bf16 (this rank's shard). */
 FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* ctx, const void* a, const void* b, void* out, int k_local,

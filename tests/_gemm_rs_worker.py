@@ -21,11 +21,12 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     provider = os.environ.get("FTB_SYMM_PROVIDER", "auto")
+    protocol = os.environ.get("FTB_RS_PROTOCOL", "auto")
     ok = True
     for (m, n, k_total) in [(world * 128, 256, world * 64), (world * 256, 1024, world * 320), (world * 1024, 7168, world * 2304 // 4)]:
         cases = [W.gemm_cfg4(tp=world, rank=r, m=m, n=n, k_total=k_total) for r in range(world)]
         ref = gemm_rs_ref([c.a for c in cases], [c.b for c in cases])[rank]
-        ctx = GemmRsContext(m, n, None, dev, provider)
+        ctx = GemmRsContext(m, n, None, dev, provider, protocol)
         a, b = cases[rank].a.to(dev), cases[rank].b.to(dev)
         outs = []
         for it in range(3):                      # repeated calls reuse the slots (epoch handling)
@@ -39,10 +40,11 @@ def main():
         scale = ref.abs().max().item()
         err_nccl = (outs[0].float() - nccl_out).abs().max().item()
         same = all(torch.equal(outs[0], o) for o in outs[1:])
-        print(f"[rank {rank}] m={m} n={n} k={k_total} provider={ctx.recv.provider}: err {err:.3e} scale {scale:.3e} "
+        print(f"[rank {rank}] m={m} n={n} k={k_total} provider={ctx.recv.provider} protocol={ctx.protocol}: err {err:.3e} scale {scale:.3e} "
               f"vs-nccl {err_nccl:.3e} repeat-identical {same}", flush=True)
-        # partials are rounded to bf16 before the cross-rank sum: world roundings of 2^-9 each
-        tol = (world + 1) * 2 ** -9 * scale
+        # every partial is rounded to bf16 (2^-9 relative to a partial that may be as large as the sum)
+        # and the fp32 sum is rounded once more
+        tol = (world + 1) * 2 ** -8 * scale
         ok = ok and err <= tol and err_nccl <= tol and same
         ctx.close()
         dist.barrier()

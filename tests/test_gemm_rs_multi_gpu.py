@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(world, provider):
-    env = dict(os.environ, FTB_SYMM_PROVIDER=provider, NCCL_NVLS_ENABLE="0")
+def _run(world, provider, protocol):
+    env = dict(os.environ, FTB_SYMM_PROVIDER=provider, FTB_RS_PROTOCOL=protocol, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", "29517", os.path.join(ROOT, "tests", "_gemm_rs_worker.py")]
     r = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600)
@@ -20,6 +20,7 @@ def _run(world, provider):
 
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
-@pytest.mark.parametrize("provider", ["auto", "cuda_ipc"])
-def test_gemm_rs_matches_oracle(provider):
-    _run(min(torch.cuda.device_count(), 8), provider)
+@pytest.mark.parametrize("provider,protocol", [("auto", "auto"), ("auto", "push"), ("cuda_ipc", "push")])
+def test_gemm_rs_matches_oracle(provider, protocol):
+    """auto/auto uses the pull protocol (in-switch reduction) when the box offers NVSwitch multicast."""
+    _run(min(torch.cuda.device_count(), 8), provider, protocol)
