@@ -383,6 +383,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
 namespace ftb {
 void set_last_error(const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
+int launch_sparse_mla_pair(const ftb_sparse_mla_args* a, cudaStream_t st);
 }  // namespace ftb
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -418,6 +419,12 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     set_last_error("ftb_sparse_mla_fwd: kv row stride must be a multiple of 8 elements");
     return FTB_ERR_INVALID;
   }
+  if (a->algo_id < 0 || a->algo_id > 2) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
+  if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
+  // algo 0 = default: CTA-pair kernel for bf16 KV; algo 1 = one CTA per (token, output half), which is
+  // also the kernel of the FP8 paged form and of the debug score tap; algo 2 = CTA-pair kernel.
+  if ((a->algo_id == 0 || a->algo_id == 2) && !a->kv_is_fp8 && a->dbg_scores == nullptr)
+    return launch_sparse_mla_pair(a, reinterpret_cast<cudaStream_t>(stream));
   MlaParams p;
   memset(&p, 0, sizeof(p));
   p.q = reinterpret_cast<const __nv_bfloat16*>(a->q);

@@ -40,7 +40,7 @@ def _check_status(status: Optional[torch.Tensor], what: str):
 def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
                    sm_scale: Optional[float] = None, d_v: int = D_V, *, lse_base2: bool = False,
                    out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-                   check: bool = False, _dbg_scores: Optional[torch.Tensor] = None
+                   check: bool = False, algo: int = 0, _dbg_scores: Optional[torch.Tensor] = None
                    ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Top-k sparse MLA forward.
 
@@ -86,7 +86,7 @@ def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
         a.idx_stride_token = indices.stride(0)
         a.out_stride_token, a.out_stride_head = os_.stride(0), os_.stride(1)
         a.lse_stride_token = ls.stride(0)
-        a.sm_scale, a.lse_base2, a.algo_id = float(sm_scale), int(lse_base2), 0
+        a.sm_scale, a.lse_base2, a.algo_id = float(sm_scale), int(lse_base2), int(algo)
         a.status = status.data_ptr() if status is not None else None
         a.kv_is_fp8 = 0
         a.dbg_scores = _dbg_scores.data_ptr() if _dbg_scores is not None else None

@@ -32,8 +32,8 @@ def _errors(out, lse, ref_out, ref_lse):
     return e_out, e_lse
 
 
-def _check(q, kv, idx, sm_scale, name=""):
-    out, lse = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), sm_scale, check=True)
+def _check(q, kv, idx, sm_scale, name="", algo=0):
+    out, lse = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), sm_scale, check=True, algo=algo)
     torch.cuda.synchronize()
     ref_out, ref_lse = sparse_mla_fwd_ref(q, kv, idx, sm_scale)
     e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
@@ -63,36 +63,40 @@ def test_scores_tap_matches_qk():
 GOLDEN = sorted(glob.glob(os.path.join(GOLDEN_DIR, "mla_topk_*.npz")))
 
 
+@pytest.mark.parametrize("algo", [1, 2], ids=["single_cta", "cta_pair"])
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
-def test_golden_vectors_from_reference_kernel(path):
+def test_golden_vectors_from_reference_kernel(path, algo):
     d = np.load(path)
     q = torch.from_numpy(d["q"]).to(torch.bfloat16)       # exact: fixtures hold bf16-representable values
     kv = torch.from_numpy(d["kv"]).to(torch.bfloat16)
     assert torch.equal(q.float(), torch.from_numpy(d["q"]).float())
     idx = torch.from_numpy(d["indices"])
-    out, lse = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), float(d["sm_scale"]), check=True)
+    out, lse = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), float(d["sm_scale"]), check=True, algo=algo)
     e_out, e_lse = _errors(out, lse, torch.from_numpy(d["out"]).float(), torch.from_numpy(d["lse"]).float())
     print(f"[golden {os.path.basename(path)}] out {e_out:.3e} lse {e_lse:.3e}")
     assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
 
 
-def test_cfg1_cpu_runnable_case_full():
+@pytest.mark.parametrize("algo", [1, 2], ids=["single_cta", "cta_pair"])
+def test_cfg1_cpu_runnable_case_full(algo):
     c = W.mla_cfg1()
-    _check(c.q, c.kv, c.indices, c.sm_scale, c.name)
+    _check(c.q, c.kv, c.indices, c.sm_scale, c.name, algo)
 
 
-@pytest.mark.parametrize("h", [1, 16, 64, 128])
+@pytest.mark.parametrize("algo", [1, 2], ids=["single_cta", "cta_pair"])
+@pytest.mark.parametrize("h", [1, 16, 64, 65, 128])
 @pytest.mark.parametrize("topk", [1, 37, 64, 200])
-def test_head_counts_and_ragged_topk(h, topk):
+def test_head_counts_and_ragged_topk(h, topk, algo):
     g = torch.Generator().manual_seed(100 + h + topk)
     s_q, s_kv = 5, 333
     q = torch.randn(s_q, h, 576, generator=g).bfloat16()
     kv = torch.randn(s_kv, 576, generator=g).bfloat16()
     idx = torch.stack([torch.randperm(s_kv, generator=g)[:topk] for _ in range(s_q)]).int()
-    _check(q, kv, idx, 576 ** -0.5, f"h{h}_topk{topk}")
+    _check(q, kv, idx, 576 ** -0.5, f"h{h}_topk{topk}_algo{algo}", algo)
 
 
-def test_padding_patterns():
+@pytest.mark.parametrize("algo", [1, 2], ids=["single_cta", "cta_pair"])
+def test_padding_patterns(algo):
     """Trailing -1 padding, a token with no valid entry, one valid entry, and -1 in the middle."""
     g = torch.Generator().manual_seed(7)
     s_q, h, s_kv, topk = 6, 128, 500, 192
@@ -104,15 +108,18 @@ def test_padding_patterns():
     idx[2, 1:] = -1
     idx[3, 10:70] = -1            # a hole spanning a tile boundary
     idx[4, 0:64] = -1             # a fully masked first tile
-    out, lse = _check(q, kv, idx, 0.07, "padding")
+    out, lse = _check(q, kv, idx, 0.07, "padding", algo)
     assert (out[1] == 0).all() and torch.isinf(lse[1]).all()
     # single selected row: the output is that row's first 512 values exactly (weight 1.0)
     assert torch.equal(out[2].cpu(), kv[idx[2, 0].item(), :512].expand(h, 512))
 
 
-def test_causal_prefill_shape_scaled_down():
+@pytest.mark.parametrize("algo", [1, 2], ids=["single_cta", "cta_pair"])
+def test_causal_prefill_shape_scaled_down(algo):
     c = W.mla_cfg2(s_q=192, s_kv=192, h=128, topk=128)
-    _check(c.q, c.kv, c.indices, c.sm_scale, c.name)
+    _check(c.q, c.kv, c.indices, c.sm_scale, c.name, algo)
+    c = W.mla_cfg2(s_q=300, s_kv=300, h=128, topk=512)      # more tiles than ring stages
+    _check(c.q, c.kv, c.indices, c.sm_scale, c.name, algo)
 
 
 def test_large_scores_are_stable():
@@ -123,7 +130,8 @@ def test_large_scores_are_stable():
     q = (torch.randn(3, 128, 576, generator=g) * 8).bfloat16()
     kv = torch.randn(256, 576, generator=g).bfloat16()
     idx = torch.stack([torch.randperm(256, generator=g)[:128] for _ in range(3)]).int()
-    _check(q, kv, idx, 0.5, "large_scores")
+    _check(q, kv, idx, 0.5, "large_scores_pair", 2)
+    _check(q, kv, idx, 0.5, "large_scores_single", 1)
 
 
 def test_order_invariance_determinism_and_token_sharding():
