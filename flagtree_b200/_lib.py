@@ -29,6 +29,7 @@ class SparseMlaArgs(C.Structure):
         ("page_size", C.c_int32), ("q_per_seq", C.c_int32),
         ("block_table_stride", C.c_int64),
         ("dbg_scores", C.c_void_p),
+        ("n_splits", C.c_int32), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
     ]
 
 
@@ -63,6 +64,8 @@ def load() -> C.CDLL:
                     raise RuntimeError(f"{LIB_PATH} does not export {name}; rebuild the library")
             lib.ftb_sparse_mla_fwd.argtypes = [C.POINTER(SparseMlaArgs), C.c_void_p]
             lib.ftb_sparse_mla_fwd.restype = C.c_int
+            lib.ftb_sparse_mla_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+            lib.ftb_sparse_mla_workspace_bytes.restype = C.c_int64
             if lib.ftb_sizeof_sparse_mla_args() != C.sizeof(SparseMlaArgs):
                 raise RuntimeError("ftb_sparse_mla_args layout differs between the header and the Python mirror")
             if lib.ftb_sizeof_gemm_args() != C.sizeof(GemmArgs):

@@ -54,6 +54,10 @@ struct MlaParams {
   const int32_t* context_lens;
   int page_size, q_per_seq;
   long long bt_stride;
+  // split over the top-k axis: partial results go to scratch and a second kernel merges them
+  int n_splits;
+  float* part_out;   // fp32 [s_q, n_splits, h, 512], each split normalised by its own sum
+  float* part_lse;   // fp32 [s_q, n_splits, h], log2-domain log-sum-exp of the split (-inf = empty)
 };
 
 struct MiscSmem {
@@ -101,8 +105,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int token = blockIdx.x >> 1;
   const int hv = blockIdx.x & 1;
+  const int split = (blockIdx.x >> 1) % p.n_splits;
+  const int token = (blockIdx.x >> 1) / p.n_splits;
   // P overwrites KV column blocks that this CTA's P.V does not read.
   const uint32_t p_s = kv_s + (hv == 0 ? 7 : 0) * kKvBlockBytes;
   const uint32_t v_s = kv_s + (hv * 4) * kKvBlockBytes;
@@ -163,8 +168,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
   float m_run = -INFINITY;   // running max in the log2 domain (score * scale_log2)
   float l_run = 0.0f;        // running sum of 2^(s - m_run)
 
-  for (int tile = 0; tile < n_tiles; ++tile) {
-    const uint32_t parity = tile & 1;
+  // this CTA's share of the tiles (all of them unless the top-k axis is split)
+  const int tiles_per_split = (n_tiles + p.n_splits - 1) / p.n_splits;
+  const int t0 = split * tiles_per_split;
+  const int t1 = min(n_tiles, t0 + tiles_per_split);
+
+  for (int tile = t0; tile < t1; ++tile) {
+    const uint32_t parity = (tile - t0) & 1;
     // ---- indices of this tile
     if (tid < kBN) {
       const int j = tile * kBN + tid;
@@ -291,9 +301,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
                      : "memory");
       }
       // Rescale the running O when the row max moved (whole warp takes part: TMEM ops are collective).
-      const bool need = (tile > 0) && (alpha != 1.0f);
+      const bool need = (tile > t0) && (alpha != 1.0f);
       if (__any_sync(0xffffffffu, need)) {
-        const float a = (tile > 0) ? alpha : 1.0f;
+        const float a = (tile > t0) ? alpha : 1.0f;
 #pragma unroll 1
         for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
           uint32_t orow[32];
@@ -317,7 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
       for (int k = 0; k < 4; ++k) {
         const uint64_t ad = smem_desc_sw128(p_s + k * 32, 16, 1024);
         const uint64_t bd = smem_desc_sw128(v_s + k * 2048, kKvBlockBytes, 1024);
-        umma_f16_ss(tmem + kTmemColO, ad, bd, kIdescPV, (tile | k) != 0 ? 1u : 0u);
+        umma_f16_ss(tmem + kTmemColO, ad, bd, kIdescPV, (tile != t0 || k != 0) ? 1u : 0u);
       }
       umma_commit(bar_o);
     }
@@ -326,15 +336,18 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
     tc_fence_after();
   }
 
-  // ---- epilogue: O / l -> bf16, LSE
+  // ---- epilogue: O / l -> bf16 and LSE, or the fp32 partial of this split
   if (warp < 4) {
     const int head = tid;
     const float inv_l = (l_run > 0.0f) ? 1.0f / l_run : 0.0f;
     __nv_bfloat16* orow = p.out + static_cast<long long>(token) * p.out_st + static_cast<long long>(head) * p.out_sh + hv * kDvHalf;
+    float* prow = nullptr;
+    if (p.n_splits > 1)
+      prow = p.part_out + ((static_cast<long long>(token) * p.n_splits + split) * p.h + head) * 512 + hv * kDvHalf;
 #pragma unroll 1
     for (int c0 = 0; c0 < kDvHalf; c0 += 32) {
       uint32_t acc[32];
-      if (n_tiles > 0) {
+      if (t1 > t0) {
         tmem_ld32(tmem_addr(tmem, warp * 32, kTmemColO + c0), acc);
         tmem_wait_ld();
       } else {
@@ -342,24 +355,36 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
         for (int j = 0; j < 32; ++j) acc[j] = 0u;
       }
       if (head < p.h) {
+        if (prow != nullptr) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l);
-          v.y = pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l);
-          v.z = pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l);
-          v.w = pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l);
-          *reinterpret_cast<uint4*>(orow + c0 + j) = v;
+          for (int j = 0; j < 32; j += 4) {
+            float4 v;
+            v.x = __uint_as_float(acc[j]) * inv_l;
+            v.y = __uint_as_float(acc[j + 1]) * inv_l;
+            v.z = __uint_as_float(acc[j + 2]) * inv_l;
+            v.w = __uint_as_float(acc[j + 3]) * inv_l;
+            *reinterpret_cast<float4*>(prow + c0 + j) = v;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c0 + j) = v;
+          }
         }
       }
     }
     if (hv == 0 && head < p.h) {
-      float v = -INFINITY;
-      if (l_run > 0.0f) {
-        const float l2 = m_run + log2f(l_run);
-        v = p.lse_base2 ? l2 : l2 * 0.6931471805599453f;
+      const float l2 = (l_run > 0.0f) ? m_run + log2f(l_run) : -INFINITY;
+      if (p.n_splits > 1) {
+        p.part_lse[(static_cast<long long>(token) * p.n_splits + split) * p.h + head] = l2;
+      } else {
+        p.lse[static_cast<long long>(token) * p.lse_st + head] = (p.lse_base2 || l2 == -INFINITY) ? l2 : l2 * 0.6931471805599453f;
       }
-      p.lse[static_cast<long long>(token) * p.lse_st + head] = v;
     }
     tc_fence_before();
   }
@@ -371,6 +396,54 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
   if (tid == 0 && p.status != nullptr) {
     if (misc->abort_flag) atomicCAS(p.status, 0, FTB_ERR_TIMEOUT);
     else if (misc->bad_index) atomicCAS(p.status, 0, FTB_ERR_BAD_INDEX);
+  }
+}
+
+
+// Merge of the per-split partial results (the role of the reference's _fwd_kernel_stage2,
+// third_party/mthreads/python/test/wmma/test_accuracy_musa_vllm_mla.py:426-477): weights 2^(lse_k - max),
+// out = sum w_k out_k / sum w_k, and the merged LSE, which the reference does not store.
+// One warp per (token, head); lane i owns output columns [16 i, 16 i + 16).
+__global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const float* __restrict__ part_out,
+                                                               const float* __restrict__ part_lse, __nv_bfloat16* out,
+                                                               float* lse, int s_q, int h, int n_splits, long long out_st,
+                                                               long long out_sh, long long lse_st, int lse_base2) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= s_q * h) return;
+  const int token = w / h, head = w - token * h;
+  float mx = -INFINITY;
+  for (int k = 0; k < n_splits; ++k) mx = fmaxf(mx, part_lse[(static_cast<long long>(token) * n_splits + k) * h + head]);
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+  float wsum = 0.0f;
+  if (mx != -INFINITY) {
+    for (int k = 0; k < n_splits; ++k) {
+      const long long row = (static_cast<long long>(token) * n_splits + k) * h + head;
+      const float l2 = part_lse[row];
+      if (l2 == -INFINITY) continue;
+      const float wk = fast_exp2(l2 - mx);
+      wsum += wk;
+      const float4* src = reinterpret_cast<const float4*>(part_out + row * 512 + lane * 16);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 v = src[j];
+        acc[4 * j] += wk * v.x; acc[4 * j + 1] += wk * v.y; acc[4 * j + 2] += wk * v.z; acc[4 * j + 3] += wk * v.w;
+      }
+    }
+  }
+  const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
+  uint4 o[2];
+  uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ow[j] = pack_bf16x2(acc[2 * j] * inv, acc[2 * j + 1] * inv);
+  uint4* dst = reinterpret_cast<uint4*>(out + token * out_st + head * out_sh + lane * 16);
+  dst[0] = o[0];
+  dst[1] = o[1];
+  if (lane == 0) {
+    const float l2 = wsum > 0.0f ? mx + log2f(wsum) : -INFINITY;
+    lse[token * lse_st + head] = (lse_base2 || l2 == -INFINITY) ? l2 : l2 * 0.6931471805599453f;
   }
 }
 
@@ -423,7 +496,7 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
   if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
   // algo 0 = default: CTA-pair kernel for bf16 KV; algo 1 = one CTA per (token, output half), which is
   // also the kernel of the FP8 paged form and of the debug score tap; algo 2 = CTA-pair kernel.
-  if ((a->algo_id == 0 || a->algo_id == 2) && !a->kv_is_fp8 && a->dbg_scores == nullptr)
+  if ((a->algo_id == 0 || a->algo_id == 2) && !a->kv_is_fp8 && a->dbg_scores == nullptr && a->n_splits <= 1)
     return launch_sparse_mla_pair(a, reinterpret_cast<cudaStream_t>(stream));
   MlaParams p;
   memset(&p, 0, sizeof(p));
@@ -445,7 +518,17 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     p.page_size = a->page_size; p.q_per_seq = a->q_per_seq; p.bt_stride = a->block_table_stride;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const dim3 grid(static_cast<unsigned>(a->s_q) * 2u), block(kThreads);
+  int n_splits = a->n_splits > 0 ? a->n_splits : 1;
+  if (n_splits > 1) {
+    if (a->workspace == nullptr || a->workspace_bytes < ftb_sparse_mla_workspace_bytes(a->s_q, a->h, n_splits)) {
+      set_last_error("ftb_sparse_mla_fwd: n_splits=%d needs a workspace of ftb_sparse_mla_workspace_bytes() bytes", n_splits);
+      return FTB_ERR_INVALID;
+    }
+    p.part_out = reinterpret_cast<float*>(a->workspace);
+    p.part_lse = p.part_out + static_cast<size_t>(a->s_q) * n_splits * a->h * 512;
+  }
+  p.n_splits = n_splits;
+  const dim3 grid(static_cast<unsigned>(a->s_q) * 2u * static_cast<unsigned>(n_splits)), block(kThreads);
   cudaError_t e;
   if (a->kv_is_fp8) {
     e = cudaFuncSetAttribute(sparse_mla_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
@@ -456,5 +539,15 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla)");
     sparse_mla_fwd_kernel<false><<<grid, block, kSmemBytes, st>>>(p);
   }
-  return check_cuda(cudaGetLastError(), "sparse_mla_fwd launch");
+  int rc = check_cuda(cudaGetLastError(), "sparse_mla_fwd launch");
+  if (rc != FTB_OK || n_splits == 1) return rc;
+  const int warps = a->s_q * a->h;
+  sparse_mla_merge_kernel<<<(warps * 32 + 255) / 256, 256, 0, st>>>(p.part_out, p.part_lse, p.out, p.lse, a->s_q, a->h, n_splits,
+                                                                    p.out_st, p.out_sh, p.lse_st, p.lse_base2);
+  return check_cuda(cudaGetLastError(), "sparse_mla_merge launch");
+}
+
+extern "C" FTB_API int64_t ftb_sparse_mla_workspace_bytes(int32_t s_q, int32_t h, int32_t n_splits) {
+  if (n_splits <= 1 || s_q <= 0 || h <= 0) return 0;
+  return static_cast<int64_t>(s_q) * n_splits * h * (512 + 1) * 4;
 }

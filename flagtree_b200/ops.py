@@ -29,6 +29,27 @@ def _stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def _auto_splits(s_q: int, topk: int, device) -> int:
+    """Split the top-k axis when there are too few query tokens to fill the SMs (decode)."""
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    tiles = max(1, (topk + 63) // 64)
+    if 2 * s_q >= sms:
+        return 1
+    return int(max(1, min(16, sms // (2 * s_q), tiles)))
+
+
+def _split_workspace(a, s_q: int, h: int, n_splits: int, device):
+    """Fills the split fields of the argument struct; returns the scratch tensor (kept alive by the caller)."""
+    a.n_splits = n_splits
+    if n_splits <= 1:
+        a.workspace, a.workspace_bytes = None, 0
+        return None
+    nbytes = int(_lib.load().ftb_sparse_mla_workspace_bytes(s_q, h, n_splits))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), nbytes
+    return ws
+
+
 def _check_status(status: Optional[torch.Tensor], what: str):
     if status is None:
         return
@@ -40,8 +61,8 @@ def _check_status(status: Optional[torch.Tensor], what: str):
 def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
                    sm_scale: Optional[float] = None, d_v: int = D_V, *, lse_base2: bool = False,
                    out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
-                   check: bool = False, algo: int = 0, _dbg_scores: Optional[torch.Tensor] = None
-                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+                   check: bool = False, algo: int = 0, num_splits: Optional[int] = None,
+                   _dbg_scores: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Top-k sparse MLA forward.
 
     q [S_q, h, 576] bf16, kv [S_kv, 576] (or [S_kv, 1, 576]) bf16, indices [S_q, topk] int32 with
@@ -50,7 +71,8 @@ def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
     (third_party/mthreads/python/test/wmma/test_accuracy_musa_vllm_mla.py:571-620) with the
     token table as `indices`.  `sm_scale` defaults to 576**-0.5 (:640 of the same file).
     `check=True` reads back the device status word (one host sync) and raises on a bad index
-    or a device-side timeout.
+    or a device-side timeout.  `num_splits` > 1 splits the top-k axis over several CTAs and merges the
+    partial results (the reference's NUM_KV_SPLITS stage 2); it selects the single-CTA kernel.
     """
     _require_cuda(q, kv, indices)
     if kv.dim() == 3:
@@ -90,6 +112,7 @@ def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
         a.status = status.data_ptr() if status is not None else None
         a.kv_is_fp8 = 0
         a.dbg_scores = _dbg_scores.data_ptr() if _dbg_scores is not None else None
+        _ws = _split_workspace(a, s_q, h1 - h0, int(num_splits) if num_splits else 1, q.device)
         with torch.cuda.device(q.device):
             rc = lib.ftb_sparse_mla_fwd(C.byref(a), C.c_void_p(_stream_ptr(q.device)))
         _lib.check(rc, "sparse_mla_fwd")
@@ -100,7 +123,8 @@ def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
 def sparse_mla_fwd_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Tensor,
                          block_table: torch.Tensor, context_lens: torch.Tensor, indices: torch.Tensor,
                          sm_scale: Optional[float] = None, d_v: int = D_V, page_size: int = 64, *,
-                         lse_base2: bool = False, check: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+                         lse_base2: bool = False, check: bool = False, num_splits: Optional[int] = None
+                         ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Sparse MLA decode over a paged FP8 (e4m3) latent cache with one fp32 scale per page.
 
     q [B, n_q, h, 576] bf16; kv_cache [num_pages, page_size, 576] e4m3 (uint8 or float8_e4m3fn);
@@ -143,6 +167,9 @@ def sparse_mla_fwd_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torc
     a.kv_scale, a.block_table, a.context_lens = kv_scale.data_ptr(), block_table.data_ptr(), context_lens.data_ptr()
     a.page_size, a.q_per_seq, a.block_table_stride = page_size, n_q, block_table.stride(0)
     a.dbg_scores = None
+    if num_splits is None:
+        num_splits = _auto_splits(b * n_q, idx2.shape[1], q.device)
+    _ws = _split_workspace(a, b * n_q, h, int(num_splits), q.device)
     with torch.cuda.device(q.device):
         rc = _lib.load().ftb_sparse_mla_fwd(C.byref(a), C.c_void_p(_stream_ptr(q.device)))
     _lib.check(rc, "sparse_mla_fwd_paged")

@@ -78,9 +78,17 @@ typedef struct ftb_sparse_mla_args {
   int64_t block_table_stride;
   /* Optional debug tap: fp32 [s_q, 128, topk_padded_to_64] raw (unscaled) scores. NULL = off. */
   float* dbg_scores;
+  /* Split of the top-k axis (for few query tokens, e.g. decode): n_splits > 1 makes every split write a
+   * partial result to `workspace` (ftb_sparse_mla_workspace_bytes() bytes of device memory, contents
+   * need not be initialised) and a merge kernel combine them, the role of _fwd_kernel_stage2
+   * (test_accuracy_musa_vllm_mla.py:426-477).  0 or 1 = no split, no workspace. */
+  int32_t n_splits;
+  void* workspace;
+  int64_t workspace_bytes;
 } ftb_sparse_mla_args;
 
 FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* args, void* stream);
+FTB_API int64_t ftb_sparse_mla_workspace_bytes(int32_t s_q, int32_t h, int32_t n_splits);
 /* sizeof(ftb_sparse_mla_args) as compiled into the library (for bindings to check their mirror). */
 FTB_API int ftb_sizeof_sparse_mla_args(void);
 

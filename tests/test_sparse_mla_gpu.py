@@ -226,3 +226,36 @@ def test_paged_fp8_short_context_and_padding():
                                                 c.indices, c.sm_scale, page_size=c.page_size)
     e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
     assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+
+
+@pytest.mark.parametrize("splits", [2, 3, 8])
+def test_split_topk_and_merge_match_unsplit(splits):
+    """Top-k axis split over several CTAs + merge kernel (the reference's stage 2) against the oracle and
+    against the unsplit kernel; includes a token whose later splits are empty and one with no valid entry."""
+    g = torch.Generator().manual_seed(40 + splits)
+    s_q, h, s_kv, topk = 5, 128, 700, 448
+    q = torch.randn(s_q, h, 576, generator=g).bfloat16()
+    kv = torch.randn(s_kv, 576, generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(s_kv, generator=g)[:topk] for _ in range(s_q)]).int()
+    idx[1, 70:] = -1
+    idx[2, :] = -1
+    out, lse = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), 0.06, check=True, num_splits=splits)
+    ref_out, ref_lse = sparse_mla_fwd_ref(q, kv, idx, 0.06)
+    e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
+    print(f"[split {splits}] out {e_out:.3e} lse {e_lse:.3e}")
+    assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+    out1, lse1 = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), 0.06, check=True, algo=1)
+    assert (out.float() - out1.float()).abs().max().item() <= 1e-2
+
+
+def test_paged_fp8_decode_with_splits():
+    c = W.mla_cfg3(batch=3, n_q=2, h=128, topk=512, len_lo=600, len_hi=2500)
+    args = (c.q.to(DEV), c.kv_cache.to(DEV), c.kv_scale.to(DEV), c.block_table.to(DEV), c.context_lens.to(DEV),
+            c.indices.to(DEV), c.sm_scale)
+    out, lse = sparse_mla_fwd_paged(*args, page_size=c.page_size, check=True)            # automatic split count
+    out4, lse4 = sparse_mla_fwd_paged(*args, page_size=c.page_size, check=True, num_splits=4)
+    ref_out, ref_lse = sparse_mla_fwd_paged_ref(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens,
+                                                c.indices, c.sm_scale, page_size=c.page_size)
+    for o, l in ((out, lse), (out4, lse4)):
+        e_out, e_lse = _errors(o, l, ref_out, ref_lse)
+        assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
