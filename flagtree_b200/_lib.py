@@ -41,6 +41,14 @@ class GemmArgs(C.Structure):
                 ("status", C.c_void_p)]
 
 
+class GemmFp8Args(C.Structure):
+    """Mirror of `ftb_gemm_fp8_args`."""
+    _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("a_scale", C.c_void_p), ("b_scale", C.c_void_p),
+                ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
+                ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("a_scale_ld", C.c_int64), ("b_scale_ld", C.c_int64),
+                ("status", C.c_void_p)]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -71,6 +79,9 @@ def load() -> C.CDLL:
             if lib.ftb_sizeof_gemm_args() != C.sizeof(GemmArgs):
                 raise RuntimeError("ftb_gemm_args layout differs between the header and the Python mirror")
             lib.ftb_gemm_bf16.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
+            if lib.ftb_sizeof_gemm_fp8_args() != C.sizeof(GemmFp8Args):
+                raise RuntimeError("ftb_gemm_fp8_args layout differs between the header and the Python mirror")
+            lib.ftb_gemm_fp8_blockscaled.argtypes = [C.POINTER(GemmFp8Args), C.c_void_p]
             lib.ftb_gemm_rs_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
             lib.ftb_gemm_rs_ctx_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int,
                                                    C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]

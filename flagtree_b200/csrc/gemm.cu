@@ -463,10 +463,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
         tc_fence_before();
-        __threadfence_system();        // this lane's stores are visible to peers before the count below
-        __syncwarp();
+        __syncwarp();                  // orders the 32 lanes' stores before lane 0's fence below
         if (lane == 0) {
-          release_acc(acc);
+          release_acc(acc);            // the MMAs of the next tile do not wait for the fence
+          __threadfence_system();      // the warp's stores are visible to peers before the count
           const unsigned int cnt = atomicAdd(p.blk_counter + m_blk, 1u) + 1u;
           if (cnt == p.flag_target) {
             // last warp of the row block on this rank: tell the owner (one 4-byte remote store)

@@ -551,3 +551,4 @@ extern "C" FTB_API int64_t ftb_sparse_mla_workspace_bytes(int32_t s_q, int32_t h
   if (n_splits <= 1 || s_q <= 0 || h <= 0) return 0;
   return static_cast<int64_t>(s_q) * n_splits * h * (512 + 1) * 4;
 }
+

@@ -9,8 +9,8 @@
 // TMEM per CTA ("2x2" layout of a pair MMA with 64 rows per CTA: row r, column j of an N-wide result
 // sits in lane r + 64*(j >= N/2), column j mod N/2): S double-buffered 2 x 32 columns, O 256 columns.
 //
-// Warp roles per CTA (288 threads): warps 0-3 softmax / rescale / epilogue (thread = TMEM lane),
-// warp 4 MMA issuer (even CTA only) and TMEM owner, warps 5-6 gather K tiles, warps 7-8 gather V tiles.
+// Warp roles per CTA (416 threads): warps 0-3 softmax / rescale / epilogue (thread = TMEM lane),
+// warp 4 MMA issuer (even CTA only) and TMEM owner, warps 5-8 gather K tiles, warps 9-12 gather V tiles.
 // K and V tiles live in separate 2-deep rings: a K stage is free as soon as Q.K^T of its tile has
 // finished, a V stage when P.V has.  All waits are bounded.
 #include "sm100.cuh"
@@ -39,7 +39,7 @@ constexpr int kOffV = kOffK + 2 * kKStage;
 constexpr int kOffP = kOffV + 2 * kVStage;
 constexpr int kOffMisc = kOffP + 2 * kPBytes;        // 229376
 constexpr int kSmemBytes = 232448;                   // everything a CTA may have: 3072 B for Misc + alignment
-constexpr int kThreads = 288;
+constexpr int kThreads = 416;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColO = 0, kColS = 256;
 
@@ -57,8 +57,8 @@ struct Params {
 };
 
 struct Misc {
-  unsigned long long k_full[2];    // even CTA: both CTAs' K rows of the stage have landed (4 warp arrivals)
-  unsigned long long v_full[2];    // even CTA: both CTAs' V columns of the stage have landed (4 warp arrivals)
+  unsigned long long k_full[2];    // even CTA: both CTAs' K rows of the stage have landed (8 warp arrivals)
+  unsigned long long v_full[2];    // even CTA: both CTAs' V columns of the stage have landed (8 warp arrivals)
   unsigned long long p_full[2];    // even CTA: P written and O rescaled by all 8 softmax warps
   unsigned long long s_full[2];    // every CTA: Q.K^T of the tile finished (S readable, K stage free)
   unsigned long long pv_done[2];   // every CTA: P.V of the tile finished (V stage, P buffer free, O updated)
@@ -102,8 +102,8 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_pair_kernel(const Para
     misc->n_scan = 0;
     misc->bad_index = 0;
     for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&misc->k_full[i]), 4);
-      mbar_init(smem_u32(&misc->v_full[i]), 4);
+      mbar_init(smem_u32(&misc->k_full[i]), 8);
+      mbar_init(smem_u32(&misc->v_full[i]), 8);
       mbar_init(smem_u32(&misc->p_full[i]), 8);
       mbar_init(smem_u32(&misc->s_full[i]), 1);
       mbar_init(smem_u32(&misc->pv_done[i]), 1);
@@ -309,32 +309,44 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_pair_kernel(const Para
         issue_pv(i);
       }
     }
-  } else if (warp < 7) {
-    // ---------------------------------------------------------------- K producers (warps 5-6, 64 threads)
-    const int pt = tid - 160;                        // 0..63
+  } else if (warp < 9) {
+    // ---------------------------------------------------------------- K producers (warps 5-8, 128 threads)
+    // A warp copies whole rows: lanes cover consecutive 16-byte chunks of one gathered row (72 per row,
+    // three warp-wide cp.async), so no per-chunk index arithmetic and full 32-byte sectors.
+    const int pt = tid - 160;                        // 0..127
+    const int pw = warp - 5;                         // 0..3: rows pw*8 .. pw*8+7 of this CTA's 32
     const uint32_t k_full0 = mapa_shared(smem_u32(&misc->k_full[0]), 0);
     const uint32_t k_full1 = mapa_shared(smem_u32(&misc->k_full[1]), 0);
-    int idx_next = (pt < p.topk) ? idx_row[pt] : -1;   // index of tile 0, slot pt
+    int idx_next = (pt < kNT && pt < p.topk) ? idx_row[pt] : -1;   // index of tile 0, slot pt
     for (int i = 0; i < n_tiles; ++i) {
       const int b = i & 1;
       const int logical = idx_next;
       {
         const int jn = (i + 1) * kNT + pt;
-        idx_next = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+        idx_next = (pt < kNT && i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
       }
       // K stage b was last read by Q.K^T of tile i-2
       if (i >= 2) mbar_wait(smem_u32(&misc->s_full[b]), ((i - 2) >> 1) & 1u, abort_flag);
-      const bool ok = logical >= 0 && logical < p.s_kv;
-      if (logical >= p.s_kv) misc->bad_index = 1;
-      const uint32_t m = __ballot_sync(0xffffffffu, ok);
-      if (lane == 0) misc->valid_mask[i & 3][warp - 5] = m;
-      if ((pt >> 5) == cta) misc->k_rows[b][pt & 31] = ok ? logical : 0;
-      named_bar_sync(3, 64);
-      for (int c = pt; c < kRowsOwn * (kDqk / 8); c += 64) {
-        const int r = c / (kDqk / 8);
-        const int ch = c - r * (kDqk / 8);
-        const uint32_t dst = k_s + b * kKStage + (ch >> 3) * kKBlock + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-        cp_async16(dst, p.kv + static_cast<long long>(misc->k_rows[b][r]) * p.kv_sr + ch * 8);
+      if (pt < kNT) {
+        const bool ok = logical >= 0 && logical < p.s_kv;
+        if (logical >= p.s_kv) misc->bad_index = 1;
+        const uint32_t m = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) misc->valid_mask[i & 3][pt >> 5] = m;
+        if ((pt >> 5) == cta) misc->k_rows[b][pt & 31] = ok ? logical : 0;
+      }
+      named_bar_sync(3, 128);
+      const uint32_t stage = k_s + b * kKStage;
+#pragma unroll
+      for (int rr = 0; rr < 8; ++rr) {
+        const int r = pw * 8 + rr;
+        const __nv_bfloat16* src = p.kv + static_cast<long long>(misc->k_rows[b][r]) * p.kv_sr;
+        const uint32_t drow = stage + r * 128;
+#pragma unroll
+        for (int part = 0; part < 3; ++part) {
+          const int ch = part * 32 + lane;
+          if (ch < kDqk / 8)
+            cp_async16(drow + (ch >> 3) * kKBlock + (((ch & 7) ^ (r & 7)) << 4), src + ch * 8);
+        }
       }
       cp_async_commit();
       if (i >= 1) {
@@ -352,32 +364,34 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_pair_kernel(const Para
       if (lane == 0) mbar_arrive_cluster(((n_tiles - 1) & 1) ? k_full1 : k_full0);
     }
   } else {
-    // ---------------------------------------------------------------- V producers (warps 7-8, 64 threads)
-    const int pt = tid - 224;                        // 0..63
+    // ---------------------------------------------------------------- V producers (warps 9-12, 128 threads)
+    // One warp-wide cp.async per gathered row: the 32 lanes cover this CTA's four 64-column blocks
+    // (two 256-byte runs of the latent row).
+    const int pt = tid - 288;                        // 0..127
+    const int pw = warp - 9;                         // rows pw*16 .. pw*16+15
     const uint32_t v_full0 = mapa_shared(smem_u32(&misc->v_full[0]), 0);
     const uint32_t v_full1 = mapa_shared(smem_u32(&misc->v_full[1]), 0);
-    int idx_next = (pt < p.topk) ? idx_row[pt] : -1;
+    const int blk = lane >> 3;                       // block inside the V stage
+    const int c16 = lane & 7;
+    const int src_off = ((blk >> 1) * 4 + 2 * cta + (blk & 1)) * 64 + c16 * 8;   // element offset in the row
+    int idx_next = (pt < kNT && pt < p.topk) ? idx_row[pt] : -1;
     for (int i = 0; i < n_tiles; ++i) {
       const int b = i & 1;
       const int logical = idx_next;
       {
         const int jn = (i + 1) * kNT + pt;
-        idx_next = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+        idx_next = (pt < kNT && i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
       }
       // V stage b was last read by P.V of tile i-2
       if (i >= 2) mbar_wait(smem_u32(&misc->pv_done[b]), ((i - 2) >> 1) & 1u, abort_flag);
-      const bool ok = logical >= 0 && logical < p.s_kv;
-      misc->v_rows[b][pt] = ok ? logical : 0;
-      named_bar_sync(4, 64);
-      // this CTA's output columns: 64-column blocks {2c, 2c+1, 4+2c, 5+2c} of the latent row
-      for (int c = pt; c < kNT * 32; c += 64) {
-        const int r = c >> 5;
-        const int w = c & 31;
-        const int blk = w >> 3;                      // 0..3: block inside the V stage
-        const int c16 = w & 7;
-        const int src_blk = (blk >> 1) * 4 + 2 * cta + (blk & 1);
-        const uint32_t dst = v_s + b * kVStage + blk * kVBlock + r * 128 + ((c16 ^ (r & 7)) << 4);
-        cp_async16(dst, p.kv + static_cast<long long>(misc->v_rows[b][r]) * p.kv_sr + src_blk * 64 + c16 * 8);
+      if (pt < kNT) misc->v_rows[b][pt] = (logical >= 0 && logical < p.s_kv) ? logical : 0;
+      named_bar_sync(4, 128);
+      const uint32_t stage = v_s + b * kVStage + blk * kVBlock;
+#pragma unroll
+      for (int rr = 0; rr < 16; ++rr) {
+        const int r = pw * 16 + rr;
+        cp_async16(stage + r * 128 + ((c16 ^ (r & 7)) << 4),
+                   p.kv + static_cast<long long>(misc->v_rows[b][r]) * p.kv_sr + src_off);
       }
       cp_async_commit();
       if (i >= 1) {

@@ -241,6 +241,35 @@ def _gemm_into(a, b, c, status=None):
     _lib.check(rc, "matmul")
 
 
+def matmul_fp8_blockscaled(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor, *,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = (A * a_scale) @ (B * b_scale) for e4m3 operands (uint8 or float8_e4m3fn storage) with 1x128 (A) and
+    128x128 (B) fp32 block scales; bf16 result.  Operands follow the reference's fp8 matmul convention of
+    raw 8-bit patterns (python/test/unit/operators/test_matmul.py:165-169)."""
+    _require_cuda(a, a_scale, b, b_scale)
+    for t in (a, b):
+        assert t.dtype in (torch.uint8, torch.float8_e4m3fn), "operands must hold e4m3 bytes"
+    assert a.shape[1] == b.shape[0], "incompatible dimensions"
+    m, k = a.shape
+    n = b.shape[1]
+    assert k % 128 == 0 and n % 128 == 0, "k and n must be multiples of the 128-wide scale blocks"
+    assert a_scale.shape == (m, k // 128) and b_scale.shape == (k // 128, n // 128)
+    assert a_scale.dtype == torch.float32 and b_scale.dtype == torch.float32
+    assert a.stride(1) == 1 and b.stride(1) == 1 and a_scale.stride(1) == 1 and b_scale.stride(1) == 1
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
+    g = _lib.GemmFp8Args()
+    g.a, g.b, g.c, g.a_scale, g.b_scale = a.data_ptr(), b.data_ptr(), out.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr()
+    g.m, g.n, g.k = m, n, k
+    g.lda, g.ldb, g.ldc = a.stride(0), b.stride(0), out.stride(0)
+    g.a_scale_ld, g.b_scale_ld = a_scale.stride(0), b_scale.stride(0)
+    g.status = None
+    with torch.cuda.device(a.device):
+        rc = _lib.load().ftb_gemm_fp8_blockscaled(C.byref(g), C.c_void_p(_stream_ptr(a.device)))
+    _lib.check(rc, "matmul_fp8_blockscaled")
+    return out
+
+
 class GemmRsContext:
     """Workspace of one (M, N, group) GEMM + reduce-scatter shape: peer-mapped receive slots and flags.
 

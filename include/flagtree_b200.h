@@ -113,6 +113,28 @@ FTB_API int ftb_gemm_bf16(const ftb_gemm_args* args, void* stream);
 FTB_API int ftb_sizeof_gemm_args(void);
 
 /* ------------------------------------------------------------------------------------------
+ * Block-scaled FP8 GEMM: A [m,k] e4m3 with one fp32 scale per 1x128 block (a_scale [m, k/128]),
+ * B [k,n] e4m3 with one fp32 scale per 128x128 block (b_scale [k/128, n/128]), bf16 output,
+ *   C = sum_kb (A[:,kb] . B[kb,:]) * a_scale[:,kb] (x) b_scale[kb, :/128],  fp32 accumulation per K block.
+ * GEMM core: python/triton/ops/matmul.py:92-151 with fp8 operands (:135-136, :204-213) and the fp8
+ * descriptor GEMM of third_party/mthreads/python/test/sqmma/base_cases/test_batch_fp8.py:8-25; the
+ * block scales have no counterpart in the reference op.  k and n must be multiples of 128.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ftb_gemm_fp8_args {
+  const void* a;          /* e4m3 [m, k], lda (bytes = elements) */
+  const void* b;          /* e4m3 [k, n], ldb */
+  void* c;                /* bf16 [m, n], ldc */
+  const float* a_scale;   /* fp32 [m, k/128], row stride a_scale_ld */
+  const float* b_scale;   /* fp32 [k/128, n/128], row stride b_scale_ld */
+  int32_t m, n, k;
+  int64_t lda, ldb, ldc, a_scale_ld, b_scale_ld;
+  int32_t* status;
+} ftb_gemm_fp8_args;
+
+FTB_API int ftb_gemm_fp8_blockscaled(const ftb_gemm_fp8_args* args, void* stream);
+FTB_API int ftb_sizeof_gemm_fp8_args(void);
+
+/* ------------------------------------------------------------------------------------------
  * Row-parallel GEMM fused with reduce-scatter (tensor parallel size tp, one rank per GPU).
  *
  * Rank r holds A_r [M, K/tp] and B_r [K/tp, N]; C = sum_r A_r.B_r; rank r receives rows
