@@ -552,3 +552,49 @@ extern "C" FTB_API int64_t ftb_sparse_mla_workspace_bytes(int32_t s_q, int32_t h
   return static_cast<int64_t>(s_q) * n_splits * h * (512 + 1) * 4;
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Entry point for callers that may not allocate device memory.
+//
+// Some hosts of this library run where cudaMalloc is off limits: inside a serving engine that has
+// handed all device memory to its own pool, inside a plugin sandbox whose allocator hooks reject
+// foreign allocations, or on a path that must not touch the allocator because a synchronising
+// allocation would stall other streams.  For them the scratch of the split sparse-MLA forward (the
+// per-split partial outputs and their log-sum-exps) lives in a fixed array inside the library image.
+// The array costs FTB_MLA_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library,
+// from load until the process exits, whether or not this entry point is ever called.
+// ---------------------------------------------------------------------------------------------
+#define FTB_MLA_STATIC_SCRATCH_BYTES (32ll << 20)
+static __device__ __align__(256) unsigned char g_mla_static_scratch[FTB_MLA_STATIC_SCRATCH_BYTES];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel can use;
+// the device address is looked up once per device, with that device current.
+static void* g_mla_static_scratch_addr[64] = {nullptr};
+
+extern "C" FTB_API int64_t ftb_sparse_mla_static_scratch_bytes(void) { return FTB_MLA_STATIC_SCRATCH_BYTES; }
+
+extern "C" FTB_API int ftb_sparse_mla_fwd_static_scratch(const ftb_sparse_mla_args* a, void* stream) {
+  using namespace ftb;
+  if (a == nullptr) { set_last_error("ftb_sparse_mla_fwd_static_scratch: args is NULL"); return FTB_ERR_INVALID; }
+  const int64_t need = ftb_sparse_mla_workspace_bytes(a->s_q, a->h, a->n_splits);
+  if (need > FTB_MLA_STATIC_SCRATCH_BYTES) {
+    set_last_error("ftb_sparse_mla_fwd_static_scratch: s_q=%d x n_splits=%d x h=%d needs %lld bytes of scratch, the built-in "
+                   "array holds %lld; use fewer splits or ftb_sparse_mla_fwd with a caller-provided workspace",
+                   a->s_q, a->n_splits, a->h, static_cast<long long>(need), static_cast<long long>(FTB_MLA_STATIC_SCRATCH_BYTES));
+    return FTB_ERR_INVALID;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return check_cuda(e, "ftb_sparse_mla_fwd_static_scratch: cudaGetDevice");
+  if (dev < 0 || dev >= 64) { set_last_error("ftb_sparse_mla_fwd_static_scratch: device ordinal %d out of range", dev); return FTB_ERR_INVALID; }
+  if (g_mla_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_mla_static_scratch);
+    if (e != cudaSuccess) return check_cuda(e, "ftb_sparse_mla_fwd_static_scratch: cudaGetSymbolAddress");
+    g_mla_static_scratch_addr[dev] = ptr;
+  }
+  ftb_sparse_mla_args b = *a;
+  b.workspace = g_mla_static_scratch_addr[dev];
+  b.workspace_bytes = FTB_MLA_STATIC_SCRATCH_BYTES;
+  return ftb_sparse_mla_fwd(&b, stream);
+}

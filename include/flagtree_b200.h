@@ -89,6 +89,18 @@ typedef struct ftb_sparse_mla_args {
 
 FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* args, void* stream);
 FTB_API int64_t ftb_sparse_mla_workspace_bytes(int32_t s_q, int32_t h, int32_t n_splits);
+/* Same operation for callers that cannot allocate device memory (an engine that owns the whole device
+ * through its own pool, a sandboxed plugin, a latency path that must stay clear of the allocator).  It has
+ * no counterpart in the reference, whose wrappers always receive `attn_logits` from the caller.
+ * The split scratch is a fixed array of ftb_sparse_mla_static_scratch_bytes() (32 MiB) inside the library
+ * image, resident on every GPU that loads the library until the process exits; `workspace` in `args` is
+ * ignored.  A problem whose ftb_sparse_mla_workspace_bytes(s_q, h, n_splits) exceeds that size is
+ * rejected with FTB_ERR_INVALID.  No cudaMalloc / cudaFree or other allocating call is made.  The first
+ * call on each device looks up the array's device address (cudaGetSymbolAddress): make that call before
+ * starting any stream capture.  All calls on a device share the array: two calls that overlap on the GPU
+ * (different streams) race on it, and nothing in it needs to be, or is, cleared between calls. */
+FTB_API int ftb_sparse_mla_fwd_static_scratch(const ftb_sparse_mla_args* args, void* stream);
+FTB_API int64_t ftb_sparse_mla_static_scratch_bytes(void);
 /* sizeof(ftb_sparse_mla_args) as compiled into the library (for bindings to check their mirror). */
 FTB_API int ftb_sizeof_sparse_mla_args(void);
 
