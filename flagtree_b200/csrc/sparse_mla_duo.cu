@@ -1,0 +1,522 @@
+// Top-k sparse MLA forward, role-split CTA pair (cluster of 2, cta_group::1 MMAs), bf16 KV.
+//
+// One cluster per query token; both CTAs run full-rate M = 128 tcgen05 MMAs over all 128 heads:
+//   CTA 0  "score" : S = Q.K^T (N = 128 gathered rows, K = 576) and the online softmax.  It keeps Q
+//                    (147 KB) and a 4-slot ring of K column blocks [128 rows x 128 B]; S is double
+//                    buffered in TMEM.  P (bf16) and the per-row rescale factor are written straight
+//                    into CTA 1's shared memory (st.shared::cluster).
+//   CTA 1  "value" : O += P.V (N = 2 x 256, K = 128 rows per tile) with the full O [128 x 512] fp32 in
+//                    TMEM (all 512 columns), a 4-slot ring of V slabs [32 rows x 1024 B], two P buffers,
+//                    the O rescale ("correction") and the epilogue.
+// Nothing is computed twice and no accumulator is split; the price is that K and V are gathered
+// separately (1152 + 1024 bytes per selected row).
+//
+// Warps (320 threads per CTA): 0-3 softmax (CTA 0) / correction + epilogue (CTA 1), 4 MMA issuer,
+// 5-8 K producers (CTA 0), 5 relay + 6-9 V producers (CTA 1).  Every wait is bounded.
+#include "sm100.cuh"
+
+namespace ftb {
+
+void set_last_error(const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+
+namespace mla3 {
+
+constexpr int kDqk = 576;
+constexpr int kNChunk = 9;
+constexpr int kNT = 128;                       // gathered rows per tile
+constexpr int kQBlock = 128 * 128;             // 16384: [128 heads x 128 B]
+constexpr int kQBytes = kNChunk * kQBlock;     // 147456
+constexpr int kNK = 4;                         // K ring slots
+constexpr int kKSlot = kNT * 128;              // 16384: [128 rows x 128 B]
+constexpr int kNV = 4;                         // V ring slots
+constexpr int kVSlabRows = 32;
+constexpr int kVBlock = kVSlabRows * 128;      // 4096: one 64-column block of a slab
+constexpr int kVSlab = 8 * kVBlock;            // 32768
+constexpr int kPBuf = 2 * kQBlock;             // 32768: P [128 heads x 128 rows] bf16 as two 64-row blocks
+// CTA 0 layout: Q | K ring | misc.   CTA 1 layout: V ring | P x 2 | misc.
+constexpr int kOff0K = kQBytes;
+constexpr int kOff0Misc = kOff0K + kNK * kKSlot;           // 212992
+constexpr int kOff1P = kNV * kVSlab;                       // 131072
+constexpr int kOff1Misc = kOff1P + 2 * kPBuf;              // 196608
+constexpr int kSmemBytes = kOff0Misc + 4096 + 1024;        // the larger of the two + misc + alignment slack
+constexpr int kThreads = 320;
+
+struct Params {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* kv;
+  const int32_t* indices;
+  __nv_bfloat16* out;
+  float* lse;
+  int s_q, h, s_kv, topk;
+  long long q_st, q_sh, kv_sr, idx_st, out_st, out_sh, lse_st;
+  float scale_log2;
+  int lse_base2;
+  int* status;
+};
+
+struct Misc0 {   // CTA 0
+  unsigned long long k_full[kNK];   // 128 producer threads, each when its own copies have landed
+  unsigned long long k_free[kNK];   // tcgen05.commit
+  unsigned long long s_full[2];     // tcgen05.commit
+  unsigned long long s_free[2];     // 4 softmax warps
+  unsigned long long p_free[2];     // relay warp of CTA 1 (remote arrival)
+  uint32_t tmem_base;
+  int abort_flag;
+  int n_scan;
+  int bad_index;
+  uint32_t valid_mask[4][4];        // per tile (mod 4): 128 validity bits
+  int rows[2][kNT];
+};
+struct Misc1 {   // CTA 1
+  unsigned long long v_full[kNV];   // 128 producer threads, each when its own copies have landed
+  unsigned long long v_free[kNV];   // tcgen05.commit
+  unsigned long long p_full[2];     // 4 softmax warps of CTA 0 (remote arrivals)
+  unsigned long long corr_done[2];  // 4 correction warps
+  unsigned long long pv_done[2];    // tcgen05.commit
+  unsigned long long fin;           // 4 softmax warps of CTA 0: 1/l is in place
+  uint32_t tmem_base;
+  int abort_flag;
+  int n_scan;
+  int pad;
+  float alpha[3][128];              // rescale factor of the tile (two buffers) and the final 1/l
+  int rows[2][kNT];
+};
+static_assert(sizeof(Misc0) <= 4096 && sizeof(Misc1) <= 4096, "misc area");
+static_assert(kOff1Misc + 4096 + 1024 <= kSmemBytes, "CTA 1 layout fits");
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait2() { asm volatile("cp.async.wait_group 2;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait0() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw_addr);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cta = static_cast<int>(cluster_ctarank());
+  const int token = blockIdx.x >> 1;
+  Misc0* m0 = reinterpret_cast<Misc0*>(sm + kOff0Misc);
+  Misc1* m1 = reinterpret_cast<Misc1*>(sm + kOff1Misc);
+  // abort_flag / n_scan / tmem_base sit at different offsets in the two layouts: pick this CTA's
+  volatile int* abort_flag = cta == 0 ? &m0->abort_flag : &m1->abort_flag;
+  int* n_scan_p = cta == 0 ? &m0->n_scan : &m1->n_scan;
+  uint32_t* tmem_base_p = cta == 0 ? &m0->tmem_base : &m1->tmem_base;
+
+  if (tid == 0) {
+    *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    *n_scan_p = 0;
+    if (cta == 0) {
+      m0->bad_index = 0;
+      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), 128); mbar_init(smem_u32(&m0->k_free[i]), 1); }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(smem_u32(&m0->s_full[i]), 1);
+        mbar_init(smem_u32(&m0->s_free[i]), 4);
+        mbar_init(smem_u32(&m0->p_free[i]), 1);
+      }
+    } else {
+      for (int i = 0; i < kNV; ++i) { mbar_init(smem_u32(&m1->v_full[i]), 128); mbar_init(smem_u32(&m1->v_free[i]), 1); }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(smem_u32(&m1->p_full[i]), 4);
+        mbar_init(smem_u32(&m1->corr_done[i]), 4);
+        mbar_init(smem_u32(&m1->pv_done[i]), 1);
+      }
+      mbar_init(smem_u32(&m1->fin), 4);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (*abort_flag) return;   // an earlier launch failed: both CTAs read the same status word
+
+  if (warp == 4) {
+    tmem_alloc(smem_u32(tmem_base_p), cta == 0 ? 256u : 512u);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  const int32_t* idx_row = p.indices + static_cast<long long>(token) * p.idx_st;
+  {
+    int local = 0;
+    for (int j = tid; j < p.topk; j += kThreads)
+      if (idx_row[j] >= 0) local = j + 1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) local = max(local, __shfl_xor_sync(0xffffffffu, local, o));
+    if (lane == 0 && local > 0) atomicMax(n_scan_p, local);
+  }
+  if (cta == 0) {
+    const __nv_bfloat16* q_tok = p.q + static_cast<long long>(token) * p.q_st;
+    for (int c = tid; c < 128 * (kDqk / 8); c += kThreads) {
+      const int r = c / (kDqk / 8);
+      const int ch = c - r * (kDqk / 8);
+      const uint32_t dst = base + (ch >> 3) * kQBlock + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+      if (r < p.h) cp_async16(dst, q_tok + static_cast<long long>(r) * p.q_sh + ch * 8);
+      else asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
+    }
+    cp_async_commit();
+    cp_async_wait_all();
+    fence_proxy_async_smem();
+  }
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_base_p;
+  const int n_tiles = (*n_scan_p + kNT - 1) / kNT;
+
+  if (cta == 0) {
+    // ======================================================================= CTA 0: scores
+    const uint32_t q_s = base;
+    const uint32_t k_s = base + kOff0K;
+    if (warp < 4) {
+      // ---------------------------------------------------------------- softmax (thread = head)
+      const uint32_t p_remote = mapa_shared(base + kOff1P, 1);
+      const uint32_t alpha_remote = mapa_shared(smem_u32(&m1->alpha[0][0]), 1);
+      const uint32_t p_full_r[2] = {mapa_shared(smem_u32(&m1->p_full[0]), 1), mapa_shared(smem_u32(&m1->p_full[1]), 1)};
+      float m_run = -INFINITY, l_run = 0.0f;
+      for (int i = 0; i < n_tiles; ++i) {
+        const int b = i & 1;
+        mbar_wait(smem_u32(&m0->s_full[b]), (i >> 1) & 1u, abort_flag);
+        tc_fence_after();
+        uint32_t sr[4][32];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tmem_addr(tmem, warp * 32, b * 128 + q4 * 32), sr[q4]);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&m0->s_free[b]));
+        const uint32_t vm0 = m0->valid_mask[i & 3][0], vm1 = m0->valid_mask[i & 3][1];
+        const uint32_t vm2 = m0->valid_mask[i & 3][2], vm3 = m0->valid_mask[i & 3][3];
+        const bool all_valid = (vm0 & vm1 & vm2 & vm3) == 0xffffffffu;     // same for every thread of the CTA
+        float mx = -INFINITY;
+        if (all_valid) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sr[q4][j]));
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint32_t vm = q4 == 0 ? vm0 : q4 == 1 ? vm1 : q4 == 2 ? vm2 : vm3;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if ((vm >> j) & 1u) mx = fmaxf(mx, __uint_as_float(sr[q4][j]));
+          }
+        }
+        // Lazy maximum: only move the reference when it grows by more than 2^8, so that the
+        // accumulator in the other CTA is rarely rescaled (P stays below 256, exact enough in bf16/fp32).
+        const float m_cand = fmaxf(m_run, mx * p.scale_log2);
+        float alpha = 1.0f;
+        if (m_cand > m_run + 8.0f || m_run == -INFINITY) {
+          alpha = (m_run == -INFINITY) ? 0.0f : fast_exp2(m_run - m_cand);
+          m_run = m_cand;
+        }
+        const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
+        float psum = 0.0f;
+        uint32_t pk[64];
+        if (all_valid) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float a0 = fast_exp2(fmaf(__uint_as_float(sr[q4][j]), p.scale_log2, -m_use));
+              const float a1 = fast_exp2(fmaf(__uint_as_float(sr[q4][j + 1]), p.scale_log2, -m_use));
+              psum += a0 + a1;
+              pk[q4 * 16 + (j >> 1)] = pack_bf16x2(a0, a1);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint32_t vm = q4 == 0 ? vm0 : q4 == 1 ? vm1 : q4 == 2 ? vm2 : vm3;
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float a0 = ((vm >> j) & 1u) ? fast_exp2(fmaf(__uint_as_float(sr[q4][j]), p.scale_log2, -m_use)) : 0.0f;
+              const float a1 = ((vm >> (j + 1)) & 1u) ? fast_exp2(fmaf(__uint_as_float(sr[q4][j + 1]), p.scale_log2, -m_use)) : 0.0f;
+              psum += a0 + a1;
+              pk[q4 * 16 + (j >> 1)] = pack_bf16x2(a0, a1);
+            }
+          }
+        }
+        l_run = l_run * alpha + psum;
+        // P buffer b of CTA 1 was last read by P.V of tile i-2
+        if (i >= 2) mbar_wait(smem_u32(&m0->p_free[b]), ((i - 2) >> 1) & 1u, abort_flag);
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          // 16-byte chunk c of the row: rows 8c..8c+7 of the tile; block c/8, position (c%8) ^ (head%8)
+          const uint32_t dst = p_remote + b * kPBuf + (c >> 3) * kQBlock + tid * 128 + (((c & 7) ^ (tid & 7)) << 4);
+          st_cluster_v4(dst, pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        }
+        st_cluster_f32(alpha_remote + (b * 128 + tid) * 4, alpha);
+        fence_proxy_async_all();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(p_full_r[b]);
+      }
+      // final: 1/l for the other CTA, LSE from here
+      const float inv_l = (l_run > 0.0f) ? 1.0f / l_run : 0.0f;
+      st_cluster_f32(alpha_remote + (2 * 128 + tid) * 4, inv_l);
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&m1->fin), 1));
+      if (tid < p.h) {
+        float v = -INFINITY;
+        if (l_run > 0.0f) {
+          const float l2 = m_run + log2f(l_run);
+          v = p.lse_base2 ? l2 : l2 * 0.6931471805599453f;
+        }
+        p.lse[static_cast<long long>(token) * p.lse_st + tid] = v;
+      }
+    } else if (warp == 4) {
+      // ---------------------------------------------------------------- Q.K^T issuer
+      if (lane == 0) {
+        constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, kNT, 0, 0);
+        for (int i = 0; i < n_tiles; ++i) {
+          const int b = i & 1;
+          if (i >= 2) mbar_wait(smem_u32(&m0->s_free[b]), ((i - 2) >> 1) & 1u, abort_flag);
+          tc_fence_after();
+#pragma unroll 1
+          for (int cc = 0; cc < kNChunk; ++cc) {
+            const int g = i * kNChunk + cc;
+            const int slot = g % kNK;
+            mbar_wait(smem_u32(&m0->k_full[slot]), (g / kNK) & 1u, abort_flag);
+            fence_proxy_async_smem();   // the copies were written through the generic proxy
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint64_t ad = smem_desc_sw128(q_s + cc * kQBlock + k * 32, 16, 1024);
+              const uint64_t bd = smem_desc_sw128(k_s + slot * kKSlot + k * 32, 16, 1024);
+              umma_f16_ss(tmem + b * 128, ad, bd, kIdesc, (cc | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&m0->k_free[slot]));
+          }
+          umma_commit(smem_u32(&m0->s_full[b]));
+        }
+      }
+    } else if (warp < 9) {
+      // ---------------------------------------------------------------- K producers (warps 5-8)
+      const int pt = tid - 160;   // 0..127: tile slot resolved by this thread
+      const int pw = warp - 5;    // rows pw*32 .. pw*32+31 of every block
+      int idx_next = (pt < p.topk) ? idx_row[pt] : -1;
+      int g = 0;
+      for (int i = 0; i < n_tiles; ++i) {
+        const int logical = idx_next;
+        {
+          const int jn = (i + 1) * kNT + pt;
+          idx_next = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+        }
+        const bool ok = logical >= 0 && logical < p.s_kv;
+        if (logical >= p.s_kv) m0->bad_index = 1;
+        const uint32_t m = __ballot_sync(0xffffffffu, ok);
+        if (lane == 0) m0->valid_mask[i & 3][pw] = m;
+        m0->rows[i & 1][pt] = ok ? logical : 0;
+        named_bar_sync(3, 128);
+        // this lane's 8 rows of every block: row = pw*32 + it*4 + lane/8, 16-byte chunk lane%8
+        const __nv_bfloat16* src[8];
+#pragma unroll
+        for (int it = 0; it < 8; ++it)
+          src[it] = p.kv + static_cast<long long>(m0->rows[i & 1][pw * 32 + it * 4 + (lane >> 3)]) * p.kv_sr + (lane & 7) * 8;
+#pragma unroll 1
+        for (int cc = 0; cc < kNChunk; ++cc, ++g) {
+          const int slot = g % kNK;
+          if (g >= kNK) mbar_wait(smem_u32(&m0->k_free[slot]), ((g / kNK) - 1) & 1u, abort_flag);
+          const uint32_t dslot = k_s + slot * kKSlot;
+#pragma unroll
+          for (int it = 0; it < 8; ++it) {
+            const int r = pw * 32 + it * 4 + (lane >> 3);
+            cp_async16(dslot + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src[it] + cc * 64);
+          }
+          // the barrier hears from this thread when the copies above have landed; the thread itself
+          // does not wait and goes on to the next ring slot
+          cp_async_mbar_arrive_noinc(smem_u32(&m0->k_full[slot]));
+        }
+      }
+      cp_async_wait_all();
+    }
+  } else {
+    // ======================================================================= CTA 1: values
+    const uint32_t v_s = base;
+    const uint32_t p_s = base + kOff1P;
+    if (warp < 4) {
+      // ---------------------------------------------------------------- correction + epilogue (thread = head)
+      for (int i = 0; i < n_tiles; ++i) {
+        const int b = i & 1;
+        mbar_wait(smem_u32(&m1->p_full[b]), (i >> 1) & 1u, abort_flag);
+        const float a = m1->alpha[b][tid];
+        const bool need = (i > 0) && (a != 1.0f);
+        if (__any_sync(0xffffffffu, need)) {
+          mbar_wait(smem_u32(&m1->pv_done[(i - 1) & 1]), ((i - 1) >> 1) & 1u, abort_flag);
+          tc_fence_after();
+#pragma unroll 1
+          for (int c0 = 0; c0 < 512; c0 += 32) {
+            uint32_t o[32];
+            tmem_ld32(tmem_addr(tmem, warp * 32, c0), o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * a);
+            tmem_st32(tmem_addr(tmem, warp * 32, c0), o);
+          }
+          tmem_wait_st();
+          tc_fence_before();
+        }
+        fence_proxy_async_all();     // P arrived through the generic proxy; the MMA reads it through the async proxy
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&m1->corr_done[b]));
+      }
+      if (n_tiles > 0) {
+        mbar_wait(smem_u32(&m1->pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1u, abort_flag);
+        tc_fence_after();
+      }
+      mbar_wait(smem_u32(&m1->fin), 0u, abort_flag);
+      const float inv_l = m1->alpha[2][tid];
+      __nv_bfloat16* orow = p.out + static_cast<long long>(token) * p.out_st + static_cast<long long>(tid) * p.out_sh;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 512; c0 += 32) {
+        uint32_t acc[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem_addr(tmem, warp * 32, c0), acc);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] = 0u;
+        }
+        if (tid < p.h) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l);
+            v.y = pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l);
+            v.z = pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l);
+            v.w = pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l);
+            *reinterpret_cast<uint4*>(orow + c0 + j) = v;
+          }
+        }
+      }
+      tc_fence_before();
+    } else if (warp == 4) {
+      // ---------------------------------------------------------------- P.V issuer
+      if (lane == 0) {
+        constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
+        for (int i = 0; i < n_tiles; ++i) {
+          const int b = i & 1;
+          mbar_wait(smem_u32(&m1->corr_done[b]), (i >> 1) & 1u, abort_flag);
+          tc_fence_after();
+#pragma unroll 1
+          for (int sl = 0; sl < kNT / kVSlabRows; ++sl) {
+            const int g = i * (kNT / kVSlabRows) + sl;
+            const int slot = g % kNV;
+            mbar_wait(smem_u32(&m1->v_full[slot]), (g / kNV) & 1u, abort_flag);
+            fence_proxy_async_smem();
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+              const int j = sl * 2 + kk;   // 16-row step inside the tile
+              const uint64_t ad = smem_desc_sw128(p_s + b * kPBuf + (j >> 2) * kQBlock + (j & 3) * 32, 16, 1024);
+#pragma unroll
+              for (int hv = 0; hv < 2; ++hv) {
+                const uint64_t bd = smem_desc_sw128(v_s + slot * kVSlab + hv * 4 * kVBlock + kk * 2048, kVBlock, 1024);
+                umma_f16_ss(tmem + hv * 256, ad, bd, kIdesc, (i | j) != 0 ? 1u : 0u);
+              }
+            }
+            umma_commit(smem_u32(&m1->v_free[slot]));
+          }
+          umma_commit(smem_u32(&m1->pv_done[b]));
+        }
+      }
+    } else if (warp == 5) {
+      // ---------------------------------------------------------------- relay: P buffer free -> CTA 0
+      if (lane == 0) {
+        const uint32_t p_free_r[2] = {mapa_shared(smem_u32(&m0->p_free[0]), 0), mapa_shared(smem_u32(&m0->p_free[1]), 0)};
+        for (int i = 0; i + 2 < n_tiles; ++i) {
+          mbar_wait(smem_u32(&m1->pv_done[i & 1]), (i >> 1) & 1u, abort_flag);
+          mbar_arrive_cluster(p_free_r[i & 1]);
+        }
+      }
+    } else {
+      // ---------------------------------------------------------------- V producers (warps 6-9)
+      const int pt = tid - 192;   // 0..127
+      const int pw = warp - 6;    // rows pw*8 .. pw*8+7 of every slab
+      int idx_next = (pt < p.topk) ? idx_row[pt] : -1;
+      int g = 0;
+      for (int i = 0; i < n_tiles; ++i) {
+        const int logical = idx_next;
+        {
+          const int jn = (i + 1) * kNT + pt;
+          idx_next = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+        }
+        m1->rows[i & 1][pt] = (logical >= 0 && logical < p.s_kv) ? logical : 0;
+        named_bar_sync(4, 128);
+#pragma unroll 1
+        for (int sl = 0; sl < kNT / kVSlabRows; ++sl, ++g) {
+          const int slot = g % kNV;
+          if (g >= kNV) mbar_wait(smem_u32(&m1->v_free[slot]), ((g / kNV) - 1) & 1u, abort_flag);
+          const uint32_t dslab = v_s + slot * kVSlab;
+#pragma unroll
+          for (int rr = 0; rr < 8; ++rr) {
+            const int r = pw * 8 + rr;           // row inside the slab
+            const __nv_bfloat16* src = p.kv + static_cast<long long>(m1->rows[i & 1][sl * kVSlabRows + r]) * p.kv_sr;
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              const int q = part * 32 + lane;     // 16-byte chunk of the 1024-byte V row
+              cp_async16(dslab + (q >> 3) * kVBlock + r * 128 + (((q & 7) ^ (r & 7)) << 4), src + q * 8);
+            }
+          }
+          cp_async_mbar_arrive_noinc(smem_u32(&m1->v_full[slot]));
+        }
+      }
+      cp_async_wait_all();
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // nobody leaves while the peer may still write or signal this CTA
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem, cta == 0 ? 256u : 512u);
+  }
+  if (tid == 0 && p.status != nullptr) {
+    if (*abort_flag) atomicCAS(p.status, 0, FTB_ERR_TIMEOUT);
+    else if (cta == 0 && m0->bad_index) atomicCAS(p.status, 0, FTB_ERR_BAD_INDEX);
+  }
+}
+
+}  // namespace mla3
+
+int launch_sparse_mla_duo(const ftb_sparse_mla_args* a, cudaStream_t st) {
+  mla3::Params p;
+  p.q = reinterpret_cast<const __nv_bfloat16*>(a->q);
+  p.kv = reinterpret_cast<const __nv_bfloat16*>(a->kv);
+  p.indices = a->indices;
+  p.out = reinterpret_cast<__nv_bfloat16*>(a->out);
+  p.lse = a->lse;
+  p.s_q = a->s_q; p.h = a->h; p.s_kv = a->s_kv; p.topk = a->topk;
+  p.q_st = a->q_stride_token; p.q_sh = a->q_stride_head; p.kv_sr = a->kv_stride_row;
+  p.idx_st = a->idx_stride_token; p.out_st = a->out_stride_token; p.out_sh = a->out_stride_head;
+  p.lse_st = a->lse_stride_token;
+  p.scale_log2 = a->sm_scale * 1.4426950408889634f;
+  p.lse_base2 = a->lse_base2;
+  p.status = a->status;
+  cudaError_t e = cudaFuncSetAttribute(mla3::sparse_mla_duo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla3::kSmemBytes);
+  if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla_duo)");
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(a->s_q) * 2u);
+  cfg.blockDim = dim3(mla3::kThreads);
+  cfg.dynamicSmemBytes = mla3::kSmemBytes;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, mla3::sparse_mla_duo_kernel, p);
+  return check_cuda(e, "sparse_mla_duo launch");
+}
+
+}  // namespace ftb
