@@ -339,7 +339,7 @@ def main():
                 prof_traffic = None
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "traffic": prof_traffic, "peak_source": f"bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json",
-                    "kernel": "sparse_mla_pair_kernel", "flops_per_launch": flops_rank, "avg_launch_ms": avg_launch_ms}
+                    "kernel": "sparse_mla_duo_kernel", "flops_per_launch": flops_rank, "avg_launch_ms": avg_launch_ms}
         cpu_b = None
         if not args.no_cpu_baseline:
             cpu_b = cpu_baseline_mla(args.cpu_tokens, reps=2)

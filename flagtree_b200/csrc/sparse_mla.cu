@@ -501,7 +501,7 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
   if (!a->kv_is_fp8 && a->dbg_scores == nullptr && a->n_splits <= 1) {
     if (a->algo_id == 2) return launch_sparse_mla_pair(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 3) return launch_sparse_mla_duo(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 0) return launch_sparse_mla_pair(a, reinterpret_cast<cudaStream_t>(stream));
+    if (a->algo_id == 0) return launch_sparse_mla_duo(a, reinterpret_cast<cudaStream_t>(stream));   // fastest so far
   }
   MlaParams p;
   memset(&p, 0, sizeof(p));
