@@ -209,7 +209,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--ref-tokens", type=int, default=512, help="query tokens per step of the CPU arm")
-    ap.add_argument("--cpu-tokens", type=int, default=2048, help="query tokens of the cpu_baseline sample")
+    ap.add_argument("--cpu-tokens", type=int, default=4096, help="query tokens of the cpu_baseline sample")
     ap.add_argument("--s-q", type=int, default=4096, help="query tokens per rank (default = full cfg2)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -342,7 +342,7 @@ def main():
                     "kernel": "sparse_mla_duo_kernel", "flops_per_launch": flops_rank, "avg_launch_ms": avg_launch_ms}
         cpu_b = None
         if not args.no_cpu_baseline:
-            cpu_b = cpu_baseline_mla(args.cpu_tokens, reps=2)
+            cpu_b = cpu_baseline_mla(args.cpu_tokens, reps=3)
             cpu_b.pop("seconds"); cpu_b.pop("flops")
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
