@@ -330,7 +330,7 @@ def main():
         achieved = flops_rank / (avg_launch_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops"]
         prof_traffic = None
-        tpath = os.path.join(ROOT, "profiles", "sparse_mla_traffic.json")
+        tpath = os.path.join(ROOT, "profiles", "sparse_mla_duo_kernel_cfg2_traffic.txt")   # figures of the ncu capture, JSON text
         if os.path.exists(tpath):
             try:
                 with open(tpath) as f:
