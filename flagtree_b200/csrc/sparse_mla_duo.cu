@@ -11,8 +11,10 @@
 // Nothing is computed twice and no accumulator is split; the price is that K and V are gathered
 // separately (1152 + 1024 bytes per selected row).
 //
-// Warps (320 threads per CTA): 0-3 softmax (CTA 0) / correction + epilogue (CTA 1), 4 MMA issuer,
-// 5-8 K producers (CTA 0), 5 relay + 6-9 V producers (CTA 1).  Every wait is bounded.
+// Warps (544 threads per CTA): CTA 0: 0-7 softmax (two threads per head row, 64 columns each), 8 MMA issuer,
+// 9-16 K producers.  CTA 1: 0-3 correction + epilogue, 4 relay, 8 MMA issuer, 9-16 V producers.  The gather
+// throughput of cp.async grows with the number of issuing warps (about 4.6 bytes per cycle per warp), hence
+// eight producer warps per CTA.  Every wait is bounded.
 #include "sm100.cuh"
 
 namespace ftb {
@@ -40,7 +42,8 @@ constexpr int kOff0Misc = kOff0K + kNK * kKSlot;           // 212992
 constexpr int kOff1P = kNV * kVSlab;                       // 131072
 constexpr int kOff1Misc = kOff1P + 2 * kPBuf;              // 196608
 constexpr int kSmemBytes = kOff0Misc + 4096 + 1024;        // the larger of the two + misc + alignment slack
-constexpr int kThreads = 320;
+constexpr int kThreads = 544;
+constexpr int kProducers = 256;                // producer threads per CTA (warps 9-16)
 
 struct Params {
   const __nv_bfloat16* q;
@@ -56,10 +59,10 @@ struct Params {
 };
 
 struct Misc0 {   // CTA 0
-  unsigned long long k_full[kNK];   // 128 producer threads, each when its own copies have landed
+  unsigned long long k_full[kNK];   // every producer thread, when its own copies have landed
   unsigned long long k_free[kNK];   // tcgen05.commit
   unsigned long long s_full[2];     // tcgen05.commit
-  unsigned long long s_free[2];     // 4 softmax warps
+  unsigned long long s_free[2];     // 8 softmax warps
   unsigned long long p_free[2];     // relay warp of CTA 1 (remote arrival)
   uint32_t tmem_base;
   int abort_flag;
@@ -67,14 +70,15 @@ struct Misc0 {   // CTA 0
   int bad_index;
   uint32_t valid_mask[4][4];        // per tile (mod 4): 128 validity bits
   int rows[2][kNT];
+  float xchg[2][256];               // row maximum / row sum exchange between the two threads of a head row
 };
 struct Misc1 {   // CTA 1
-  unsigned long long v_full[kNV];   // 128 producer threads, each when its own copies have landed
+  unsigned long long v_full[kNV];   // every producer thread, when its own copies have landed
   unsigned long long v_free[kNV];   // tcgen05.commit
-  unsigned long long p_full[2];     // 4 softmax warps of CTA 0 (remote arrivals)
+  unsigned long long p_full[2];     // 8 softmax warps of CTA 0 (remote arrivals)
   unsigned long long corr_done[2];  // 4 correction warps
   unsigned long long pv_done[2];    // tcgen05.commit
-  unsigned long long fin;           // 4 softmax warps of CTA 0: 1/l is in place
+  unsigned long long fin;           // 8 softmax warps of CTA 0: 1/l is in place
   uint32_t tmem_base;
   int abort_flag;
   int n_scan;
@@ -119,27 +123,27 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Param
     *n_scan_p = 0;
     if (cta == 0) {
       m0->bad_index = 0;
-      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), 128); mbar_init(smem_u32(&m0->k_free[i]), 1); }
+      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), kProducers); mbar_init(smem_u32(&m0->k_free[i]), 1); }
       for (int i = 0; i < 2; ++i) {
         mbar_init(smem_u32(&m0->s_full[i]), 1);
-        mbar_init(smem_u32(&m0->s_free[i]), 4);
+        mbar_init(smem_u32(&m0->s_free[i]), 8);
         mbar_init(smem_u32(&m0->p_free[i]), 1);
       }
     } else {
-      for (int i = 0; i < kNV; ++i) { mbar_init(smem_u32(&m1->v_full[i]), 128); mbar_init(smem_u32(&m1->v_free[i]), 1); }
+      for (int i = 0; i < kNV; ++i) { mbar_init(smem_u32(&m1->v_full[i]), kProducers); mbar_init(smem_u32(&m1->v_free[i]), 1); }
       for (int i = 0; i < 2; ++i) {
-        mbar_init(smem_u32(&m1->p_full[i]), 4);
+        mbar_init(smem_u32(&m1->p_full[i]), 8);
         mbar_init(smem_u32(&m1->corr_done[i]), 4);
         mbar_init(smem_u32(&m1->pv_done[i]), 1);
       }
-      mbar_init(smem_u32(&m1->fin), 4);
+      mbar_init(smem_u32(&m1->fin), 8);
     }
     fence_mbar_init();
   }
   __syncthreads();
   if (*abort_flag) return;   // an earlier launch failed: both CTAs read the same status word
 
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(smem_u32(tmem_base_p), cta == 0 ? 256u : 512u);
     tmem_relinquish();
     tc_fence_before();
@@ -176,41 +180,44 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Param
     // ======================================================================= CTA 0: scores
     const uint32_t q_s = base;
     const uint32_t k_s = base + kOff0K;
-    if (warp < 4) {
-      // ---------------------------------------------------------------- softmax (thread = head)
+    if (warp < 8) {
+      // ---------------------------------------------------------------- softmax (two threads per head row)
+      // thread tid: head row = tid % 128 (TMEM lane), columns 64*(tid/128) .. +63 of the tile.  Two passes
+      // over TMEM (maximum, then exponentials) keep the register count low.
+      const int rowi = tid & 127;
+      const int ch = tid >> 7;
       const uint32_t p_remote = mapa_shared(base + kOff1P, 1);
       const uint32_t alpha_remote = mapa_shared(smem_u32(&m1->alpha[0][0]), 1);
       const uint32_t p_full_r[2] = {mapa_shared(smem_u32(&m1->p_full[0]), 1), mapa_shared(smem_u32(&m1->p_full[1]), 1)};
+      const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
       float m_run = -INFINITY, l_run = 0.0f;
       for (int i = 0; i < n_tiles; ++i) {
         const int b = i & 1;
         mbar_wait(smem_u32(&m0->s_full[b]), (i >> 1) & 1u, abort_flag);
         tc_fence_after();
-        uint32_t sr[4][32];
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) tmem_ld32(tmem_addr(tmem, warp * 32, b * 128 + q4 * 32), sr[q4]);
-        tmem_wait_ld();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&m0->s_free[b]));
-        const uint32_t vm0 = m0->valid_mask[i & 3][0], vm1 = m0->valid_mask[i & 3][1];
-        const uint32_t vm2 = m0->valid_mask[i & 3][2], vm3 = m0->valid_mask[i & 3][3];
-        const bool all_valid = (vm0 & vm1 & vm2 & vm3) == 0xffffffffu;     // same for every thread of the CTA
+        const uint32_t vmA = m0->valid_mask[i & 3][2 * ch], vmB = m0->valid_mask[i & 3][2 * ch + 1];
+        const bool all_valid = (m0->valid_mask[i & 3][0] & m0->valid_mask[i & 3][1] & m0->valid_mask[i & 3][2] &
+                                m0->valid_mask[i & 3][3]) == 0xffffffffu;      // uniform over the CTA
+        const uint32_t t_s = tmem_addr(tmem, lane_base, b * 128 + ch * 64);
         float mx = -INFINITY;
-        if (all_valid) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4)
+        for (int q = 0; q < 2; ++q) {
+          uint32_t sr[32];
+          tmem_ld32(t_s + q * 32, sr);
+          tmem_wait_ld();
+          if (all_valid) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sr[q4][j]));
-        } else {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const uint32_t vm = q4 == 0 ? vm0 : q4 == 1 ? vm1 : q4 == 2 ? vm2 : vm3;
+            for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sr[j]));
+          } else {
+            const uint32_t vm = q == 0 ? vmA : vmB;
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if ((vm >> j) & 1u) mx = fmaxf(mx, __uint_as_float(sr[q4][j]));
+              if ((vm >> j) & 1u) mx = fmaxf(mx, __uint_as_float(sr[j]));
           }
         }
+        m0->xchg[b][tid] = mx;
+        named_bar_sync(2, 256);
+        mx = fmaxf(mx, m0->xchg[b][tid ^ 128]);
         // Lazy maximum: only move the reference when it grows by more than 2^8, so that the
         // accumulator in the other CTA is rarely rescaled (P stays below 256, exact enough in bf16/fp32).
         const float m_cand = fmaxf(m_run, mx * p.scale_log2);
@@ -220,60 +227,65 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Param
           m_run = m_cand;
         }
         const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
-        float psum = 0.0f;
-        uint32_t pk[64];
-        if (all_valid) {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float a0 = fast_exp2(fmaf(__uint_as_float(sr[q4][j]), p.scale_log2, -m_use));
-              const float a1 = fast_exp2(fmaf(__uint_as_float(sr[q4][j + 1]), p.scale_log2, -m_use));
-              psum += a0 + a1;
-              pk[q4 * 16 + (j >> 1)] = pack_bf16x2(a0, a1);
-            }
-          }
-        } else {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const uint32_t vm = q4 == 0 ? vm0 : q4 == 1 ? vm1 : q4 == 2 ? vm2 : vm3;
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float a0 = ((vm >> j) & 1u) ? fast_exp2(fmaf(__uint_as_float(sr[q4][j]), p.scale_log2, -m_use)) : 0.0f;
-              const float a1 = ((vm >> (j + 1)) & 1u) ? fast_exp2(fmaf(__uint_as_float(sr[q4][j + 1]), p.scale_log2, -m_use)) : 0.0f;
-              psum += a0 + a1;
-              pk[q4 * 16 + (j >> 1)] = pack_bf16x2(a0, a1);
-            }
-          }
-        }
-        l_run = l_run * alpha + psum;
         // P buffer b of CTA 1 was last read by P.V of tile i-2
         if (i >= 2) mbar_wait(smem_u32(&m0->p_free[b]), ((i - 2) >> 1) & 1u, abort_flag);
+        float psum = 0.0f;
+        // this thread's 64 columns are block `ch` of the P buffer: row rowi, eight 16-byte chunks
+        const uint32_t p_row = p_remote + b * kPBuf + ch * kQBlock + rowi * 128;
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          // 16-byte chunk c of the row: rows 8c..8c+7 of the tile; block c/8, position (c%8) ^ (head%8)
-          const uint32_t dst = p_remote + b * kPBuf + (c >> 3) * kQBlock + tid * 128 + (((c & 7) ^ (tid & 7)) << 4);
-          st_cluster_v4(dst, pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+        for (int q = 0; q < 2; ++q) {
+          uint32_t sr[32];
+          tmem_ld32(t_s + q * 32, sr);
+          tmem_wait_ld();
+          const uint32_t vm = all_valid ? 0xffffffffu : (q == 0 ? vmA : vmB);
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float a0 = fast_exp2(fmaf(__uint_as_float(sr[j]), p.scale_log2, -m_use));
+            float a1 = fast_exp2(fmaf(__uint_as_float(sr[j + 1]), p.scale_log2, -m_use));
+            if (!all_valid) {
+              a0 = ((vm >> j) & 1u) ? a0 : 0.0f;
+              a1 = ((vm >> (j + 1)) & 1u) ? a1 : 0.0f;
+            }
+            psum += a0 + a1;
+            pk[j >> 1] = pack_bf16x2(a0, a1);
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int chunk = q * 4 + c;
+            st_cluster_v4(p_row + ((chunk ^ (rowi & 7)) << 4), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          }
         }
-        st_cluster_f32(alpha_remote + (b * 128 + tid) * 4, alpha);
+        tc_fence_before();
+        l_run = l_run * alpha + psum;
+        if (ch == 0) st_cluster_f32(alpha_remote + (b * 128 + rowi) * 4, alpha);
         fence_proxy_async_all();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(p_full_r[b]);
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&m0->s_free[b]));      // both passes over S[b] are done
+          mbar_arrive_cluster(p_full_r[b]);
+        }
       }
-      // final: 1/l for the other CTA, LSE from here
-      const float inv_l = (l_run > 0.0f) ? 1.0f / l_run : 0.0f;
-      st_cluster_f32(alpha_remote + (2 * 128 + tid) * 4, inv_l);
+      // final: combine the two halves of every row sum; 1/l goes to the other CTA, LSE is written here
+      named_bar_sync(2, 256);
+      m0->xchg[0][tid] = l_run;
+      named_bar_sync(2, 256);
+      const float l_tot = l_run + m0->xchg[0][tid ^ 128];
+      if (ch == 0) {
+        const float inv_l = (l_tot > 0.0f) ? 1.0f / l_tot : 0.0f;
+        st_cluster_f32(alpha_remote + (2 * 128 + rowi) * 4, inv_l);
+        if (rowi < p.h) {
+          float v = -INFINITY;
+          if (l_tot > 0.0f) {
+            const float l2 = m_run + log2f(l_tot);
+            v = p.lse_base2 ? l2 : l2 * 0.6931471805599453f;
+          }
+          p.lse[static_cast<long long>(token) * p.lse_st + rowi] = v;
+        }
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&m1->fin), 1));
-      if (tid < p.h) {
-        float v = -INFINITY;
-        if (l_run > 0.0f) {
-          const float l2 = m_run + log2f(l_run);
-          v = p.lse_base2 ? l2 : l2 * 0.6931471805599453f;
-        }
-        p.lse[static_cast<long long>(token) * p.lse_st + tid] = v;
-      }
-    } else if (warp == 4) {
+    } else if (warp == 8) {
       // ---------------------------------------------------------------- Q.K^T issuer
       if (lane == 0) {
         constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, kNT, 0, 0);
@@ -281,55 +293,60 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Param
           const int b = i & 1;
           if (i >= 2) mbar_wait(smem_u32(&m0->s_free[b]), ((i - 2) >> 1) & 1u, abort_flag);
           tc_fence_after();
+          // Two column blocks per synchronisation: the per-block barrier wait, proxy fence and commit cost
+          // more issue time than the four 64-cycle MMAs of one block.
 #pragma unroll 1
-          for (int cc = 0; cc < kNChunk; ++cc) {
-            const int g = i * kNChunk + cc;
-            const int slot = g % kNK;
-            mbar_wait(smem_u32(&m0->k_full[slot]), (g / kNK) & 1u, abort_flag);
+          for (int cc = 0; cc < kNChunk; cc += 2) {
+            const int nb = (cc + 1 < kNChunk) ? 2 : 1;
+            const int g0 = i * kNChunk + cc;
+            for (int u = 0; u < nb; ++u) mbar_wait(smem_u32(&m0->k_full[(g0 + u) % kNK]), ((g0 + u) / kNK) & 1u, abort_flag);
             fence_proxy_async_smem();   // the copies were written through the generic proxy
             tc_fence_after();
+            for (int u = 0; u < nb; ++u) {
+              const int slot = (g0 + u) % kNK;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint64_t ad = smem_desc_sw128(q_s + cc * kQBlock + k * 32, 16, 1024);
-              const uint64_t bd = smem_desc_sw128(k_s + slot * kKSlot + k * 32, 16, 1024);
-              umma_f16_ss(tmem + b * 128, ad, bd, kIdesc, (cc | k) != 0 ? 1u : 0u);
+              for (int k = 0; k < 4; ++k) {
+                const uint64_t ad = smem_desc_sw128(q_s + (cc + u) * kQBlock + k * 32, 16, 1024);
+                const uint64_t bd = smem_desc_sw128(k_s + slot * kKSlot + k * 32, 16, 1024);
+                umma_f16_ss(tmem + b * 128, ad, bd, kIdesc, ((cc + u) | k) != 0 ? 1u : 0u);
+              }
+              umma_commit(smem_u32(&m0->k_free[slot]));
             }
-            umma_commit(smem_u32(&m0->k_free[slot]));
           }
           umma_commit(smem_u32(&m0->s_full[b]));
         }
       }
-    } else if (warp < 9) {
-      // ---------------------------------------------------------------- K producers (warps 5-8)
-      const int pt = tid - 160;   // 0..127: tile slot resolved by this thread
-      const int pw = warp - 5;    // rows pw*32 .. pw*32+31 of every block
-      int idx_next = (pt < p.topk) ? idx_row[pt] : -1;
+    } else {
+      // ---------------------------------------------------------------- K producers (warps 9-16)
+      const int pt = tid - 288;   // 0..255; the first 128 also resolve one tile slot each
+      const int pw = warp - 9;    // rows pw*16 .. pw*16+15 of every block
+      int idx_next = (pt < kNT && pt < p.topk) ? idx_row[pt] : -1;
       int g = 0;
       for (int i = 0; i < n_tiles; ++i) {
-        const int logical = idx_next;
-        {
+        if (pt < kNT) {
+          const int logical = idx_next;
           const int jn = (i + 1) * kNT + pt;
           idx_next = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+          const bool ok = logical >= 0 && logical < p.s_kv;
+          if (logical >= p.s_kv) m0->bad_index = 1;
+          const uint32_t m = __ballot_sync(0xffffffffu, ok);
+          if (lane == 0) m0->valid_mask[i & 3][pt >> 5] = m;
+          m0->rows[i & 1][pt] = ok ? logical : 0;
         }
-        const bool ok = logical >= 0 && logical < p.s_kv;
-        if (logical >= p.s_kv) m0->bad_index = 1;
-        const uint32_t m = __ballot_sync(0xffffffffu, ok);
-        if (lane == 0) m0->valid_mask[i & 3][pw] = m;
-        m0->rows[i & 1][pt] = ok ? logical : 0;
-        named_bar_sync(3, 128);
-        // this lane's 8 rows of every block: row = pw*32 + it*4 + lane/8, 16-byte chunk lane%8
-        const __nv_bfloat16* src[8];
+        named_bar_sync(3, kProducers);
+        // this lane's 4 rows of every block: row = pw*16 + it*4 + lane/8, 16-byte chunk lane%8
+        const __nv_bfloat16* src[4];
 #pragma unroll
-        for (int it = 0; it < 8; ++it)
-          src[it] = p.kv + static_cast<long long>(m0->rows[i & 1][pw * 32 + it * 4 + (lane >> 3)]) * p.kv_sr + (lane & 7) * 8;
+        for (int it = 0; it < 4; ++it)
+          src[it] = p.kv + static_cast<long long>(m0->rows[i & 1][pw * 16 + it * 4 + (lane >> 3)]) * p.kv_sr + (lane & 7) * 8;
 #pragma unroll 1
         for (int cc = 0; cc < kNChunk; ++cc, ++g) {
           const int slot = g % kNK;
           if (g >= kNK) mbar_wait(smem_u32(&m0->k_free[slot]), ((g / kNK) - 1) & 1u, abort_flag);
           const uint32_t dslot = k_s + slot * kKSlot;
 #pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int r = pw * 32 + it * 4 + (lane >> 3);
+          for (int it = 0; it < 4; ++it) {
+            const int r = pw * 16 + it * 4 + (lane >> 3);
             cp_async16(dslot + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src[it] + cc * 64);
           }
           // the barrier hears from this thread when the copies above have landed; the thread itself
@@ -399,7 +416,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Param
         }
       }
       tc_fence_before();
-    } else if (warp == 4) {
+    } else if (warp == 8) {
       // ---------------------------------------------------------------- P.V issuer
       if (lane == 0) {
         constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
@@ -429,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Param
           umma_commit(smem_u32(&m1->pv_done[b]));
         }
       }
-    } else if (warp == 5) {
+    } else if (warp == 4) {
       // ---------------------------------------------------------------- relay: P buffer free -> CTA 0
       if (lane == 0) {
         const uint32_t p_free_r[2] = {mapa_shared(smem_u32(&m0->p_free[0]), 0), mapa_shared(smem_u32(&m0->p_free[1]), 0)};
@@ -438,28 +455,28 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Param
           mbar_arrive_cluster(p_free_r[i & 1]);
         }
       }
-    } else {
-      // ---------------------------------------------------------------- V producers (warps 6-9)
-      const int pt = tid - 192;   // 0..127
-      const int pw = warp - 6;    // rows pw*8 .. pw*8+7 of every slab
-      int idx_next = (pt < p.topk) ? idx_row[pt] : -1;
+    } else if (warp >= 9) {
+      // ---------------------------------------------------------------- V producers (warps 9-16)
+      const int pt = tid - 288;   // 0..255
+      const int pw = warp - 9;    // rows pw*4 .. pw*4+3 of every slab
+      int idx_next = (pt < kNT && pt < p.topk) ? idx_row[pt] : -1;
       int g = 0;
       for (int i = 0; i < n_tiles; ++i) {
-        const int logical = idx_next;
-        {
+        if (pt < kNT) {
+          const int logical = idx_next;
           const int jn = (i + 1) * kNT + pt;
           idx_next = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+          m1->rows[i & 1][pt] = (logical >= 0 && logical < p.s_kv) ? logical : 0;
         }
-        m1->rows[i & 1][pt] = (logical >= 0 && logical < p.s_kv) ? logical : 0;
-        named_bar_sync(4, 128);
+        named_bar_sync(4, kProducers);
 #pragma unroll 1
         for (int sl = 0; sl < kNT / kVSlabRows; ++sl, ++g) {
           const int slot = g % kNV;
           if (g >= kNV) mbar_wait(smem_u32(&m1->v_free[slot]), ((g / kNV) - 1) & 1u, abort_flag);
           const uint32_t dslab = v_s + slot * kVSlab;
 #pragma unroll
-          for (int rr = 0; rr < 8; ++rr) {
-            const int r = pw * 8 + rr;           // row inside the slab
+          for (int rr = 0; rr < 4; ++rr) {
+            const int r = pw * 4 + rr;           // row inside the slab
             const __nv_bfloat16* src = p.kv + static_cast<long long>(m1->rows[i & 1][sl * kVSlabRows + r]) * p.kv_sr;
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
@@ -477,7 +494,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo_kernel(const Param
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();            // nobody leaves while the peer may still write or signal this CTA
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, cta == 0 ? 256u : 512u);
   }
