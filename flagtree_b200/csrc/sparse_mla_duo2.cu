@@ -3,14 +3,27 @@
 // Same division of labour as sparse_mla_duo.cu (CTA 0: S = Q.K^T + softmax, CTA 1: O += P.V, P sent over
 // distributed shared memory) with one change that matters for the K ring: Q [128 heads x 576] is not kept
 // in shared memory (147 KB) but in CTA 0's tensor memory (288 of 512 columns, two bf16 per 32-bit column)
-// and enters the MMA as the TMEM A operand.  That frees the shared memory for a 13-slot ring of K column
-// blocks (208 KB) instead of 4 slots, so the gather runs far ahead of the MMAs.  TMEM of CTA 0: Q in
-// columns 0-287, one S buffer [128 x 128] in columns 320-447 (the softmax copies S to registers at once,
-// so one buffer is enough).
+// and enters the MMA as the TMEM A operand.  That frees the shared memory for a 9-slot ring of K column
+// blocks (a whole tile in flight instead of 4 blocks: the refill latency of a slot, about 3000 cycles from
+// the commit that frees it to the landing of the new rows, no longer paces the MMAs) and for two local
+// staging buffers of P.  The softmax writes P into local shared memory (conflict-free 16-byte stores) and
+// each warp then sends its 4 KB with one bulk copy over distributed shared memory that completes on the
+// P barrier of CTA 1; 16-byte st.shared::cluster stores scattered over 32 rows per instruction took about
+// 6000 cycles per tile.  TMEM of CTA 0: Q in columns 0-287, one S buffer [128 x 128] in columns 320-447
+// (the softmax copies S to registers at once, so one buffer is enough).  The epilogue of CTA 1 runs on
+// eight warps, stages O in shared memory and leaves through bulk stores of 512-byte half rows.
 //
-// Warps (544 threads per CTA): CTA 0: 0-7 softmax (two threads per head row), 8 MMA issuer, 9-16 K producers.
-// CTA 1: 0-3 correction + epilogue, 4 relay, 8 MMA issuer, 9-16 V producers.  Every wait is bounded.
+// KV rows are fetched with TMA tile::gather4 (four row indices per instruction, boxes of 64 columns x 1 row,
+// 128B swizzle, never multicast), one producer warp per 64-column block and every lane issuing its own
+// gathers: one warp alone issues a gather every 67 cycles, nine warps together one every 12.  The copies
+// are writes of the async proxy, like the reads of the MMA, so the MMA issuer needs no proxy fence: with
+// cp.async producers that fence cost the issuer about 1300 cycles per pair of blocks while copies were in
+// flight, and the tensor pipe ran dry behind it.
+//
+// Warps (576 threads per CTA): CTA 0: 0-7 softmax (two threads per head row), 8 MMA issuer, 9-17 K producers.
+// CTA 1: 0-3 correction, 4 relay, 0-7 epilogue, 8 MMA issuer, 9-16 V producers.  Every wait is bounded.
 #include "sm100.cuh"
+#include "tmap.cuh"
 
 namespace ftb {
 
@@ -23,25 +36,25 @@ constexpr int kDqk = 576;
 constexpr int kNChunk = 9;
 constexpr int kNT = 128;                       // gathered rows per tile
 constexpr int kQBlock = 128 * 128;             // 16384: [128 heads x 128 B]
-constexpr int kQBytes = kNChunk * kQBlock;     // 147456
-constexpr int kNK = 13;                        // K ring slots (Q lives in TMEM)
+constexpr int kNK = 9;                         // K ring slots (Q lives in TMEM): one whole tile
 constexpr int kKSlot = kNT * 128;              // 16384: [128 rows x 128 B]
 constexpr int kNV = 4;                         // V ring slots
 constexpr int kVSlabRows = 32;
 constexpr int kVBlock = kVSlabRows * 128;      // 4096: one 64-column block of a slab
 constexpr int kVSlab = 8 * kVBlock;            // 32768
 constexpr int kPBuf = 2 * kQBlock;             // 32768: P [128 heads x 128 rows] bf16 as two 64-row blocks
-// CTA 0 layout: K ring | misc (Q is staged in ring slots 0-8 once, then moved to TMEM).
-// CTA 1 layout: V ring | P x 2 | misc.
+// CTA 0 layout: K ring | P staging x 2 | misc (Q is staged in ring slots 0-8 once, then moved to TMEM).
+// CTA 1 layout: V ring | P x 2 | misc; after the last tile the first 130 KB stage O [128 x (1024 + 16) B].
 constexpr int kOff0K = 0;
-constexpr int kOff0Misc = kOff0K + kNK * kKSlot;           // 212992
+constexpr int kOff0P = kOff0K + kNK * kKSlot;              // 147456
+constexpr int kOff0Misc = kOff0P + 2 * kPBuf;              // 212992
+constexpr int kORow = 1024 + 16;                           // padded O row: 16-byte stores of a warp spread over all banks
 constexpr int kOff1P = kNV * kVSlab;                       // 131072
 constexpr int kOff1Misc = kOff1P + 2 * kPBuf;              // 196608
 constexpr int kSmemBytes = kOff0Misc + 4096 + 1024;        // the larger of the two + misc + alignment slack
-constexpr int kThreads = 544;
+constexpr int kThreads = 576;
 constexpr uint32_t kColQ = 0;                  // TMEM columns of CTA 0: Q (288), then S
 constexpr uint32_t kColS = 320;
-constexpr int kProducers = 256;                // producer threads per CTA (warps 9-16)
 
 struct Params {
   const __nv_bfloat16* q;
@@ -57,7 +70,7 @@ struct Params {
 };
 
 struct Misc0 {   // CTA 0
-  unsigned long long k_full[kNK];   // every producer thread, when its own copies have landed
+  unsigned long long k_full[kNK];   // one arrival announcing 16 KB of gathers
   unsigned long long k_free[kNK];   // tcgen05.commit
   unsigned long long s_full[2];     // tcgen05.commit (index 0 used: one S buffer)
   unsigned long long s_free[2];     // 8 softmax warps (index 0 used)
@@ -67,13 +80,12 @@ struct Misc0 {   // CTA 0
   int n_scan;
   int bad_index;
   uint32_t valid_mask[4][4];        // per tile (mod 4): 128 validity bits
-  int rows[2][kNT];
   float xchg[2][256];               // row maximum / row sum exchange between the two threads of a head row
 };
 struct Misc1 {   // CTA 1
-  unsigned long long v_full[kNV];   // every producer thread, when its own copies have landed
+  unsigned long long v_full[kNV];   // one arrival announcing 32 KB of gathers
   unsigned long long v_free[kNV];   // tcgen05.commit
-  unsigned long long p_full[2];     // 8 softmax warps of CTA 0 (remote arrivals)
+  unsigned long long p_full[2];     // 8 softmax warps of CTA 0 (remote arrivals, each expecting its 4 KB bulk copy)
   unsigned long long corr_done[2];  // 4 correction warps
   unsigned long long pv_done[2];    // tcgen05.commit
   unsigned long long fin;           // 8 softmax warps of CTA 0: 1/l is in place
@@ -82,26 +94,46 @@ struct Misc1 {   // CTA 1
   int n_scan;
   int pad;
   float alpha[3][128];              // rescale factor of the tile (two buffers) and the final 1/l
-  int rows[2][kNT];
 };
 static_assert(sizeof(Misc0) <= 4096 && sizeof(Misc1) <= 4096, "misc area");
 static_assert(kOff1Misc + 4096 + 1024 <= kSmemBytes, "CTA 1 layout fits");
+static_assert(128 * kORow <= kOff1Misc, "O staging fits below the misc area of CTA 1");
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
-__device__ __forceinline__ void cp_async_wait2() { asm volatile("cp.async.wait_group 2;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait0() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+// Four rows (indices r0..r3) x 64 columns starting at column `col` -> 512 contiguous bytes of shared memory.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, uint32_t bar, int col, int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
 __device__ __forceinline__ void st_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// remote arrival that also announces `bytes` of bulk-copy traffic to the barrier of another CTA of the cluster
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
+}
+// bulk copy local shared memory -> shared memory of another CTA; completes (byte count) on that CTA's barrier
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void bulk_store_global(void* dst, uint32_t src_cta, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_cta), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 
-__global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const Params p) {
+__global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const __grid_constant__ CUtensorMap tm_kv, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -121,14 +153,14 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const Para
     *n_scan_p = 0;
     if (cta == 0) {
       m0->bad_index = 0;
-      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), kProducers); mbar_init(smem_u32(&m0->k_free[i]), 1); }
+      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), 1); mbar_init(smem_u32(&m0->k_free[i]), 1); }
       for (int i = 0; i < 2; ++i) {
         mbar_init(smem_u32(&m0->s_full[i]), 1);
         mbar_init(smem_u32(&m0->s_free[i]), 8);
         mbar_init(smem_u32(&m0->p_free[i]), 1);
       }
     } else {
-      for (int i = 0; i < kNV; ++i) { mbar_init(smem_u32(&m1->v_full[i]), kProducers); mbar_init(smem_u32(&m1->v_free[i]), 1); }
+      for (int i = 0; i < kNV; ++i) { mbar_init(smem_u32(&m1->v_full[i]), 1); mbar_init(smem_u32(&m1->v_free[i]), 1); }
       for (int i = 0; i < 2; ++i) {
         mbar_init(smem_u32(&m1->p_full[i]), 8);
         mbar_init(smem_u32(&m1->corr_done[i]), 4);
@@ -167,6 +199,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const Para
     }
     cp_async_commit();
     cp_async_wait_all();
+    fence_proxy_async_smem();   // these generic-proxy writes precede TMA writes to the same slots
   }
   __syncthreads();
   tc_fence_after();
@@ -186,6 +219,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const Para
     }
     tmem_wait_st();
     tc_fence_before();
+    fence_proxy_async_smem();   // the ring slots read above are next written by TMA (async proxy)
   }
   __syncthreads();
   cluster_sync_all();
@@ -203,6 +237,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const Para
       const int rowi = tid & 127;
       const int ch = tid >> 7;
       const uint32_t p_remote = mapa_shared(base + kOff1P, 1);
+      const uint32_t p_local = base + kOff0P;
       const uint32_t alpha_remote = mapa_shared(smem_u32(&m1->alpha[0][0]), 1);
       const uint32_t p_full_r[2] = {mapa_shared(smem_u32(&m1->p_full[0]), 1), mapa_shared(smem_u32(&m1->p_full[1]), 1)};
       const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32);
@@ -251,8 +286,9 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const Para
         // P buffer b of CTA 1 was last read by P.V of tile i-2
         if (i >= 2) mbar_wait(smem_u32(&m0->p_free[b]), ((i - 2) >> 1) & 1u, abort_flag);
         float psum = 0.0f;
-        // this thread's 64 columns are block `ch` of the P buffer: row rowi, eight 16-byte chunks
-        const uint32_t p_row = p_remote + b * kPBuf + ch * kQBlock + rowi * 128;
+        // this thread's 64 columns are block `ch` of the P buffer: row rowi, eight 16-byte chunks.  The
+        // staging buffer b was last sent for tile i-2, whose P.V (awaited above) came after its arrival.
+        const uint32_t p_row = p_local + b * kPBuf + ch * kQBlock + rowi * 128;
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           const uint32_t vm = all_valid ? 0xffffffffu : (q == 0 ? vmA : vmB);
@@ -271,15 +307,19 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const Para
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int chunk = q * 4 + c;
-            st_cluster_v4(p_row + ((chunk ^ (rowi & 7)) << 4), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+            st_shared_v4(p_row + ((chunk ^ (rowi & 7)) << 4), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
           }
         }
-        tc_fence_before();
         l_run = l_run * alpha + psum;
         if (ch == 0) st_cluster_f32(alpha_remote + (b * 128 + rowi) * 4, alpha);
-        fence_proxy_async_all();
+        fence_proxy_async_smem();   // the bulk copy reads this warp's rows through the async proxy
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(p_full_r[b]);
+        if (lane == 0) {
+          // this warp's 32 rows of block ch are 4 KB in a row, here and in CTA 1
+          const uint32_t off = b * kPBuf + ch * kQBlock + lane_base * 128;
+          mbar_arrive_expect_tx_cluster(p_full_r[b], 32 * 128);
+          bulk_copy_to_cluster(p_remote + off, p_local + off, 32 * 128, p_full_r[b]);
+        }
       }
       // final: combine the two halves of every row sum; 1/l goes to the other CTA, LSE is written here
       named_bar_sync(2, 256);
@@ -302,207 +342,223 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const Para
       if (lane == 0) mbar_arrive_cluster(mapa_shared(smem_u32(&m1->fin), 1));
     } else if (warp == 8) {
       // ---------------------------------------------------------------- Q.K^T issuer
+      // Straight-line code per tile (the ring holds exactly one tile, so block c always sits in slot c):
+      // the descriptors differ in their low word only and every offset is a compile-time constant.
+      static_assert(kNK == kNChunk, "slot index = column block index");
       if (lane == 0) {
         constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, kNT, 0, 0);
+        const uint64_t bd0 = smem_desc_sw128(k_s, 16, 1024);
+        const uint32_t bd_lo = static_cast<uint32_t>(bd0), bd_hi = static_cast<uint32_t>(bd0 >> 32);
+        const uint32_t t_s = tmem + kColS, t_q = tmem + kColQ;
+        const uint32_t k_full0 = smem_u32(&m0->k_full[0]), k_free0 = smem_u32(&m0->k_free[0]);
+        const uint32_t s_full = smem_u32(&m0->s_full[0]), s_free = smem_u32(&m0->s_free[0]);
         for (int i = 0; i < n_tiles; ++i) {
-          const int b = i & 1;
+          const uint32_t ph = i & 1u;
           // the single S buffer: the softmax of tile i-1 has copied it to registers
-          if (i >= 1) mbar_wait(smem_u32(&m0->s_free[0]), (i - 1) & 1u, abort_flag);
-          tc_fence_after();
-          // Two column blocks per synchronisation: the per-block barrier wait, proxy fence and commit cost
-          // more issue time than the four 64-cycle MMAs of one block.
-#pragma unroll 1
-          for (int cc = 0; cc < kNChunk; cc += 2) {
-            const int nb = (cc + 1 < kNChunk) ? 2 : 1;
-            const int g0 = i * kNChunk + cc;
-            for (int u = 0; u < nb; ++u) mbar_wait(smem_u32(&m0->k_full[(g0 + u) % kNK]), ((g0 + u) / kNK) & 1u, abort_flag);
-            fence_proxy_async_smem();   // the copies were written through the generic proxy
-            tc_fence_after();
-            for (int u = 0; u < nb; ++u) {
-              const int slot = (g0 + u) % kNK;
+          if (i >= 1) mbar_wait(s_free, ph ^ 1u, abort_flag);
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                const uint64_t bd = smem_desc_sw128(k_s + slot * kKSlot + k * 32, 16, 1024);
-                umma_f16_ts(tmem + kColS, tmem + kColQ + (cc + u) * 32 + k * 8, bd, kIdesc, ((cc + u) | k) != 0 ? 1u : 0u);
-              }
-              umma_commit(smem_u32(&m0->k_free[slot]));
+          for (int cc = 0; cc < kNChunk; ++cc) {
+            mbar_wait(k_full0 + cc * 8, ph, abort_flag);
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t lo = bd_lo + ((cc * kKSlot + k * 32) >> 4);
+              if (cc == 0 && k == 0) umma_f16_ts_lohi<false>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+              else umma_f16_ts_lohi<true>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
             }
+            umma_commit(k_free0 + cc * 8);
           }
-          umma_commit(smem_u32(&m0->s_full[0]));
+          umma_commit(s_full);
         }
       }
     } else {
-      // ---------------------------------------------------------------- K producers (warps 9-16)
-      const int pt = tid - 288;   // 0..255; the first 128 also resolve one tile slot each
-      const int pw = warp - 9;    // rows pw*16 .. pw*16+15 of every block
-      int idx_next = (pt < kNT && pt < p.topk) ? idx_row[pt] : -1;
-      int g = 0;
+      // ---------------------------------------------------------------- K producers (warps 9-17)
+      // warp 9+c fetches 64-column block c of every tile; lane l owns tile rows 4l..4l+3 (one gather4).
+      const int c = warp - 9;
+      int nxt[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) nxt[j] = (4 * lane + j < p.topk) ? idx_row[4 * lane + j] : -1;
       for (int i = 0; i < n_tiles; ++i) {
-        if (pt < kNT) {
-          const int logical = idx_next;
-          const int jn = (i + 1) * kNT + pt;
-          idx_next = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
-          const bool ok = logical >= 0 && logical < p.s_kv;
-          if (logical >= p.s_kv) m0->bad_index = 1;
-          const uint32_t m = __ballot_sync(0xffffffffu, ok);
-          if (lane == 0) m0->valid_mask[i & 3][pt >> 5] = m;
-          m0->rows[i & 1][pt] = ok ? logical : 0;
-        }
-        named_bar_sync(3, kProducers);
-        // this lane's 4 rows of every block: row = pw*16 + it*4 + lane/8, 16-byte chunk lane%8
-        const __nv_bfloat16* src[4];
+        int row[4];
+        uint32_t nib = 0;
 #pragma unroll
-        for (int it = 0; it < 4; ++it)
-          src[it] = p.kv + static_cast<long long>(m0->rows[i & 1][pw * 16 + it * 4 + (lane >> 3)]) * p.kv_sr + (lane & 7) * 8;
-#pragma unroll 1
-        for (int cc = 0; cc < kNChunk; ++cc, ++g) {
-          const int slot = g % kNK;
-          if (g >= kNK) mbar_wait(smem_u32(&m0->k_free[slot]), ((g / kNK) - 1) & 1u, abort_flag);
-          const uint32_t dslot = k_s + slot * kKSlot;
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int r = pw * 16 + it * 4 + (lane >> 3);
-            cp_async16(dslot + r * 128 + (((lane & 7) ^ (r & 7)) << 4), src[it] + cc * 64);
-          }
-          // the barrier hears from this thread when the copies above have landed; the thread itself
-          // does not wait and goes on to the next ring slot
-          cp_async_mbar_arrive_noinc(smem_u32(&m0->k_full[slot]));
+        for (int j = 0; j < 4; ++j) {
+          const bool ok = nxt[j] >= 0 && nxt[j] < p.s_kv;
+          if (c == 0 && nxt[j] >= p.s_kv) m0->bad_index = 1;
+          row[j] = ok ? nxt[j] : 0;
+          nib |= ok ? (1u << j) : 0u;
         }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int jn = (i + 1) * kNT + 4 * lane + j;
+          nxt[j] = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+        }
+        if (c == 0) {
+          // 128 validity bits of the tile: word w = rows 32w..32w+31 = lanes 8w..8w+7, four bits each
+          uint32_t v = nib << ((lane & 7) * 4);
+          v |= __shfl_xor_sync(0xffffffffu, v, 1);
+          v |= __shfl_xor_sync(0xffffffffu, v, 2);
+          v |= __shfl_xor_sync(0xffffffffu, v, 4);
+          if ((lane & 7) == 0) m0->valid_mask[i & 3][lane >> 3] = v;
+        }
+        const int g = i * kNChunk + c;
+        const int slot = g % kNK;
+        if (g >= kNK) mbar_wait(smem_u32(&m0->k_free[slot]), ((g / kNK) - 1) & 1u, abort_flag);
+        const uint32_t full = smem_u32(&m0->k_full[slot]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive_expect_tx(full, kKSlot);
+        __syncwarp();
+        tma_gather4(k_s + slot * kKSlot + lane * 512, &tm_kv, full, c * 64, row[0], row[1], row[2], row[3]);
       }
-      cp_async_wait_all();
     }
   } else {
     // ======================================================================= CTA 1: values
     const uint32_t v_s = base;
     const uint32_t p_s = base + kOff1P;
-    if (warp < 4) {
-      // ---------------------------------------------------------------- correction + epilogue (thread = head)
-      for (int i = 0; i < n_tiles; ++i) {
-        const int b = i & 1;
-        mbar_wait(smem_u32(&m1->p_full[b]), (i >> 1) & 1u, abort_flag);
-        const float a = m1->alpha[b][tid];
-        const bool need = (i > 0) && (a != 1.0f);
-        if (__any_sync(0xffffffffu, need)) {
-          mbar_wait(smem_u32(&m1->pv_done[(i - 1) & 1]), ((i - 1) >> 1) & 1u, abort_flag);
-          tc_fence_after();
-#pragma unroll 1
-          for (int c0 = 0; c0 < 512; c0 += 32) {
-            uint32_t o[32];
-            tmem_ld32(tmem_addr(tmem, warp * 32, c0), o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * a);
-            tmem_st32(tmem_addr(tmem, warp * 32, c0), o);
-          }
-          tmem_wait_st();
-          tc_fence_before();
-        }
-        fence_proxy_async_all();     // P arrived through the generic proxy; the MMA reads it through the async proxy
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&m1->corr_done[b]));
-      }
-      if (n_tiles > 0) {
-        mbar_wait(smem_u32(&m1->pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1u, abort_flag);
-        tc_fence_after();
-      }
-      mbar_wait(smem_u32(&m1->fin), 0u, abort_flag);
-      const float inv_l = m1->alpha[2][tid];
-      __nv_bfloat16* orow = p.out + static_cast<long long>(token) * p.out_st + static_cast<long long>(tid) * p.out_sh;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 512; c0 += 32) {
-        uint32_t acc[32];
-        if (n_tiles > 0) {
-          tmem_ld32(tmem_addr(tmem, warp * 32, c0), acc);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[j] = 0u;
-        }
-        if (tid < p.h) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l);
-            v.y = pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l);
-            v.z = pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l);
-            v.w = pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l);
-            *reinterpret_cast<uint4*>(orow + c0 + j) = v;
-          }
-        }
-      }
-      tc_fence_before();
-    } else if (warp == 8) {
-      // ---------------------------------------------------------------- P.V issuer
-      if (lane == 0) {
-        constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
+    if (warp < 8) {
+      if (warp < 4) {
+        // -------------------------------------------------------------- correction (thread = head)
         for (int i = 0; i < n_tiles; ++i) {
           const int b = i & 1;
-          mbar_wait(smem_u32(&m1->corr_done[b]), (i >> 1) & 1u, abort_flag);
-          tc_fence_after();
-#pragma unroll 1
-          for (int sl = 0; sl < kNT / kVSlabRows; ++sl) {
-            const int g = i * (kNT / kVSlabRows) + sl;
-            const int slot = g % kNV;
-            mbar_wait(smem_u32(&m1->v_full[slot]), (g / kNV) & 1u, abort_flag);
-            fence_proxy_async_smem();
+          mbar_wait(smem_u32(&m1->p_full[b]), (i >> 1) & 1u, abort_flag);
+          const float a = m1->alpha[b][tid];
+          const bool need = (i > 0) && (a != 1.0f);
+          if (__any_sync(0xffffffffu, need)) {
+            mbar_wait(smem_u32(&m1->pv_done[(i - 1) & 1]), ((i - 1) >> 1) & 1u, abort_flag);
             tc_fence_after();
+#pragma unroll 1
+            for (int c0 = 0; c0 < 512; c0 += 32) {
+              uint32_t o[32];
+              tmem_ld32(tmem_addr(tmem, warp * 32, c0), o);
+              tmem_wait_ld();
 #pragma unroll
-            for (int kk = 0; kk < 2; ++kk) {
-              const int j = sl * 2 + kk;   // 16-row step inside the tile
-              const uint64_t ad = smem_desc_sw128(p_s + b * kPBuf + (j >> 2) * kQBlock + (j & 3) * 32, 16, 1024);
-#pragma unroll
-              for (int hv = 0; hv < 2; ++hv) {
-                const uint64_t bd = smem_desc_sw128(v_s + slot * kVSlab + hv * 4 * kVBlock + kk * 2048, kVBlock, 1024);
-                umma_f16_ss(tmem + hv * 256, ad, bd, kIdesc, (i | j) != 0 ? 1u : 0u);
-              }
+              for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * a);
+              tmem_st32(tmem_addr(tmem, warp * 32, c0), o);
             }
-            umma_commit(smem_u32(&m1->v_free[slot]));
+            tmem_wait_st();
+            tc_fence_before();
           }
-          umma_commit(smem_u32(&m1->pv_done[b]));
+          // P arrived through the async proxy (bulk copy), which is also how the MMA reads it: no proxy fence
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&m1->corr_done[b]));
         }
-      }
-    } else if (warp == 4) {
-      // ---------------------------------------------------------------- relay: P buffer free -> CTA 0
-      if (lane == 0) {
+      } else if (warp == 4 && lane == 0) {
+        // -------------------------------------------------------------- relay: P buffer free -> CTA 0
         const uint32_t p_free_r[2] = {mapa_shared(smem_u32(&m0->p_free[0]), 0), mapa_shared(smem_u32(&m0->p_free[1]), 0)};
         for (int i = 0; i + 2 < n_tiles; ++i) {
           mbar_wait(smem_u32(&m1->pv_done[i & 1]), (i >> 1) & 1u, abort_flag);
           mbar_arrive_cluster(p_free_r[i & 1]);
         }
       }
-    } else if (warp >= 9) {
-      // ---------------------------------------------------------------- V producers (warps 9-16)
-      const int pt = tid - 288;   // 0..255
-      const int pw = warp - 9;    // rows pw*4 .. pw*4+3 of every slab
-      int idx_next = (pt < kNT && pt < p.topk) ? idx_row[pt] : -1;
-      int g = 0;
-      for (int i = 0; i < n_tiles; ++i) {
-        if (pt < kNT) {
-          const int logical = idx_next;
-          const int jn = (i + 1) * kNT + pt;
-          idx_next = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
-          m1->rows[i & 1][pt] = (logical >= 0 && logical < p.s_kv) ? logical : 0;
-        }
-        named_bar_sync(4, kProducers);
+      __syncwarp();
+      // ---------------------------------------------------------------- epilogue (8 warps)
+      // warp w: head rows 32*(w%4) .. +31 (its TMEM lanes), output columns 256*(w/4) .. +255.  The V ring
+      // and the P buffers are idle once the last P.V has completed; O is staged there as bf16 rows of
+      // 1024 + 16 bytes and each thread sends its 512-byte half row with one bulk store.
+      // `fin` first: warps 4-7 arrive here before the first tile, and a parity wait is only exact once the
+      // barrier is in, or past, the phase waited for (after `fin` the P.V of tile n-3 has completed)
+      mbar_wait(smem_u32(&m1->fin), 0u, abort_flag);
+      if (n_tiles > 0) {
+        mbar_wait(smem_u32(&m1->pv_done[(n_tiles - 1) & 1]), ((n_tiles - 1) >> 1) & 1u, abort_flag);
+        tc_fence_after();
+      }
+      const int row = (warp & 3) * 32 + lane;
+      const int half = warp >> 2;
+      const float inv_l = m1->alpha[2][row];
+      const uint32_t o_row = base + row * kORow + half * 512;
 #pragma unroll 1
-        for (int sl = 0; sl < kNT / kVSlabRows; ++sl, ++g) {
-          const int slot = g % kNV;
-          if (g >= kNV) mbar_wait(smem_u32(&m1->v_free[slot]), ((g / kNV) - 1) & 1u, abort_flag);
-          const uint32_t dslab = v_s + slot * kVSlab;
+      for (int c0 = 0; c0 < 256; c0 += 32) {
+        uint32_t acc[32];
+        if (n_tiles > 0) {
+          tmem_ld32(tmem_addr(tmem, (warp & 3) * 32, half * 256 + c0), acc);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-          for (int rr = 0; rr < 4; ++rr) {
-            const int r = pw * 4 + rr;           // row inside the slab
-            const __nv_bfloat16* src = p.kv + static_cast<long long>(m1->rows[i & 1][sl * kVSlabRows + r]) * p.kv_sr;
+          for (int j = 0; j < 32; ++j) acc[j] = 0u;
+        }
 #pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              const int q = part * 32 + lane;     // 16-byte chunk of the 1024-byte V row
-              cp_async16(dslab + (q >> 3) * kVBlock + r * 128 + (((q & 7) ^ (r & 7)) << 4), src + q * 8);
+        for (int j = 0; j < 32; j += 8)
+          st_shared_v4(o_row + (c0 + j) * 2,
+                       pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l),
+                       pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l),
+                       pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l),
+                       pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l));
+      }
+      fence_proxy_async_smem();   // the bulk store reads this thread's own half row through the async proxy
+      if (row < p.h) {
+        __nv_bfloat16* orow = p.out + static_cast<long long>(token) * p.out_st + static_cast<long long>(row) * p.out_sh + half * 256;
+        bulk_store_global(orow, o_row, 512);
+      }
+      bulk_commit();
+      bulk_wait_all();
+      tc_fence_before();
+    } else if (warp == 8) {
+      // ---------------------------------------------------------------- P.V issuer
+      static_assert(kNV == kNT / kVSlabRows, "slab index = ring slot index");
+      if (lane == 0) {
+        constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
+        const uint64_t ad0 = smem_desc_sw128(p_s, 16, 1024);
+        const uint64_t bd0 = smem_desc_sw128(v_s, kVBlock, 1024);
+        const uint32_t ad_lo = static_cast<uint32_t>(ad0), ad_hi = static_cast<uint32_t>(ad0 >> 32);
+        const uint32_t bd_lo = static_cast<uint32_t>(bd0), bd_hi = static_cast<uint32_t>(bd0 >> 32);
+        const uint32_t v_full0 = smem_u32(&m1->v_full[0]), v_free0 = smem_u32(&m1->v_free[0]);
+        for (int i = 0; i < n_tiles; ++i) {
+          const int b = i & 1;
+          const uint32_t ph = i & 1u;
+          mbar_wait(smem_u32(&m1->corr_done[b]), (i >> 1) & 1u, abort_flag);
+          tc_fence_after();
+          const uint32_t a_lo = ad_lo + ((b * kPBuf) >> 4);
+#pragma unroll
+          for (int sl = 0; sl < kNV; ++sl) {
+            mbar_wait(v_full0 + sl * 8, ph, abort_flag);
+            tc_fence_after();
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+              const int j = sl * 2 + kk;   // 16-row step inside the tile
+              const uint32_t alo = a_lo + (((j >> 2) * kQBlock + (j & 3) * 32) >> 4);
+#pragma unroll
+              for (int hv = 0; hv < 2; ++hv) {
+                const uint32_t blo = bd_lo + ((sl * kVSlab + hv * 4 * kVBlock + kk * 2048) >> 4);
+                if (j == 0) {
+                  if (i == 0) umma_f16_ss_lohi<false>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                  else umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                } else {
+                  umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                }
+              }
             }
+            umma_commit(v_free0 + sl * 8);
           }
-          cp_async_mbar_arrive_noinc(smem_u32(&m1->v_full[slot]));
+          umma_commit(smem_u32(&m1->pv_done[b]));
         }
       }
-      cp_async_wait_all();
+    } else if (warp >= 9 && warp < 17) {
+      // ---------------------------------------------------------------- V producers (warps 9-16)
+      // warp 9+w fetches 64-column block w of the 512 value columns; lane l owns tile rows 4l..4l+3, which
+      // are rows 4(l%8).. of slab l/8.
+      const int w = warp - 9;
+      const int sl = lane >> 3;
+      int nxt[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) nxt[j] = (4 * lane + j < p.topk) ? idx_row[4 * lane + j] : -1;
+      for (int i = 0; i < n_tiles; ++i) {
+        int row[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) row[j] = (nxt[j] >= 0 && nxt[j] < p.s_kv) ? nxt[j] : 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int jn = (i + 1) * kNT + 4 * lane + j;
+          nxt[j] = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+        }
+        const int g = i * (kNT / kVSlabRows) + sl;
+        const int slot = g % kNV;
+        if (g >= kNV) mbar_wait(smem_u32(&m1->v_free[slot]), ((g / kNV) - 1) & 1u, abort_flag);
+        const uint32_t full = smem_u32(&m1->v_full[slot]);
+        // one arrival per slab announces all 64 gathers of the eight warps (the byte count may run
+        // ahead of the announcement: the phase cannot complete before this arrival)
+        if (w == 0 && (lane & 7) == 0) mbar_arrive_expect_tx(full, kVSlab);
+        tma_gather4(v_s + slot * kVSlab + w * kVBlock + (lane & 7) * 512, &tm_kv, full, w * 64, row[0], row[1], row[2], row[3]);
+      }
     }
   }
 
@@ -535,6 +591,13 @@ int launch_sparse_mla_duo2(const ftb_sparse_mla_args* a, cudaStream_t st) {
   p.scale_log2 = a->sm_scale * 1.4426950408889634f;
   p.lse_base2 = a->lse_base2;
   p.status = a->status;
+  // box = 64 columns x 1 row: tile::gather4 fetches four such rows per instruction
+  CUtensorMap tm_kv;
+  if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla4::kDqk,
+                    static_cast<uint64_t>(a->kv_stride_row), 1, 64)) {
+    set_last_error("sparse_mla_duo2: cuTensorMapEncodeTiled failed");
+    return FTB_ERR_CUDA;
+  }
   cudaError_t e = cudaFuncSetAttribute(mla4::sparse_mla_duo2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla4::kSmemBytes);
   if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla_duo)");
   cudaLaunchConfig_t cfg = {};
@@ -547,7 +610,7 @@ int launch_sparse_mla_duo2(const ftb_sparse_mla_args* a, cudaStream_t st) {
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, mla4::sparse_mla_duo2_kernel, p);
+  e = cudaLaunchKernelEx(&cfg, mla4::sparse_mla_duo2_kernel, tm_kv, p);
   return check_cuda(e, "sparse_mla_duo launch");
 }
 
