@@ -10,8 +10,9 @@
 // each warp then sends its 4 KB with one bulk copy over distributed shared memory that completes on the
 // P barrier of CTA 1; 16-byte st.shared::cluster stores scattered over 32 rows per instruction took about
 // 6000 cycles per tile.  TMEM of CTA 0: Q in columns 0-287, one S buffer [128 x 128] in columns 320-447
-// (the softmax copies S to registers at once, so one buffer is enough).  The epilogue of CTA 1 runs on
-// eight warps, stages O in shared memory and leaves through bulk stores of 512-byte half rows.
+// (the softmax copies S to registers at once, so one buffer is enough).  Q arrives by nine TMA tile loads;
+// the epilogue of CTA 1 runs on eight warps, stages O in shared memory in the swizzled tile layout and
+// leaves through eight TMA tile stores (256 bulk stores of half rows took 6000 cycles to issue).
 //
 // KV rows are fetched with TMA tile::gather4 (four row indices per instruction, boxes of 64 columns x 1 row,
 // 128B swizzle, never multicast), one producer warp per 64-column block and every lane issuing its own
@@ -44,11 +45,10 @@ constexpr int kVBlock = kVSlabRows * 128;      // 4096: one 64-column block of a
 constexpr int kVSlab = 8 * kVBlock;            // 32768
 constexpr int kPBuf = 2 * kQBlock;             // 32768: P [128 heads x 128 rows] bf16 as two 64-row blocks
 // CTA 0 layout: K ring | P staging x 2 | misc (Q is staged in ring slots 0-8 once, then moved to TMEM).
-// CTA 1 layout: V ring | P x 2 | misc; after the last tile the first 130 KB stage O [128 x (1024 + 16) B].
+// CTA 1 layout: V ring | P x 2 | misc; after the last tile the V ring stages O as eight 64-column blocks.
 constexpr int kOff0K = 0;
 constexpr int kOff0P = kOff0K + kNK * kKSlot;              // 147456
 constexpr int kOff0Misc = kOff0P + 2 * kPBuf;              // 212992
-constexpr int kORow = 1024 + 16;                           // padded O row: 16-byte stores of a warp spread over all banks
 constexpr int kOff1P = kNV * kVSlab;                       // 131072
 constexpr int kOff1Misc = kOff1P + 2 * kPBuf;              // 196608
 constexpr int kSmemBytes = kOff0Misc + 4096 + 1024;        // the larger of the two + misc + alignment slack
@@ -75,6 +75,7 @@ struct Misc0 {   // CTA 0
   unsigned long long s_full[2];     // tcgen05.commit (index 0 used: one S buffer)
   unsigned long long s_free[2];     // 8 softmax warps (index 0 used)
   unsigned long long p_free[2];     // relay warp of CTA 1 (remote arrival)
+  unsigned long long q_full;        // one arrival announcing the 9 tile loads of Q
   uint32_t tmem_base;
   int abort_flag;
   int n_scan;
@@ -97,7 +98,6 @@ struct Misc1 {   // CTA 1
 };
 static_assert(sizeof(Misc0) <= 4096 && sizeof(Misc1) <= 4096, "misc area");
 static_assert(kOff1Misc + 4096 + 1024 <= kSmemBytes, "CTA 1 layout fits");
-static_assert(128 * kORow <= kOff1Misc, "O staging fits below the misc area of CTA 1");
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
@@ -124,16 +124,16 @@ __device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint3
   asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster) : "memory");
 }
-__device__ __forceinline__ void bulk_store_global(void* dst, uint32_t src_cta, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_cta), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// waits until the bulk stores of this thread have read their shared-memory source (the global writes
+// themselves complete before the grid does)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-__global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const __grid_constant__ CUtensorMap tm_kv, const Params p) {
+__global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
+                                                                       const __grid_constant__ CUtensorMap tm_o, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -159,6 +159,7 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const __gr
         mbar_init(smem_u32(&m0->s_free[i]), 8);
         mbar_init(smem_u32(&m0->p_free[i]), 1);
       }
+      mbar_init(smem_u32(&m0->q_full), 1);
     } else {
       for (int i = 0; i < kNV; ++i) { mbar_init(smem_u32(&m1->v_full[i]), 1); mbar_init(smem_u32(&m1->v_free[i]), 1); }
       for (int i = 0; i < 2; ++i) {
@@ -178,6 +179,13 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const __gr
     tmem_relinquish();
     tc_fence_before();
   }
+  if (cta == 0 && tid == 0) {
+    // Q first, so that the loads run under the index scan below
+    const uint32_t qf = smem_u32(&m0->q_full);
+    mbar_arrive_expect_tx(qf, static_cast<uint32_t>(kNChunk * p.h * 128));
+#pragma unroll 1
+    for (int c = 0; c < kNChunk; ++c) tma_load_3d(base + c * kKSlot, &tm_q, qf, c * 64, 0, token);
+  }
   const int32_t* idx_row = p.indices + static_cast<long long>(token) * p.idx_st;
   {
     int local = 0;
@@ -188,23 +196,21 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const __gr
     if (lane == 0 && local > 0) atomicMax(n_scan_p, local);
   }
   if (cta == 0) {
-    // Q -> ring slots 0-8 (one 64-column block per slot, same 128B-swizzled layout as a K block)
-    const __nv_bfloat16* q_tok = p.q + static_cast<long long>(token) * p.q_st;
-    for (int c = tid; c < 128 * (kDqk / 8); c += kThreads) {
-      const int r = c / (kDqk / 8);
-      const int ch = c - r * (kDqk / 8);
-      const uint32_t dst = base + (ch >> 3) * kKSlot + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
-      if (r < p.h) cp_async16(dst, q_tok + static_cast<long long>(r) * p.q_sh + ch * 8);
-      else asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
+    // Q goes to ring slots 0-8 (one 64-column block per slot, same 128B-swizzled layout as a K block) by
+    // nine TMA tile loads of [h rows x 64 columns]; head rows h..127 of the slots are zeroed by hand.
+    if (p.h < 128) {
+      const int per_blk = (128 - p.h) * 8;
+      for (int x = tid; x < kNChunk * per_blk; x += kThreads) {
+        const int c = x / per_blk, y = x - c * per_blk;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + c * kKSlot + p.h * 128 + y * 16), "r"(0) : "memory");
+      }
     }
-    cp_async_commit();
-    cp_async_wait_all();
-    fence_proxy_async_smem();   // these generic-proxy writes precede TMA writes to the same slots
   }
   __syncthreads();
   tc_fence_after();
   if (cta == 0 && warp < 4) {
     // shared memory -> TMEM: thread = head row; a 32-bit TMEM column holds two consecutive bf16 of the row
+    mbar_wait(smem_u32(&m0->q_full), 0u, abort_flag);
     const uint32_t tq = tmem_addr(*tmem_base_p, warp * 32, kColQ);
 #pragma unroll 1
     for (int cc = 0; cc < kNChunk; ++cc) {
@@ -465,7 +471,6 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const __gr
       const int row = (warp & 3) * 32 + lane;
       const int half = warp >> 2;
       const float inv_l = m1->alpha[2][row];
-      const uint32_t o_row = base + row * kORow + half * 512;
 #pragma unroll 1
       for (int c0 = 0; c0 < 256; c0 += 32) {
         uint32_t acc[32];
@@ -476,21 +481,27 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_duo2_kernel(const __gr
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[j] = 0u;
         }
+        // 64-column block cb of the staging area: [128 rows x 128 B], 16-byte chunks XOR-swizzled by row % 8
+        const int cb = half * 4 + (c0 >> 6);
+        const uint32_t o_blk = base + cb * kQBlock + row * 128;
 #pragma unroll
-        for (int j = 0; j < 32; j += 8)
-          st_shared_v4(o_row + (c0 + j) * 2,
+        for (int j = 0; j < 32; j += 8) {
+          const int chunk = ((c0 & 63) + j) >> 3;
+          st_shared_v4(o_blk + ((chunk ^ (row & 7)) << 4),
                        pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l),
                        pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l),
                        pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l),
                        pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l));
+        }
       }
-      fence_proxy_async_smem();   // the bulk store reads this thread's own half row through the async proxy
-      if (row < p.h) {
-        __nv_bfloat16* orow = p.out + static_cast<long long>(token) * p.out_st + static_cast<long long>(row) * p.out_sh + half * 256;
-        bulk_store_global(orow, o_row, 512);
+      fence_proxy_async_smem();   // the tile stores read the staging area through the async proxy
+      named_bar_sync(5, 256);
+      if (lane == 0) {
+        // warp w stores 64-column block w: one TMA tile store of [h rows x 64 columns]
+        tma_store_3d(&tm_o, base + warp * kQBlock, warp * 64, 0, token);
+        bulk_commit();
+        bulk_wait_read_all();
       }
-      bulk_commit();
-      bulk_wait_all();
       tc_fence_before();
     } else if (warp == 8) {
       // ---------------------------------------------------------------- P.V issuer
@@ -598,6 +609,17 @@ int launch_sparse_mla_duo2(const ftb_sparse_mla_args* a, cudaStream_t st) {
     set_last_error("sparse_mla_duo2: cuTensorMapEncodeTiled failed");
     return FTB_ERR_CUDA;
   }
+  const uint32_t box_h = static_cast<uint32_t>(a->h < 128 ? a->h : 128);
+  CUtensorMap tm_q, tm_o;
+  if (!make_tmap_3d(&tm_q, a->q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mla4::kDqk, static_cast<uint64_t>(a->h),
+                    static_cast<uint64_t>(a->s_q), static_cast<uint64_t>(a->q_stride_head),
+                    static_cast<uint64_t>(a->q_stride_token), 64, box_h) ||
+      !make_tmap_3d(&tm_o, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 512, static_cast<uint64_t>(a->h),
+                    static_cast<uint64_t>(a->s_q), static_cast<uint64_t>(a->out_stride_head),
+                    static_cast<uint64_t>(a->out_stride_token), 64, box_h)) {
+    set_last_error("sparse_mla_duo2: cuTensorMapEncodeTiled failed for q or out");
+    return FTB_ERR_CUDA;
+  }
   cudaError_t e = cudaFuncSetAttribute(mla4::sparse_mla_duo2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla4::kSmemBytes);
   if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla_duo)");
   cudaLaunchConfig_t cfg = {};
@@ -610,7 +632,7 @@ int launch_sparse_mla_duo2(const ftb_sparse_mla_args* a, cudaStream_t st) {
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  e = cudaLaunchKernelEx(&cfg, mla4::sparse_mla_duo2_kernel, tm_kv, p);
+  e = cudaLaunchKernelEx(&cfg, mla4::sparse_mla_duo2_kernel, tm_kv, tm_q, tm_o, p);
   return check_cuda(e, "sparse_mla_duo launch");
 }
 

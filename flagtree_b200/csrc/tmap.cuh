@@ -39,4 +39,19 @@ inline bool make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType
   return r == CUDA_SUCCESS;
 }
 
+// 3-D tensor [d2, d1, d0] of `elem_bytes`-wide elements, d0 contiguous, `ld1` / `ld2` elements between
+// consecutive indices of d1 / d2; box = [1, box1, box0]; 128B swizzle (box0 * elem_bytes must be 128).
+inline bool make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t d0,
+                         uint64_t d1, uint64_t d2, uint64_t ld1, uint64_t ld2, uint32_t box0, uint32_t box1) {
+  EncodeTiledFn fn = get_encode_tiled();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {ld1 * static_cast<uint64_t>(elem_bytes), ld2 * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[3] = {box0, box1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 }  // namespace ftb
