@@ -459,6 +459,7 @@ int check_cuda(cudaError_t e, const char* what);
 int launch_sparse_mla_pair(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_duo(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_duo2(const ftb_sparse_mla_args* a, cudaStream_t st);
+int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st);
 }  // namespace ftb
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -494,7 +495,7 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     set_last_error("ftb_sparse_mla_fwd: kv row stride must be a multiple of 8 elements");
     return FTB_ERR_INVALID;
   }
-  if (a->algo_id < 0 || a->algo_id > 4) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
+  if (a->algo_id < 0 || a->algo_id > 5) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
   if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
   // algo 0 = default; algo 1 = one CTA per (token, output half), which is also the kernel of the FP8 paged
   // form, of the split form and of the debug score tap; algo 2 = CTA pair sharing one MMA (cta_group::2);
@@ -503,6 +504,7 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     if (a->algo_id == 2) return launch_sparse_mla_pair(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 3) return launch_sparse_mla_duo(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 4) return launch_sparse_mla_duo2(a, reinterpret_cast<cudaStream_t>(stream));
+    if (a->algo_id == 5) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 0) return launch_sparse_mla_duo(a, reinterpret_cast<cudaStream_t>(stream));   // fastest so far
   }
   MlaParams p;

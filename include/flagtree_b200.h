@@ -67,7 +67,8 @@ typedef struct ftb_sparse_mla_args {
   int32_t lse_base2;        /* 0: lse = log sum exp(s);  1: log2 sum 2^(s*log2 e)            */
   int32_t algo_id;          /* 0 = default; 1 = one CTA per (token, output half); 2 = CTA pair,
                                one shared MMA; 3 = CTA pair, scores / values split;
-                               4 = as 3 with Q in tensor memory */
+                               4 = as 3 with Q in tensor memory and TMA row gathers;
+                               5 = as 4, persistent pairs that walk through the tokens */
   int32_t* status;          /* optional device int32: kernels OR-in a non-zero FTB_ERR_* code */
   /* Paged FP8 form (kv_is_fp8 != 0): physical row = block_table[seq, p / page] * page + p % page,
    * the rule of test_accuracy_musa_vllm_mla.py:278-283.  Query token t belongs to sequence
