@@ -330,7 +330,7 @@ def main():
         achieved = flops_rank / (avg_launch_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops"]
         prof_traffic = None
-        tpath = os.path.join(ROOT, "profiles", "sparse_mla_duo_kernel_cfg2_traffic.txt")   # figures of the ncu capture, JSON text
+        tpath = os.path.join(ROOT, "profiles", "sparse_mla_stream_kernel_cfg2_traffic.txt")   # figures of the ncu capture, JSON text
         if os.path.exists(tpath):
             try:
                 with open(tpath) as f:
@@ -339,7 +339,7 @@ def main():
                 prof_traffic = None
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "traffic": prof_traffic, "peak_source": f"bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json",
-                    "kernel": "sparse_mla_duo_kernel", "flops_per_launch": flops_rank, "avg_launch_ms": avg_launch_ms}
+                    "kernel": "sparse_mla_stream_kernel", "flops_per_launch": flops_rank, "avg_launch_ms": avg_launch_ms}
         cpu_b = None
         if not args.no_cpu_baseline:
             cpu_b = cpu_baseline_mla(args.cpu_tokens, reps=3)
