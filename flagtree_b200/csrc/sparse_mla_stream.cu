@@ -8,17 +8,18 @@
 // (launch gap, barrier setup, TMEM allocation, index scan, Q load, pipeline fill, last P.V, epilogue)
 // was about 20000 cycles against 5100 cycles per tile of 128 rows.  In the persistent loop every
 // barrier keeps counting across tokens and the stages overlap across the token boundary:
-//   * Q of the next token is loaded (TMA) into the ring slots and moved to TMEM as soon as the last
-//     Q.K^T of the current token has completed, while its softmax, P.V and epilogue still run;
-//   * the epilogue of CTA 1 (TMEM -> bf16 -> swizzled staging in the V ring -> 8 TMA tile stores) runs
-//     while CTA 0 already computes the first scores of the next token; the next token's first P.V waits
-//     for the accumulator to be read (o_free), its first V gather for the staging area (epi_done_l).
+//   * Q of the next token passes through the ring slots on its way to TMEM block by block, each block as
+//     soon as the same block of the current token's last tile has been multiplied, so that the first
+//     gathers of the next token are under way while the last Q.K^T of the current one still runs;
+//   * the epilogue of CTA 1 runs on 16 warps while CTA 0 already computes the first scores of the next
+//     token: the rows leave through the P buffer of the last tile by TMA tile stores, so that the V
+//     ring keeps gathering for the next token (o_free lets its first P.V overwrite the accumulator).
 // The number of tiles of a token (last non-negative index, rounded up to 128 rows, at least one) is
 // found for 64 tokens at a time by all warps of a CTA, with a CTA barrier on either side.
 //
 // Warps (576 threads per CTA): CTA 0: 0-7 softmax (two threads per head row), 8 MMA issuer, 9-17 K producers
-// (17 also issues the Q loads, 9-12 move Q to TMEM).  CTA 1: 0-3 correction, 4 relay, 0-7 epilogue,
-// 8 MMA issuer, 9-16 V producers.  Every wait is bounded; a wait that runs out sets the abort flag, after
+// (each also loads its block of Q, 9-12 move Q to TMEM).  CTA 1: 0-3 correction, 4 relay, 8 MMA issuer,
+// 9-16 V producers, 0-7 and 9-16 epilogue.  Every wait is bounded; a wait that runs out sets the abort flag, after
 // which every later wait returns at once and the status word reports a timeout.
 #include "sm100.cuh"
 #include "tmap.cuh"
@@ -43,7 +44,7 @@ constexpr int kVSlab = 8 * kVBlock;            // 32768
 constexpr int kPBuf = 2 * kQBlock;             // 32768: P [128 heads x 128 rows] bf16 as two 64-row blocks
 constexpr int kBatch = 64;                     // tokens whose tile counts are found in one go
 // CTA 0 layout: K ring | P staging x 2 | misc (Q passes through ring slots 0-8 on its way to TMEM).
-// CTA 1 layout: V ring | P x 2 | misc; between tokens the V ring stages O as eight 64-column blocks.
+// CTA 1 layout: V ring | P x 2 | misc; between tokens the P buffer of the last tile stages O.
 constexpr int kOff0K = 0;
 constexpr int kOff0P = kOff0K + kNK * kKSlot;              // 147456
 constexpr int kOff0Misc = kOff0P + 2 * kPBuf;              // 212992
@@ -71,8 +72,8 @@ struct Misc0 {   // CTA 0
   unsigned long long s_full;        // tcgen05.commit
   unsigned long long s_free;        // 8 softmax warps
   unsigned long long p_free[2];     // relay warp of CTA 1 (remote arrival)
-  unsigned long long q_full;        // one arrival announcing the 9 tile loads of Q
-  unsigned long long q_ready;       // 4 copy warps: Q is in TMEM, the ring slots are free
+  unsigned long long q_full[kNK];   // one arrival announcing the tile load of Q block c into slot c
+  unsigned long long q_copied[kNK]; // 4 copier warps: Q block c is in TMEM, slot c is free
   unsigned long long epi_done[2];   // CTA 1 (remote arrival): the epilogue of token t (t % 2) is over
   uint32_t tmem_base;
   int abort_flag;
@@ -89,8 +90,9 @@ struct Misc1 {   // CTA 1
   unsigned long long corr_done[2];  // 4 correction warps
   unsigned long long pv_done[2];    // tcgen05.commit
   unsigned long long fin[2];        // 8 softmax warps of CTA 0: 1/l of token t (t % 2) is in place
-  unsigned long long o_free;        // 8 epilogue warps: the accumulator has been read
-  unsigned long long epi_done_l;    // the O staging area (V ring) has been read by the tile stores
+  unsigned long long o_free;        // 16 epilogue warps: the accumulator has been read
+  unsigned long long stg_free[8];   // epilogue warp w < 8: its staging piece is free for warp 9 + w
+  unsigned long long epi_cnt;       // 16 epilogue warps: the output of the token has left the staging area
   uint32_t tmem_base;
   int abort_flag;
   int pad[2];
@@ -156,8 +158,7 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
       for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), 1); mbar_init(smem_u32(&m0->k_free[i]), 1); }
       mbar_init(smem_u32(&m0->s_full), 1);
       mbar_init(smem_u32(&m0->s_free), 8);
-      mbar_init(smem_u32(&m0->q_full), 1);
-      mbar_init(smem_u32(&m0->q_ready), 4);
+      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->q_full[i]), 1); mbar_init(smem_u32(&m0->q_copied[i]), 4); }
       for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&m0->p_free[i]), 1); mbar_init(smem_u32(&m0->epi_done[i]), 1); }
     } else {
       for (int i = 0; i < kNV; ++i) { mbar_init(smem_u32(&m1->v_full[i]), 1); mbar_init(smem_u32(&m1->v_free[i]), 1); }
@@ -167,8 +168,9 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
         mbar_init(smem_u32(&m1->pv_done[i]), 1);
         mbar_init(smem_u32(&m1->fin[i]), 8);
       }
-      mbar_init(smem_u32(&m1->o_free), 8);
-      mbar_init(smem_u32(&m1->epi_done_l), 1);
+      mbar_init(smem_u32(&m1->o_free), 16);
+      for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&m1->stg_free[i]), 1);
+      mbar_init(smem_u32(&m1->epi_cnt), 16);
     }
     fence_mbar_init();
   }
@@ -341,10 +343,7 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
           const uint32_t k_full0 = smem_u32(&m0->k_full[0]), k_free0 = smem_u32(&m0->k_free[0]);
           const uint32_t s_full = smem_u32(&m0->s_full), s_free = smem_u32(&m0->s_free);
           for (int t = 0; t < nb; ++t) {
-            const int ti = batch0 + t;
             const int n_tiles = nt[t];
-            mbar_wait(smem_u32(&m0->q_ready), ti & 1u, abort_flag);   // Q of this token is in TMEM
-            tc_fence_after();
             for (int i = 0; i < n_tiles; ++i) {
               const uint32_t G = gt + i;
               const uint32_t ph = G & 1u;
@@ -370,8 +369,13 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
       } else {
         // -------------------------------------------------------------- K producers (warps 9-17)
         // warp 9+c fetches 64-column block c of every tile; lane l owns tile rows 4l..4l+3 (one gather4).
-        // At the start of a token warp 17 loads Q into the ring slots and warps 9-12 move it to TMEM.
+        // Between tokens the hand-over runs block by block: as soon as block c of the last tile has been
+        // multiplied (k_free[c]), warp 9+c loads block c of the next token's Q into slot c (q_full[c]);
+        // warps 9-12 (TMEM lane quarters 1, 2, 3, 0) move it to the Q columns of block c in tensor memory
+        // (q_copied[c]), after which slot c takes block c of the next token's first tile.  The MMA issuer
+        // needs no extra wait: k_full[c] of that tile cannot complete before q_copied[c].
         const int c = warp - 9;
+        const bool copier = c < 4;
         for (int t = 0; t < nb; ++t) {
           const int ti = batch0 + t;
           const int tok = pair + ti * n_pairs;
@@ -380,48 +384,8 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
           int nxt[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) nxt[j] = (4 * lane + j < p.topk) ? idx_row[4 * lane + j] : -1;
-          if (c == kNK - 1 && lane == 0) {
-            // every Q.K^T of the previous token has completed (the last commit covers all earlier MMAs):
-            // the ring slots and the Q columns of TMEM are free.  The warp of the last block issues the
-            // loads because it has followed k_free[8] phase by phase: a parity wait by a thread that is two
-            // phases behind the barrier's next completion would return at once.
-            if (gt >= 1) mbar_wait(smem_u32(&m0->k_free[kNK - 1]), (gt - 1) & 1u, abort_flag);
-            const uint32_t qf = smem_u32(&m0->q_full);
-            mbar_arrive_expect_tx(qf, static_cast<uint32_t>(kNChunk * p.h * 128));
-#pragma unroll 1
-            for (int cc = 0; cc < kNChunk; ++cc) tma_load_3d(base + cc * kKSlot, &tm_q, qf, cc * 64, 0, tok);
-          }
-          __syncwarp();
-          if (c < 4) {
-            // shared memory -> TMEM: thread = head row (TMEM lane quarter = warp % 4); a 32-bit TMEM column
-            // holds two consecutive bf16 of the row; head rows >= h are zero
-            mbar_wait(smem_u32(&m0->q_full), ti & 1u, abort_flag);
-            tc_fence_after();
-            const int row = (warp & 3) * 32 + lane;
-            const uint32_t tq = tmem_addr(tmem, (warp & 3) * 32, kColQ);
-#pragma unroll 1
-            for (int cc = 0; cc < kNChunk; ++cc) {
-              uint32_t v[32];
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const uint32_t src = base + cc * kKSlot + row * 128 + ((q ^ (row & 7)) << 4);
-                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                             : "=r"(v[4 * q]), "=r"(v[4 * q + 1]), "=r"(v[4 * q + 2]), "=r"(v[4 * q + 3]) : "r"(src));
-              }
-              if (row >= p.h) {
-#pragma unroll
-                for (int q = 0; q < 32; ++q) v[q] = 0u;
-              }
-              tmem_st32(tq + cc * 32, v);
-            }
-            tmem_wait_st();
-            tc_fence_before();
-            fence_proxy_async_smem();   // the ring slots read above are next written by TMA (async proxy)
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&m0->q_ready));
-          }
-          mbar_wait(smem_u32(&m0->q_ready), ti & 1u, abort_flag);
-          for (int i = 0; i < n_tiles; ++i) {
+          // one tile: resolve this lane's four rows, then gather them once slot c is free
+          auto issue_tile = [&](int i) {
             const uint32_t G = gt + i;
             int row[4];
             uint32_t nib = 0;
@@ -445,13 +409,72 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
               v |= __shfl_xor_sync(0xffffffffu, v, 4);
               if ((lane & 7) == 0) m0->valid_mask[G & 3][lane >> 3] = v;
             }
-            if (G >= 1) mbar_wait(smem_u32(&m0->k_free[c]), (G - 1) & 1u, abort_flag);
+            // tile 0 follows the Q block that passed through the slot (the caller has seen q_copied[c])
+            if (i > 0) mbar_wait(smem_u32(&m0->k_free[c]), (G - 1) & 1u, abort_flag);
             const uint32_t full = smem_u32(&m0->k_full[c]);
             __syncwarp();
             if (lane == 0) mbar_arrive_expect_tx(full, kKSlot);
             __syncwarp();
             tma_gather4(k_s + c * kKSlot + lane * 512, &tm_kv, full, c * 64, row[0], row[1], row[2], row[3]);
+          };
+          // Q block c of this token: slot c and the Q columns of block c are free once block c of the previous
+          // token's last tile has been multiplied
+          auto load_q_block = [&]() {
+            if (lane == 0) {
+              if (gt >= 1) mbar_wait(smem_u32(&m0->k_free[c]), (gt - 1) & 1u, abort_flag);
+              const uint32_t qf = smem_u32(&m0->q_full[c]);
+              mbar_arrive_expect_tx(qf, static_cast<uint32_t>(p.h * 128));
+              tma_load_3d(base + c * kKSlot, &tm_q, qf, c * 64, 0, tok);
+            }
+            __syncwarp();
+          };
+          load_q_block();
+          if (!copier) {
+            mbar_wait(smem_u32(&m0->q_copied[c]), ti & 1u, abort_flag);
+            issue_tile(0);
+          } else {
+            // shared memory -> TMEM: thread = head row (TMEM lane quarter = warp % 4); a 32-bit TMEM column
+            // holds two consecutive bf16 of the row; head rows >= h are zero.  The blocks are moved in the
+            // order in which they arrive (every warp has asked for its own block above: a load takes about
+            // 2600 cycles, so the loads must not wait for one another), and this warp's own first gather
+            // goes out as soon as all four copiers are through with block c.
+            const int row = (warp & 3) * 32 + lane;
+            const uint32_t tq = tmem_addr(tmem, (warp & 3) * 32, kColQ);
+            bool tile0_out = false;
+#pragma unroll 1
+            for (int cc = 0; cc < kNChunk; ++cc) {
+              mbar_wait(smem_u32(&m0->q_full[cc]), ti & 1u, abort_flag);
+              tc_fence_after();
+              uint32_t v[32];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const uint32_t src = base + cc * kKSlot + row * 128 + ((q ^ (row & 7)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[4 * q]), "=r"(v[4 * q + 1]), "=r"(v[4 * q + 2]), "=r"(v[4 * q + 3]) : "r"(src));
+              }
+              if (row >= p.h) {
+#pragma unroll
+                for (int q = 0; q < 32; ++q) v[q] = 0u;
+              }
+              tmem_st32(tq + cc * 32, v);
+              tmem_wait_st();
+              tc_fence_before();
+              fence_proxy_async_smem();   // the slot read above is next written by TMA (async proxy)
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&m0->q_copied[cc]));
+              if (!tile0_out && cc > c) {
+                uint32_t ok = 0;
+                if (lane == 0) ok = mbar_try_wait(smem_u32(&m0->q_copied[c]), ti & 1u) ? 1u : 0u;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (ok) { issue_tile(0); tile0_out = true; }
+              }
+            }
+            if (!tile0_out) {
+              mbar_wait(smem_u32(&m0->q_copied[c]), ti & 1u, abort_flag);
+              issue_tile(0);
+            }
           }
+          for (int i = 1; i < n_tiles; ++i) issue_tile(i);
           gt += n_tiles;
         }
       }
@@ -459,9 +482,67 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
       // ===================================================================== CTA 1: values
       const uint32_t v_s = base;
       const uint32_t p_s = base + kOff1P;
+      const uint32_t epi_done_r[2] = {mapa_shared(smem_u32(&m0->epi_done[0]), 0), mapa_shared(smem_u32(&m0->epi_done[1]), 0)};
+      // ---------------------------------------------------------------- epilogue duty (16 warps: 0-7 and 9-16)
+      // warp -> TMEM lane quarter warp % 4 (head rows 32q .. 32q+31) and column group g (output columns
+      // 128g .. 128g+127): warps 0-3 g = 0, 4-7 g = 1, 9-12 g = 2, 13-16 g = 3.  A warp works alone: it
+      // converts 64 columns of its rows to bf16 into a private 4 KB piece of the P buffer of the token's
+      // last tile ([32 rows x 128 B], the swizzled tile layout) and sends it with one TMA tile store, twice.
+      // That P buffer is idle until the softmax two tiles later asks for it, and the relay holds its
+      // p_free back until the last store has read it; the V ring is not touched, so the gathers of the
+      // next token run underneath.  Warp w < 8 and warp 9 + w share piece w: the V producers come later
+      // (they first send out the next token's first gathers) and wait for their partner (stg_free).
+      auto epilogue_duty = [&](int ti, uint32_t Gl, int tok) {
+        const int q4 = warp & 3;
+        const int grp = warp < 8 ? (warp >> 2) : 2 + ((warp - 9) >> 2);
+        const int piece = warp < 8 ? warp : warp - 9;
+        // `fin` first: a parity wait is only exact once the barrier is in, or past, the phase waited for
+        // (after `fin` the P.V two tiles before the last one has completed)
+        mbar_wait(smem_u32(&m1->fin[ti & 1]), (ti >> 1) & 1u, abort_flag);
+        mbar_wait(smem_u32(&m1->pv_done[Gl & 1]), (Gl >> 1) & 1u, abort_flag);
+        if (warp >= 9) mbar_wait(smem_u32(&m1->stg_free[piece]), ti & 1u, abort_flag);
+        tc_fence_after();
+        const int row = q4 * 32 + lane;
+        const float inv_l = m1->inv_l[ti & 1][row];
+        const uint32_t stg = p_s + (Gl & 1u) * kPBuf + piece * 4096 + lane * 128;
+#pragma unroll 1
+        for (int cb = 0; cb < 2; ++cb) {
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t acc[32];
+            tmem_ld32(tmem_addr(tmem, q4 * 32, grp * 128 + cb * 64 + c2 * 32), acc);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int chunk = c2 * 4 + (j >> 3);
+              st_shared_v4(stg + ((chunk ^ (lane & 7)) << 4),
+                           pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l),
+                           pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l),
+                           pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l),
+                           pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l));
+            }
+          }
+          if (cb == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&m1->o_free));   // the next token's P.V may overwrite the accumulator
+          }
+          fence_proxy_async_smem();   // the tile store reads the piece through the async proxy
+          __syncwarp();
+          if (lane == 0) {
+            if (q4 * 32 < p.h) tma_store_3d(&tm_o, stg - lane * 128, (grp * 2 + cb) * 64, q4 * 32, tok);
+            bulk_commit();
+            bulk_wait_read_all();
+          }
+          __syncwarp();
+        }
+        if (lane == 0) {
+          if (warp < 8) mbar_arrive(smem_u32(&m1->stg_free[piece]));
+          mbar_arrive(smem_u32(&m1->epi_cnt));
+        }
+      };
       if (warp < 8) {
         const uint32_t p_free_r[2] = {mapa_shared(smem_u32(&m0->p_free[0]), 0), mapa_shared(smem_u32(&m0->p_free[1]), 0)};
-        const uint32_t epi_done_r[2] = {mapa_shared(smem_u32(&m0->epi_done[0]), 0), mapa_shared(smem_u32(&m0->epi_done[1]), 0)};
         for (int t = 0; t < nb; ++t) {
           const int ti = batch0 + t;
           const int tok = pair + ti * n_pairs;
@@ -495,7 +576,7 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
             }
           } else if (warp == 4 && lane == 0) {
             // ------------------------------------------------------------ relay: P buffer free -> CTA 0
-            for (int i = 0; i < n_tiles; ++i) {
+            for (int i = 0; i + 1 < n_tiles; ++i) {
               const uint32_t G = gt + i;
               mbar_wait(smem_u32(&m1->pv_done[G & 1]), (G >> 1) & 1u, abort_flag);
               mbar_arrive_cluster(p_free_r[G & 1]);
@@ -503,51 +584,12 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
           }
           __syncwarp();
           gt += n_tiles;
-          // -------------------------------------------------------------- epilogue (8 warps)
-          // warp w: head rows 32*(w%4) .. +31 (its TMEM lanes), output columns 256*(w/4) .. +255.  The V
-          // ring is idle once the last P.V of the token has completed (its next gathers wait for
-          // epi_done_l); O is staged there as eight 64-column blocks [128 rows x 128 B], 16-byte chunks
-          // XOR-swizzled by row % 8, and leaves through one TMA tile store per block.
-          // `fin` first: a parity wait is only exact once the barrier is in, or past, the phase waited for
-          // (after `fin` the P.V two tiles before the last one has completed)
-          mbar_wait(smem_u32(&m1->fin[ti & 1]), (ti >> 1) & 1u, abort_flag);
-          const uint32_t Gl = gt - 1;
-          mbar_wait(smem_u32(&m1->pv_done[Gl & 1]), (Gl >> 1) & 1u, abort_flag);
-          tc_fence_after();
-          const int row = (warp & 3) * 32 + lane;
-          const int half = warp >> 2;
-          const float inv_l = m1->inv_l[ti & 1][row];
-#pragma unroll 1
-          for (int c0 = 0; c0 < 256; c0 += 32) {
-            uint32_t acc[32];
-            tmem_ld32(tmem_addr(tmem, (warp & 3) * 32, half * 256 + c0), acc);
-            tmem_wait_ld();
-            const int cb = half * 4 + (c0 >> 6);
-            const uint32_t o_blk = base + cb * kQBlock + row * 128;
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              const int chunk = ((c0 & 63) + j) >> 3;
-              st_shared_v4(o_blk + ((chunk ^ (row & 7)) << 4),
-                           pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l),
-                           pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l),
-                           pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l),
-                           pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l));
-            }
-          }
-          tc_fence_before();
-          fence_proxy_async_smem();   // the tile stores read the staging area through the async proxy
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&m1->o_free));   // the next token's P.V may overwrite the accumulator
-          named_bar_sync(5, 256);
-          if (lane == 0) {
-            // warp w stores 64-column block w: one TMA tile store of [h rows x 64 columns]
-            tma_store_3d(&tm_o, base + warp * kQBlock, warp * 64, 0, tok);
-            bulk_commit();
-            bulk_wait_read_all();
-          }
-          named_bar_sync(5, 256);
-          if (tid == 0) {
-            mbar_arrive(smem_u32(&m1->epi_done_l));
+          epilogue_duty(ti, gt - 1, tok);
+          // the P buffer of the last tile staged the output: it is free for the softmax, and 1/l of this
+          // token may be replaced, once all 16 warps are through
+          if (warp == 4 && lane == 0) {
+            mbar_wait(smem_u32(&m1->epi_cnt), ti & 1u, abort_flag);
+            mbar_arrive_cluster(p_free_r[(gt - 1) & 1]);
             mbar_arrive_cluster(epi_done_r[ti & 1]);
           }
         }
@@ -612,9 +654,7 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
           int nxt[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) nxt[j] = (4 * lane + j < p.topk) ? idx_row[4 * lane + j] : -1;
-          // the V ring staged the output of the previous token: its tile stores have read it
-          if (ti >= 1) mbar_wait(smem_u32(&m1->epi_done_l), (ti - 1) & 1u, abort_flag);
-          for (int i = 0; i < n_tiles; ++i) {
+          auto issue_tile = [&](int i) {
             const uint32_t G = gt + i;
             int row[4];
 #pragma unroll
@@ -630,9 +670,18 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
             // ahead of the announcement: the phase cannot complete before this arrival)
             if (w == 0 && (lane & 7) == 0) mbar_arrive_expect_tx(full, kVSlab);
             tma_gather4(v_s + sl * kVSlab + w * kVBlock + (lane & 7) * 512, &tm_kv, full, w * 64, row[0], row[1], row[2], row[3]);
-          }
+          };
+          // the first tile goes out before this warp helps with the previous token's epilogue, so that the
+          // gathers run underneath it
+          issue_tile(0);
+          __syncwarp();
+          if (t > 0) epilogue_duty(ti - 1, gt - 1, tok - n_pairs);
+          for (int i = 1; i < n_tiles; ++i) issue_tile(i);
           gt += n_tiles;
         }
+        // the last token of the batch: nothing of the next batch is known yet
+        __syncwarp();
+        epilogue_duty(batch0 + nb - 1, gt - 1, pair + (batch0 + nb - 1) * n_pairs);
       }
     }
     __syncthreads();   // nt[] is rewritten by the next batch
@@ -664,7 +713,8 @@ int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st) {
   p.lse_base2 = a->lse_base2;
   p.status = a->status;
   // KV: box = 64 columns x 1 row (tile::gather4 fetches four such rows per instruction);
-  // Q and O: boxes of [h rows x 64 columns] of one token
+  // Q: boxes of [h rows x 64 columns] of one token; O: boxes of [32 rows x 64 columns] (a store that
+  // reaches past row h is clipped)
   const uint32_t box_h = static_cast<uint32_t>(a->h < 128 ? a->h : 128);
   CUtensorMap tm_kv, tm_q, tm_o;
   if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla5::kDqk,
@@ -674,7 +724,7 @@ int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st) {
                     static_cast<uint64_t>(a->q_stride_token), 64, box_h) ||
       !make_tmap_3d(&tm_o, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 512, static_cast<uint64_t>(a->h),
                     static_cast<uint64_t>(a->s_q), static_cast<uint64_t>(a->out_stride_head),
-                    static_cast<uint64_t>(a->out_stride_token), 64, box_h)) {
+                    static_cast<uint64_t>(a->out_stride_token), 64, box_h < 32 ? box_h : 32)) {
     set_last_error("sparse_mla_stream: cuTensorMapEncodeTiled failed");
     return FTB_ERR_CUDA;
   }
