@@ -12,6 +12,7 @@
 namespace ftb {
 
 constexpr long long kWaitLimitCycles = 2000000000LL;   // about one second at B200 clocks
+constexpr uint32_t kWaitSleepNs = 20000;                // longest sleep of one try_wait inside a bounded wait
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -41,12 +42,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint (nanoseconds): the thread sleeps until the phase completes or the time
+// is up instead of coming back to poll, which leaves the issue slots of its scheduler to the other warps.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  `abort_flag` lives in shared memory; once set every later wait returns at once.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_sleep(bar, parity, kWaitSleepNs)) {
     if (*abort_flag) return false;
     if (clock64() - t0 > kWaitLimitCycles) {
       *abort_flag = 1;
