@@ -111,6 +111,38 @@ def cpu_baseline_mla(n_tokens: int, reps: int = 1):
             "seconds": best, "flops": flops}
 
 
+def bench_mla_decode_fp8(args, dev, peaks):
+    """Third workload (a parity-test case with a timing beside it, not the headline): sparse MLA decode over
+    the paged FP8 latent cache of cfg3 (64 sequences x 2 query tokens, h = 128, topk = 2048, 64-token pages
+    with one fp32 scale each, context 8192..65536).  The gathered FP8 rows (151 MB) exceed L2.  Near the
+    ridge: reported both as TFLOP/s and as GB/s of the bytes that must move."""
+    from flagtree_b200 import sparse_mla_fwd_paged
+    from flagtree_b200 import workloads as W
+    c = W.mla_cfg3(device=dev)
+    b, n_q, h, _ = c.q.shape
+    n_valid = int((c.indices >= 0).sum())
+    flops = 2 * (576 + 512) * h * n_valid
+    nbytes = n_valid * 576 + c.q.numel() * 2 + b * n_q * h * 512 * 2 + c.indices.numel() * 4
+    iters = max(5, min(args.steps, 20))
+    for _ in range(max(3, args.warmup)):
+        sparse_mla_fwd_paged(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens, c.indices, c.sm_scale,
+                             page_size=c.page_size)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        sparse_mla_fwd_paged(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens, c.indices, c.sm_scale,
+                             page_size=c.page_size)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / iters
+    return {"workload": c.name, "dtype": "fp8 e4m3 KV (bf16 math)", "ms": ms, "iters": iters, "flops": flops,
+            "tflops": flops / (ms * 1e-3) / 1e12, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+            "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+            "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "l2": "gathered rows (151 MB) larger than L2", "kernel": "mla_dequant_rows_kernel + sparse_mla_stream_kernel"}
+
+
 def bench_gemm_rs(args, dev, rank, world, dist, peaks):
     """Second hot path: row-parallel bf16 GEMM fused with reduce-scatter at tp = number of GPUs, per-rank
     shape of cfg4 (A [8192 x 2304], B [2304 x 7168]; K grows with tp).  tp = 1 is the plain GEMM.  Each
@@ -214,6 +246,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM + reduce-scatter section")
+    ap.add_argument("--no-decode", action="store_true", help="skip the paged FP8 decode section (cfg3)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -320,6 +353,9 @@ def main():
         e2e = {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e}
 
+    decode_fp8 = None
+    if world == 1 and not args.no_decode:
+        decode_fp8 = bench_mla_decode_fp8(args, dev, load_peaks())
     gemm_rs = None
     if not args.no_gemm:
         gemm_rs = bench_gemm_rs(args, dev, rank, world, dist, load_peaks())
@@ -354,6 +390,7 @@ def main():
                        "flops_per_gpu_step": flops_rank},
             "roofline": roofline, "cpu_baseline": cpu_b, "e2e": e2e, "gpu_launches": args.steps,
             "gemm_rs": gemm_rs,
+            "mla_decode_fp8": decode_fp8,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

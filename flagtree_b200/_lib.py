@@ -74,6 +74,8 @@ def load() -> C.CDLL:
             lib.ftb_sparse_mla_fwd.restype = C.c_int
             lib.ftb_sparse_mla_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
             lib.ftb_sparse_mla_workspace_bytes.restype = C.c_int64
+            lib.ftb_sparse_mla_dequant_workspace_bytes.argtypes = [C.c_int32, C.c_int32]
+            lib.ftb_sparse_mla_dequant_workspace_bytes.restype = C.c_int64
             lib.ftb_sparse_mla_fwd_static_scratch.argtypes = [C.POINTER(SparseMlaArgs), C.c_void_p]
             lib.ftb_sparse_mla_fwd_static_scratch.restype = C.c_int
             lib.ftb_sparse_mla_static_scratch_bytes.restype = C.c_int64

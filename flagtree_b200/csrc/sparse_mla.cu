@@ -89,6 +89,49 @@ __device__ __forceinline__ int resolve_row(const MlaParams& p, int token, int lo
   return ok ? row : 0;
 }
 
+// Paged FP8 form, first pass of the two-pass path: one warp per selected row.  The row is resolved through
+// the page table, its 576 e4m3 values are converted to bf16 times the page scale (the same arithmetic as
+// the gather of the one-pass kernel below) and written to row r = token * topk + j of a compact bf16 table;
+// `out_idx[r]` is r, or -1 for padding and for positions at or past the context length.  The bf16 kernels
+// then run on the compact table with these indices.
+__global__ void __launch_bounds__(256) mla_dequant_rows_kernel(const MlaParams p, __nv_bfloat16* table, int32_t* out_idx) {
+  const int lane = threadIdx.x & 31;
+  const long long n_rows = static_cast<long long>(p.s_q) * p.topk;
+  const uint8_t* kvp = reinterpret_cast<const uint8_t*>(p.kv);
+  for (long long r = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; r < n_rows;
+       r += (static_cast<long long>(gridDim.x) * blockDim.x) >> 5) {
+    const int token = static_cast<int>(r / p.topk);
+    const int j = static_cast<int>(r - static_cast<long long>(token) * p.topk);
+    const int logical = p.indices[static_cast<long long>(token) * p.idx_st + j];
+    bool ok;
+    float sc;
+    const int row = resolve_row(p, token, logical, ok, sc);
+    if (lane == 0) out_idx[r] = ok ? static_cast<int32_t>(r) : -1;
+    if (!ok) continue;
+    const uint8_t* src = kvp + static_cast<long long>(row) * p.kv_sr;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(table + r * kDqk);
+    // 36 chunks of 16 bytes: every lane one, lanes 0-3 a second one
+    for (int c16 = lane; c16 < kDqk / 16; c16 += 32) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + c16 * 16);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t o[8];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_fp8x2_storage_t lo = static_cast<__nv_fp8x2_storage_t>(w[i] & 0xffffu);
+        const __nv_fp8x2_storage_t hi = static_cast<__nv_fp8x2_storage_t>(w[i] >> 16);
+        const __half2_raw hlo = __nv_cvt_fp8x2_to_halfraw2(lo, __NV_E4M3);
+        const __half2_raw hhi = __nv_cvt_fp8x2_to_halfraw2(hi, __NV_E4M3);
+        const float2 flo = __half22float2(*reinterpret_cast<const __half2*>(&hlo));
+        const float2 fhi = __half22float2(*reinterpret_cast<const __half2*>(&hhi));
+        o[2 * i] = pack_bf16x2(flo.x * sc, flo.y * sc);
+        o[2 * i + 1] = pack_bf16x2(fhi.x * sc, fhi.y * sc);
+      }
+      reinterpret_cast<uint4*>(dst)[c16 * 2] = make_uint4(o[0], o[1], o[2], o[3]);
+      reinterpret_cast<uint4*>(dst)[c16 * 2 + 1] = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+  }
+}
+
 template <bool kFp8>
 __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -495,7 +538,7 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     set_last_error("ftb_sparse_mla_fwd: kv row stride must be a multiple of 8 elements");
     return FTB_ERR_INVALID;
   }
-  if (a->algo_id < 0 || a->algo_id > 5) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
+  if (a->algo_id < 0 || a->algo_id > 6) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
   if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
   // algo 0 = default; algo 1 = one CTA per (token, output half), which is also the kernel of the FP8 paged
   // form, of the split form and of the debug score tap; algo 2 = CTA pair sharing one MMA (cta_group::2);
@@ -529,6 +572,41 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int n_splits = a->n_splits > 0 ? a->n_splits : 1;
+  // Paged FP8 form with a workspace for the dequantised rows (algo 0 or 6, no split): convert the selected
+  // rows once, then run the persistent bf16 kernel on the compact table.  Without such a workspace the
+  // one-pass kernel below converts while it gathers.
+  if (a->kv_is_fp8 && n_splits == 1 && a->dbg_scores == nullptr && (a->algo_id == 0 || a->algo_id == 6)) {
+    const int64_t need = ftb_sparse_mla_dequant_workspace_bytes(a->s_q, a->topk);
+    const bool have = a->workspace != nullptr && a->workspace_bytes >= need && need > 0 &&
+                      (reinterpret_cast<uintptr_t>(a->workspace) & 15u) == 0 &&
+                      static_cast<long long>(a->s_q) * a->topk < (1LL << 31);
+    if (a->algo_id == 6 && !have) {
+      set_last_error("ftb_sparse_mla_fwd: algo 6 needs a 16-byte aligned workspace of ftb_sparse_mla_dequant_workspace_bytes() bytes");
+      return FTB_ERR_INVALID;
+    }
+    if (have) {
+      p.topk = a->topk;
+      __nv_bfloat16* table = reinterpret_cast<__nv_bfloat16*>(a->workspace);
+      int32_t* idx2 = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(a->workspace) +
+                                                static_cast<size_t>(a->s_q) * a->topk * kDqk * 2);
+      const long long n_rows = static_cast<long long>(a->s_q) * a->topk;
+      const unsigned blocks = static_cast<unsigned>(n_rows / 8 < 148 * 16 ? (n_rows + 7) / 8 : 148 * 16);
+      mla_dequant_rows_kernel<<<blocks, 256, 0, st>>>(p, table, idx2);
+      int rc0 = check_cuda(cudaGetLastError(), "mla_dequant_rows launch");
+      if (rc0 != FTB_OK) return rc0;
+      ftb_sparse_mla_args b = *a;
+      b.kv = table;
+      b.kv_is_fp8 = 0;
+      b.kv_scale = nullptr; b.block_table = nullptr; b.context_lens = nullptr;
+      b.s_kv = static_cast<int32_t>(n_rows);
+      b.kv_stride_row = kDqk;
+      b.indices = idx2;
+      b.idx_stride_token = a->topk;
+      b.algo_id = 5;
+      b.workspace = nullptr; b.workspace_bytes = 0; b.n_splits = 0;
+      return launch_sparse_mla_stream(&b, st);
+    }
+  }
   if (n_splits > 1) {
     if (a->workspace == nullptr || a->workspace_bytes < ftb_sparse_mla_workspace_bytes(a->s_q, a->h, n_splits)) {
       set_last_error("ftb_sparse_mla_fwd: n_splits=%d needs a workspace of ftb_sparse_mla_workspace_bytes() bytes", n_splits);
@@ -555,6 +633,11 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
   sparse_mla_merge_kernel<<<(warps * 32 + 255) / 256, 256, 0, st>>>(p.part_out, p.part_lse, p.out, p.lse, a->s_q, a->h, n_splits,
                                                                     p.out_st, p.out_sh, p.lse_st, p.lse_base2);
   return check_cuda(cudaGetLastError(), "sparse_mla_merge launch");
+}
+
+extern "C" FTB_API int64_t ftb_sparse_mla_dequant_workspace_bytes(int32_t s_q, int32_t topk) {
+  if (s_q <= 0 || topk <= 0) return 0;
+  return static_cast<int64_t>(s_q) * topk * (576 * 2 + 4);
 }
 
 extern "C" FTB_API int64_t ftb_sparse_mla_workspace_bytes(int32_t s_q, int32_t h, int32_t n_splits) {
@@ -604,7 +687,12 @@ extern "C" FTB_API int ftb_sparse_mla_fwd_static_scratch(const ftb_sparse_mla_ar
     g_mla_static_scratch_addr[dev] = ptr;
   }
   ftb_sparse_mla_args b = *a;
-  b.workspace = g_mla_static_scratch_addr[dev];
-  b.workspace_bytes = FTB_MLA_STATIC_SCRATCH_BYTES;
+  if (a->n_splits > 1) {
+    b.workspace = g_mla_static_scratch_addr[dev];
+    b.workspace_bytes = FTB_MLA_STATIC_SCRATCH_BYTES;
+  } else {   // no split, no scratch (and no two-pass FP8 path through this entry)
+    b.workspace = nullptr;
+    b.workspace_bytes = 0;
+  }
   return ftb_sparse_mla_fwd(&b, stream);
 }

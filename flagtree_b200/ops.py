@@ -123,8 +123,8 @@ def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
 def sparse_mla_fwd_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Tensor,
                          block_table: torch.Tensor, context_lens: torch.Tensor, indices: torch.Tensor,
                          sm_scale: Optional[float] = None, d_v: int = D_V, page_size: int = 64, *,
-                         lse_base2: bool = False, check: bool = False, num_splits: Optional[int] = None
-                         ) -> Tuple[torch.Tensor, torch.Tensor]:
+                         lse_base2: bool = False, check: bool = False, num_splits: Optional[int] = None,
+                         two_pass: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Sparse MLA decode over a paged FP8 (e4m3) latent cache with one fp32 scale per page.
 
     q [B, n_q, h, 576] bf16; kv_cache [num_pages, page_size, 576] e4m3 (uint8 or float8_e4m3fn);
@@ -132,6 +132,10 @@ def sparse_mla_fwd_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torc
     context_lens [B] int32; indices [B, n_q, topk] int32 LOGICAL positions (-1 = padding).
     Physical row = block_table[b, p // page] * page + p % page, the addressing rule of
     test_accuracy_musa_vllm_mla.py:278-283.  Returns (out [B,n_q,h,512] bf16, lse [B,n_q,h] fp32).
+
+    `two_pass`: convert the selected rows to a compact bf16 table first and run the persistent bf16 kernel on
+    it (needs 1156 bytes of scratch per selected row); None = do so when the top-k axis is not split and the
+    scratch stays below 4 GiB, False = the one-pass kernel that converts while it gathers.
     """
     _require_cuda(q, kv_cache, kv_scale, block_table, context_lens, indices)
     assert q.dim() == 4 and indices.dim() == 3 and kv_cache.dim() == 3
@@ -170,6 +174,12 @@ def sparse_mla_fwd_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torc
     if num_splits is None:
         num_splits = _auto_splits(b * n_q, idx2.shape[1], q.device)
     _ws = _split_workspace(a, b * n_q, h, int(num_splits), q.device)
+    if int(num_splits) <= 1 and two_pass is not False:
+        need = int(_lib.load().ftb_sparse_mla_dequant_workspace_bytes(b * n_q, idx2.shape[1]))
+        if two_pass or need <= (4 << 30):
+            _ws = torch.empty(need, dtype=torch.uint8, device=q.device)
+            a.workspace, a.workspace_bytes = _ws.data_ptr(), need
+            a.algo_id = 6
     with torch.cuda.device(q.device):
         rc = _lib.load().ftb_sparse_mla_fwd(C.byref(a), C.c_void_p(_stream_ptr(q.device)))
     _lib.check(rc, "sparse_mla_fwd_paged")

@@ -68,7 +68,8 @@ typedef struct ftb_sparse_mla_args {
   int32_t algo_id;          /* 0 = default; 1 = one CTA per (token, output half); 2 = CTA pair,
                                one shared MMA; 3 = CTA pair, scores / values split;
                                4 = as 3 with Q in tensor memory and TMA row gathers;
-                               5 = as 4, persistent pairs that walk through the tokens */
+                               5 = as 4, persistent pairs that walk through the tokens;
+                               6 = paged FP8 form only: dequantise the selected rows, then 5 */
   int32_t* status;          /* optional device int32: kernels OR-in a non-zero FTB_ERR_* code */
   /* Paged FP8 form (kv_is_fp8 != 0): physical row = block_table[seq, p / page] * page + p % page,
    * the rule of test_accuracy_musa_vllm_mla.py:278-283.  Query token t belongs to sequence
@@ -92,6 +93,12 @@ typedef struct ftb_sparse_mla_args {
 
 FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* args, void* stream);
 FTB_API int64_t ftb_sparse_mla_workspace_bytes(int32_t s_q, int32_t h, int32_t n_splits);
+/* Paged FP8 form, two passes: when `workspace` holds at least this many bytes (16-byte aligned) and
+ * n_splits <= 1, the selected rows are first converted to a compact bf16 table (row = token * topk + j,
+ * the role of the dequantising loads of decode_attention_int4kv.py:345-450, done once per row instead of
+ * inside the attention loop) and the persistent bf16 kernel runs on that table.  algo_id 6 demands this
+ * path, algo_id 0 takes it when the workspace allows. */
+FTB_API int64_t ftb_sparse_mla_dequant_workspace_bytes(int32_t s_q, int32_t topk);
 /* Same operation for callers that cannot allocate device memory (an engine that owns the whole device
  * through its own pool, a sandboxed plugin, a latency path that must stay clear of the allocator).  It has
  * no counterpart in the reference, whose wrappers always receive `attn_logits` from the caller.

@@ -173,6 +173,31 @@ def test_full_size_prefill_sampled_tokens():
     assert torch.equal(out, out2)
 
 
+def test_full_size_decode_fp8_sampled_sequences():
+    """cfg3 at full size (64 sequences x 2 query tokens, h = 128, topk = 2048, paged FP8 cache with contexts of
+    8192..65536 tokens): every output is produced on the GPU by the default path (selected rows dequantised
+    once, then the persistent kernel); three sequences are cut out with their own pages and compared with
+    the CPU oracle; the one-pass kernel must agree on all of them."""
+    c = W.mla_cfg3(device=DEV)
+    args = (c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens, c.indices, c.sm_scale)
+    out, lse = sparse_mla_fwd_paged(*args, page_size=c.page_size, check=True)                 # two passes
+    out1, lse1 = sparse_mla_fwd_paged(*args, page_size=c.page_size, check=True, num_splits=1, two_pass=False)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out.float()).all() and torch.isfinite(lse).all()
+    assert (out.float() - out1.float()).abs().max().item() <= OUT_ATOL
+    assert ((lse - lse1).abs() / lse1.abs().clamp(min=1)).max().item() <= LSE_RTOL
+    for b in (0, 17, 63):
+        n_pages = (int(c.context_lens[b]) + c.page_size - 1) // c.page_size
+        pages = c.block_table[b, :n_pages].long()
+        ref_out, ref_lse = sparse_mla_fwd_paged_ref(
+            c.q[b:b + 1].cpu(), c.kv_cache[pages].cpu(), c.kv_scale[pages].cpu(),
+            torch.arange(n_pages, dtype=torch.int32).view(1, -1), c.context_lens[b:b + 1].cpu(),
+            c.indices[b:b + 1].cpu(), c.sm_scale, page_size=c.page_size)
+        e_out, e_lse = _errors(out[b:b + 1], lse[b:b + 1], ref_out, ref_lse)
+        print(f"[cfg3 full, sequence {b}] out {e_out:.3e} lse {e_lse:.3e}")
+        assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+
+
 def test_more_than_128_heads_and_strided_views():
     g = torch.Generator().manual_seed(11)
     q_big = torch.randn(3, 160, 640, generator=g).bfloat16()
@@ -207,11 +232,12 @@ def test_decode_attention_fwd_shim_matches_reference_signature():
     assert (o.float().cpu() - torch.from_numpy(d["out"]).float()).abs().max().item() <= OUT_ATOL
 
 
-def test_paged_fp8_decode_scaled_down():
+@pytest.mark.parametrize("two_pass", [False, True], ids=["one_pass", "dequant_then_persistent"])
+def test_paged_fp8_decode_scaled_down(two_pass):
     c = W.mla_cfg3(batch=4, n_q=2, h=128, topk=256, len_lo=300, len_hi=1500)
     out, lse = sparse_mla_fwd_paged(c.q.to(DEV), c.kv_cache.to(DEV), c.kv_scale.to(DEV), c.block_table.to(DEV),
                                     c.context_lens.to(DEV), c.indices.to(DEV), c.sm_scale, page_size=c.page_size,
-                                    check=True)
+                                    check=True, num_splits=1, two_pass=two_pass)
     ref_out, ref_lse = sparse_mla_fwd_paged_ref(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens,
                                                 c.indices, c.sm_scale, page_size=c.page_size)
     e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
@@ -219,11 +245,12 @@ def test_paged_fp8_decode_scaled_down():
     assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
 
 
-def test_paged_fp8_short_context_and_padding():
+@pytest.mark.parametrize("two_pass", [False, True], ids=["one_pass", "dequant_then_persistent"])
+def test_paged_fp8_short_context_and_padding(two_pass):
     c = W.mla_cfg3(batch=3, n_q=2, h=16, topk=128, len_lo=20, len_hi=100)   # topk > context: -1 padded
     out, lse = sparse_mla_fwd_paged(c.q.to(DEV), c.kv_cache.to(DEV), c.kv_scale.to(DEV), c.block_table.to(DEV),
                                     c.context_lens.to(DEV), c.indices.to(DEV), c.sm_scale, page_size=c.page_size,
-                                    check=True)
+                                    check=True, num_splits=1, two_pass=two_pass)
     ref_out, ref_lse = sparse_mla_fwd_paged_ref(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens,
                                                 c.indices, c.sm_scale, page_size=c.page_size)
     e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
