@@ -94,6 +94,9 @@ def load() -> C.CDLL:
             lib.ftb_gemm_rs_ctx_set_multicast.argtypes = [C.c_void_p, C.c_void_p]
             lib.ftb_gemm_rs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
                                         C.c_int64, C.c_void_p, C.c_void_p]
+            lib.ftb_gemm_rs_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                            C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+            lib.ftb_gemm_rs_fp8.restype = C.c_int
             lib.ftb_ipc_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_uint8)]
             lib.ftb_ipc_open.argtypes = [C.POINTER(C.c_uint8), C.POINTER(C.c_void_p)]
             lib.ftb_ipc_close.argtypes = [C.c_void_p]

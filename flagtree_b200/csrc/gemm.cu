@@ -745,6 +745,7 @@ struct ftb_gemm_rs_ctx {
   unsigned int* d_blk_counter;   // pull mode: arrivals per 128-row block
   void* mc_recv;                 // multicast address of the receive/partial buffers (NULL = push mode)
   unsigned int epoch;
+  int form;                      // 0 = not used yet, 1 = bf16 calls (ftb_gemm_rs), 2 = FP8 calls (ftb_gemm_rs_fp8)
 };
 
 extern "C" FTB_API int ftb_gemm_rs_workspace_bytes(int m, int n, int tp, int64_t* recv_bytes, int64_t* flag_bytes) {
@@ -770,6 +771,7 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
   c->shard_rows = m / tp;
   c->blocks_per_shard = c->shard_rows / gemm::BM;
   c->epoch = 0;
+  c->form = 0;
   for (int i = 0; i < tp; ++i) {
     if (!recv_ptrs[i] || !flag_ptrs[i]) { delete c; set_last_error("ftb_gemm_rs_ctx_create: null peer pointer"); return FTB_ERR_INVALID; }
     c->recv[i] = recv_ptrs[i];
@@ -806,6 +808,8 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
                                    int64_t lda, int64_t ldb, int64_t ldo, int32_t* status, void* stream) {
   if (!c || !a || !b || !out) { set_last_error("ftb_gemm_rs: null pointer"); return FTB_ERR_INVALID; }
   if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs: out alignment"); return FTB_ERR_INVALID; }
+  if (c->form == 2) { set_last_error("ftb_gemm_rs: this context serves FP8 calls (the flag words differ)"); return FTB_ERR_INVALID; }
+  c->form = 1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   c->epoch += 1;
   gemm::Params p;
@@ -825,6 +829,151 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
   p.mc_part = reinterpret_cast<const __nv_bfloat16*>(c->mc_recv);
   p.blk_counter = c->d_blk_counter;
   return launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Block-scaled FP8 GEMM + reduce-scatter (the FP8 shape family of the tensor-parallel path).
+//
+// Two phases per call, all kernels of this library: (1) the block-scaled FP8 GEMM writes this rank's whole
+// partial product [m, n] as bf16 into its own peer-mapped buffer and a one-warp kernel publishes "partial
+// e is complete" in every peer's flag words; (2) the reduce kernel waits (bounded) for the same word from
+// every peer and writes this rank's row shard as the sum over ranks: with an NVSwitch multicast mapping one
+// multimem.ld_reduce per 16 bytes (the switch adds the eight partials), else plain peer loads added in
+// fp32 in rank order.  When its last CTA is through, it tells every peer that their buffers have been read,
+// which is what the next call waits for before the GEMM overwrites the partial.  The exchange is not
+// overlapped with the GEMM yet (the reduce starts when every rank has finished its product).
+// Flag words of rank d in this form: [src] = last complete partial of rank src, [tp + src] = last call in
+// which rank src finished reading rank d's partial.  Every kernel here waits on other GPUs only.
+namespace ftb {
+namespace gemm {
+
+__global__ void rs_fp8_wait_kernel(const unsigned int* flags, int first, int tp, unsigned int target, int* status) {
+  const int i = threadIdx.x;
+  if (i >= tp) return;
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
+  const long long t0 = clock64();
+  while (ld_acquire_sys(flags + first + i) < target) {
+    if (clock64() - t0 > kWaitLimitCycles) {
+      if (status != nullptr) atomicCAS(status, 0, FTB_ERR_TIMEOUT);
+      return;
+    }
+  }
+}
+
+struct RsFp8Ptrs {
+  unsigned int* flags[MAX_TP];
+  const __nv_bfloat16* recv[MAX_TP];
+};
+
+__global__ void rs_fp8_publish_kernel(RsFp8Ptrs q, int tp, int word, unsigned int value) {
+  const int d = threadIdx.x;
+  if (d >= tp) return;
+  __threadfence_system();
+  st_release_sys(q.flags[d] + word, value);
+}
+
+__global__ void __launch_bounds__(256) rs_fp8_reduce_kernel(RsFp8Ptrs q, const __nv_bfloat16* mc_part, __nv_bfloat16* out,
+                                                           long long ldo, int shard_rows, int n, int rank, int tp,
+                                                           unsigned int epoch, unsigned int* counter, int* status) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
+  __syncthreads();
+  if (threadIdx.x < tp && !s_abort) {
+    // partial `epoch` of every rank is complete
+    const long long t0 = clock64();
+    while (ld_acquire_sys(q.flags[rank] + threadIdx.x) < epoch) {
+      if (clock64() - t0 > kWaitLimitCycles) {
+        s_abort = 1;
+        if (status != nullptr) atomicCAS(status, 0, FTB_ERR_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_abort) {
+    const int vec_per_row = n / 8;
+    const long long total = static_cast<long long>(shard_rows) * vec_per_row;
+    const long long row0 = static_cast<long long>(rank) * shard_rows;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+      const long long r = i / vec_per_row;
+      const int c8 = static_cast<int>(i - r * vec_per_row);
+      const long long off = (row0 + r) * n + c8 * 8;
+      uint4 o;
+      if (mc_part != nullptr) {
+        o = multimem_ld_reduce_bf16x8(mc_part + off);
+      } else {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int src = 0; src < tp; ++src) {
+          const uint4 v = *reinterpret_cast<const uint4*>(q.recv[src] + off);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            acc[2 * k] += __uint_as_float(w[k] << 16);
+            acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+          }
+        }
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+      }
+      *reinterpret_cast<uint4*>(out + r * ldo + c8 * 8) = o;
+    }
+  }
+  // the last CTA tells every peer that this rank has read their partials of this call
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(counter, 1u) == gridDim.x - 1u) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) *counter = 0u;
+    if (threadIdx.x < tp) st_release_sys(q.flags[threadIdx.x] + tp + rank, epoch);
+  }
+}
+
+}  // namespace gemm
+}  // namespace ftb
+
+extern "C" FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* c, const void* a, const void* b, const float* a_scale,
+                                       const float* b_scale, void* out, int k_local, int64_t lda, int64_t ldb,
+                                       int64_t a_scale_ld, int64_t b_scale_ld, int64_t ldo, int32_t* status, void* stream) {
+  if (!c || !a || !b || !a_scale || !b_scale || !out) { set_last_error("ftb_gemm_rs_fp8: null pointer"); return FTB_ERR_INVALID; }
+  if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs_fp8: out alignment"); return FTB_ERR_INVALID; }
+  if (c->form == 1) { set_last_error("ftb_gemm_rs_fp8: this context serves bf16 calls (the flag words differ)"); return FTB_ERR_INVALID; }
+  if ((c->n % 128) || (k_local % 128)) { set_last_error("ftb_gemm_rs_fp8: n and k_local must be multiples of 128"); return FTB_ERR_INVALID; }
+  c->form = 2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  c->epoch += 1;
+  gemm::RsFp8Ptrs q;
+  memset(&q, 0, sizeof(q));
+  for (int i = 0; i < c->tp; ++i) {
+    q.flags[i] = c->flags[i];
+    q.recv[i] = reinterpret_cast<const __nv_bfloat16*>(c->recv[i]);
+  }
+  // every peer has read the partial of the call before (their words start at [tp])
+  gemm::rs_fp8_wait_kernel<<<1, 32, 0, st>>>(c->flags[c->rank], c->tp, c->tp, c->epoch - 1u, status);
+  int rc = check_cuda(cudaGetLastError(), "rs_fp8_wait launch");
+  if (rc != FTB_OK) return rc;
+  ftb_gemm_fp8_args g;
+  memset(&g, 0, sizeof(g));
+  g.a = a; g.b = b; g.c = c->recv[c->rank];
+  g.a_scale = a_scale; g.b_scale = b_scale;
+  g.m = c->m; g.n = c->n; g.k = k_local;
+  g.lda = lda; g.ldb = ldb; g.ldc = c->n;
+  g.a_scale_ld = a_scale_ld; g.b_scale_ld = b_scale_ld;
+  g.status = status;
+  rc = ftb_gemm_fp8_blockscaled(&g, stream);
+  if (rc != FTB_OK) return rc;
+  gemm::rs_fp8_publish_kernel<<<1, 32, 0, st>>>(q, c->tp, c->rank, c->epoch);
+  rc = check_cuda(cudaGetLastError(), "rs_fp8_publish launch");
+  if (rc != FTB_OK) return rc;
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  gemm::rs_fp8_reduce_kernel<<<sms * 2, 256, 0, st>>>(q, reinterpret_cast<const __nv_bfloat16*>(c->mc_recv),
+                                                      reinterpret_cast<__nv_bfloat16*>(out), ldo, c->shard_rows, c->n, c->rank,
+                                                      c->tp, c->epoch, c->d_counter, status);
+  return check_cuda(cudaGetLastError(), "rs_fp8_reduce launch");
 }
 
 // ---- CUDA IPC helpers for callers that do not have a symmetric-memory allocator of their own.

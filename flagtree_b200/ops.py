@@ -333,6 +333,31 @@ class GemmRsContext:
         _lib.check(rc, "gemm_rs")
         return out
 
+    def fp8(self, a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Block-scaled FP8 form: A_r [M, K/tp] e4m3 with fp32 scales [M, (K/tp)/128], B_r [K/tp, N] e4m3 with
+        fp32 scales [(K/tp)/128, N/128]; returns this rank's rows of the sum of the dequantised products as
+        bf16.  A context serves either bf16 calls or FP8 calls."""
+        _require_cuda(a, a_scale, b, b_scale)
+        for t in (a, b):
+            assert t.dtype in (torch.uint8, torch.float8_e4m3fn), "operands must hold e4m3 bytes"
+        assert a.shape[0] == self.m and b.shape[1] == self.n and a.shape[1] == b.shape[0], "incompatible dimensions"
+        k = a.shape[1]
+        assert k % 128 == 0 and self.n % 128 == 0, "k and n must be multiples of the 128-wide scale blocks"
+        assert a_scale.shape == (self.m, k // 128) and b_scale.shape == (k // 128, self.n // 128)
+        assert a_scale.dtype == torch.float32 and b_scale.dtype == torch.float32
+        assert a.stride(1) == 1 and b.stride(1) == 1 and a_scale.stride(1) == 1 and b_scale.stride(1) == 1
+        if out is None:
+            out = torch.empty(self.m // self.tp, self.n, dtype=torch.bfloat16, device=a.device)
+        assert out.shape == (self.m // self.tp, self.n) and out.stride(1) == 1
+        with torch.cuda.device(a.device):
+            rc = _lib.load().ftb_gemm_rs_fp8(self._ctx, a.data_ptr(), b.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr(),
+                                             out.data_ptr(), k, a.stride(0), b.stride(0), a_scale.stride(0),
+                                             b_scale.stride(0), out.stride(0), self.status.data_ptr(),
+                                             C.c_void_p(_stream_ptr(a.device)))
+        _lib.check(rc, "gemm_rs_fp8")
+        return out
+
     def check(self):
         _check_status(self.status, "gemm_rs")
 

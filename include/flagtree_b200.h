@@ -187,6 +187,15 @@ FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* ctx, const void* a, const void* b, void
 
 /* CUDA IPC helpers for callers without a symmetric-memory allocator: allocate a zeroed device buffer
  * and export a 64-byte handle; open a peer's handle (enables peer access lazily); close; free. */
+/* Block-scaled FP8 form of the same collective: rank r passes A_r [m, k_local] e4m3 with fp32 scales per
+ * 1 x 128 block ([m, k_local / 128]) and B_r [k_local, n] e4m3 with fp32 scales per 128 x 128 block, and
+ * gets rows [r * m / tp, (r + 1) * m / tp) of sum_r dequant(A_r) . dequant(B_r) as bf16.  The reference has
+ * no counterpart (its fp8 matmul, python/triton/ops/matmul.py:162-228, is single-device and unscaled).  A
+ * context serves either ftb_gemm_rs or ftb_gemm_rs_fp8 calls, not both; n and k_local are multiples of 128. */
+FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* ctx, const void* a, const void* b, const float* a_scale,
+                            const float* b_scale, void* out, int k_local, int64_t lda, int64_t ldb,
+                            int64_t a_scale_ld, int64_t b_scale_ld, int64_t ldo, int32_t* status, void* stream);
+
 FTB_API int ftb_ipc_alloc(int64_t bytes, void** ptr, uint8_t handle[64]);
 FTB_API int ftb_ipc_open(const uint8_t handle[64], void** ptr);
 FTB_API int ftb_ipc_close(void* ptr);

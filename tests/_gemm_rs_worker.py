@@ -48,6 +48,26 @@ def main():
         ok = ok and err <= tol and err_nccl <= tol and same
         ctx.close()
         dist.barrier()
+    # block-scaled FP8 form (cfg5 family, scaled down): GEMM, then this library's own reduce-scatter kernels
+    from oracle.gemm_rs_ref import gemm_rs_fp8_ref
+    for (m, n, k_total) in [(world * 128, 256, world * 128), (world * 256, 1024, world * 384)]:
+        cases = [W.gemm_cfg5(tp=world, rank=r, m=m, n=n, k_total=k_total) for r in range(world)]
+        ref = gemm_rs_fp8_ref([c.a for c in cases], [c.a_scale for c in cases], [c.b for c in cases],
+                              [c.b_scale for c in cases])[rank]
+        ctx = GemmRsContext(m, n, None, dev, provider, protocol)
+        me = cases[rank]
+        a, b, a_s, b_s = me.a.to(dev), me.b.to(dev), me.a_scale.to(dev), me.b_scale.to(dev)
+        outs = [ctx.fp8(a, a_s, b, b_s).clone() for _ in range(3)]
+        torch.cuda.synchronize()
+        ctx.check()
+        err = (outs[0].float().cpu() - ref).abs().max().item()
+        scale = ref.abs().max().item()
+        same = all(torch.equal(outs[0], o) for o in outs[1:])
+        print(f"[rank {rank}] fp8 m={m} n={n} k={k_total} protocol={ctx.protocol}: err {err:.3e} scale {scale:.3e} "
+              f"repeat-identical {same}", flush=True)
+        ok = ok and err <= (world + 1) * 2 ** -8 * scale and same
+        ctx.close()
+        dist.barrier()
     t = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()
