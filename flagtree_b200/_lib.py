@@ -92,6 +92,7 @@ def load() -> C.CDLL:
                                                    C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
             lib.ftb_gemm_rs_ctx_destroy.argtypes = [C.c_void_p]
             lib.ftb_gemm_rs_ctx_set_multicast.argtypes = [C.c_void_p, C.c_void_p]
+            lib.ftb_gemm_rs_ctx_set_staged.argtypes = [C.c_void_p, C.c_int]
             lib.ftb_gemm_rs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
                                         C.c_int64, C.c_void_p, C.c_void_p]
             lib.ftb_gemm_rs_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,

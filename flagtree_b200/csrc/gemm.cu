@@ -745,7 +745,8 @@ struct ftb_gemm_rs_ctx {
   unsigned int* d_blk_counter;   // pull mode: arrivals per 128-row block
   void* mc_recv;                 // multicast address of the receive/partial buffers (NULL = push mode)
   unsigned int epoch;
-  int form;                      // 0 = not used yet, 1 = bf16 calls (ftb_gemm_rs), 2 = FP8 calls (ftb_gemm_rs_fp8)
+  int form;                      // 0 = not used yet, 1 = fused bf16 calls, 2 = staged calls (bf16 or FP8): the flag words differ
+  int staged;                    // bf16 calls: 0 = fused kernel (push or pull), 1 = staged (GEMM per shard group + one reduce)
 };
 
 extern "C" FTB_API int ftb_gemm_rs_workspace_bytes(int m, int n, int tp, int64_t* recv_bytes, int64_t* flag_bytes) {
@@ -772,6 +773,7 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
   c->blocks_per_shard = c->shard_rows / gemm::BM;
   c->epoch = 0;
   c->form = 0;
+  c->staged = 0;
   for (int i = 0; i < tp; ++i) {
     if (!recv_ptrs[i] || !flag_ptrs[i]) { delete c; set_last_error("ftb_gemm_rs_ctx_create: null peer pointer"); return FTB_ERR_INVALID; }
     c->recv[i] = recv_ptrs[i];
@@ -802,33 +804,6 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* c) {
   cudaFree(c->d_blk_counter);
   delete c;
   return FTB_OK;
-}
-
-extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b, void* out, int k_local,
-                                   int64_t lda, int64_t ldb, int64_t ldo, int32_t* status, void* stream) {
-  if (!c || !a || !b || !out) { set_last_error("ftb_gemm_rs: null pointer"); return FTB_ERR_INVALID; }
-  if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs: out alignment"); return FTB_ERR_INVALID; }
-  if (c->form == 2) { set_last_error("ftb_gemm_rs: this context serves FP8 calls (the flag words differ)"); return FTB_ERR_INVALID; }
-  c->form = 1;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  c->epoch += 1;
-  gemm::Params p;
-  memset(&p, 0, sizeof(p));
-  p.tp = c->tp; p.rank = c->rank; p.shard_rows = c->shard_rows; p.blocks_per_shard = c->blocks_per_shard;
-  for (int i = 0; i < c->tp; ++i) {
-    p.recv[i] = reinterpret_cast<__nv_bfloat16*>(c->recv[i]);
-    p.flags[i] = c->flags[i];
-  }
-  p.epoch = c->epoch;
-  const int n_blocks = (c->n + gemm::BN - 1) / gemm::BN;
-  p.flag_target = c->epoch * static_cast<unsigned int>(n_blocks) * 4u;   // 4 epilogue warps per tile
-  p.out = reinterpret_cast<__nv_bfloat16*>(out);
-  p.ldo = ldo;
-  p.counter = c->d_counter;
-  p.status = status;
-  p.mc_part = reinterpret_cast<const __nv_bfloat16*>(c->mc_recv);
-  p.blk_counter = c->d_blk_counter;
-  return launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -865,9 +840,10 @@ struct RsFp8Ptrs {
   const __nv_bfloat16* recv[MAX_TP];
 };
 
-__global__ void rs_fp8_publish_kernel(RsFp8Ptrs q, int tp, int word, unsigned int value) {
-  const int d = threadIdx.x;
-  if (d >= tp) return;
+// ranks d0 .. d0 + nd - 1 learn that this rank's partial of their rows is complete
+__global__ void rs_fp8_publish_kernel(RsFp8Ptrs q, int d0, int nd, int word, unsigned int value) {
+  const int d = d0 + static_cast<int>(threadIdx.x);
+  if (static_cast<int>(threadIdx.x) >= nd) return;
   __threadfence_system();
   st_release_sys(q.flags[d] + word, value);
 }
@@ -894,29 +870,53 @@ __global__ void __launch_bounds__(256) rs_fp8_reduce_kernel(RsFp8Ptrs q, const _
     const int vec_per_row = n / 8;
     const long long total = static_cast<long long>(shard_rows) * vec_per_row;
     const long long row0 = static_cast<long long>(rank) * shard_rows;
-    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-         i += static_cast<long long>(gridDim.x) * blockDim.x) {
-      const long long r = i / vec_per_row;
-      const int c8 = static_cast<int>(i - r * vec_per_row);
-      const long long off = (row0 + r) * n + c8 * 8;
-      uint4 o;
-      if (mc_part != nullptr) {
-        o = multimem_ld_reduce_bf16x8(mc_part + off);
-      } else {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int src = 0; src < tp; ++src) {
-          const uint4 v = *reinterpret_cast<const uint4*>(q.recv[src] + off);
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    constexpr int kU = 8;   // loads in flight per thread: one at a time moved 250 GB/s
+    for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * kU) {
+      uint4 o[kU];
+      long long off[kU], dst[kU];
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            acc[2 * k] += __uint_as_float(w[k] << 16);
-            acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+      for (int u = 0; u < kU; ++u) {
+        const long long i = i0 + u * stride;
+        const long long r = i < total ? i / vec_per_row : 0;
+        const int c8 = i < total ? static_cast<int>(i - r * vec_per_row) : 0;
+        off[u] = (row0 + r) * n + c8 * 8;
+        dst[u] = r * ldo + c8 * 8;
+      }
+      if (mc_part != nullptr) {
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+          if (i0 + u * stride < total) o[u] = multimem_ld_reduce_bf16x8(mc_part + off[u]);
+      } else {
+        float acc[kU][8];
+#pragma unroll
+        for (int u = 0; u < kU; ++u)
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
+        for (int src = 0; src < tp; ++src) {
+          uint4 v[kU];
+#pragma unroll
+          for (int u = 0; u < kU; ++u)
+            v[u] = (i0 + u * stride < total) ? *reinterpret_cast<const uint4*>(q.recv[src] + off[u]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int u = 0; u < kU; ++u) {
+            const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              acc[u][2 * k] += __uint_as_float(w[k] << 16);
+              acc[u][2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+            }
           }
         }
-        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+          o[u].x = pack_bf16x2(acc[u][0], acc[u][1]); o[u].y = pack_bf16x2(acc[u][2], acc[u][3]);
+          o[u].z = pack_bf16x2(acc[u][4], acc[u][5]); o[u].w = pack_bf16x2(acc[u][6], acc[u][7]);
+        }
       }
-      *reinterpret_cast<uint4*>(out + r * ldo + c8 * 8) = o;
+#pragma unroll
+      for (int u = 0; u < kU; ++u)
+        if (i0 + u * stride < total) *reinterpret_cast<uint4*>(out + dst[u]) = o[u];
     }
   }
   // the last CTA tells every peer that this rank has read their partials of this call
@@ -934,15 +934,15 @@ __global__ void __launch_bounds__(256) rs_fp8_reduce_kernel(RsFp8Ptrs q, const _
 }  // namespace gemm
 }  // namespace ftb
 
-extern "C" FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* c, const void* a, const void* b, const float* a_scale,
-                                       const float* b_scale, void* out, int k_local, int64_t lda, int64_t ldb,
-                                       int64_t a_scale_ld, int64_t b_scale_ld, int64_t ldo, int32_t* status, void* stream) {
-  if (!c || !a || !b || !a_scale || !b_scale || !out) { set_last_error("ftb_gemm_rs_fp8: null pointer"); return FTB_ERR_INVALID; }
-  if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs_fp8: out alignment"); return FTB_ERR_INVALID; }
-  if (c->form == 1) { set_last_error("ftb_gemm_rs_fp8: this context serves bf16 calls (the flag words differ)"); return FTB_ERR_INVALID; }
-  if ((c->n % 128) || (k_local % 128)) { set_last_error("ftb_gemm_rs_fp8: n and k_local must be multiples of 128"); return FTB_ERR_INVALID; }
-  c->form = 2;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+// Staged driver shared by the bf16 and FP8 forms.  The GEMM runs once per group of row shards, the groups in
+// rotated order (the group after this rank's own first, its own last), each launch writing rows of this rank's
+// partial [m, n] in its peer-mapped buffer; after a group the owners of its shards learn that this rank's
+// partial of their rows is complete.  When the own group is done only the stragglers and one pass over this
+// rank's shard are left: the reduce kernel.  `gemm_rows(row0, rows, c)` launches the GEMM of rows
+// [row0, row0 + rows) into c (row stride n).
+template <typename GemmRows>
+static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int64_t ldo, int32_t* status, cudaStream_t st) {
+  using namespace ftb;
   c->epoch += 1;
   gemm::RsFp8Ptrs q;
   memset(&q, 0, sizeof(q));
@@ -952,28 +952,110 @@ extern "C" FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* c, const void* a, const 
   }
   // every peer has read the partial of the call before (their words start at [tp])
   gemm::rs_fp8_wait_kernel<<<1, 32, 0, st>>>(c->flags[c->rank], c->tp, c->tp, c->epoch - 1u, status);
-  int rc = check_cuda(cudaGetLastError(), "rs_fp8_wait launch");
+  int rc = check_cuda(cudaGetLastError(), "rs wait launch");
   if (rc != FTB_OK) return rc;
-  ftb_gemm_fp8_args g;
-  memset(&g, 0, sizeof(g));
-  g.a = a; g.b = b; g.c = c->recv[c->rank];
-  g.a_scale = a_scale; g.b_scale = b_scale;
-  g.m = c->m; g.n = c->n; g.k = k_local;
-  g.lda = lda; g.ldb = ldb; g.ldc = c->n;
-  g.a_scale_ld = a_scale_ld; g.b_scale_ld = b_scale_ld;
-  g.status = status;
-  rc = ftb_gemm_fp8_blockscaled(&g, stream);
-  if (rc != FTB_OK) return rc;
-  gemm::rs_fp8_publish_kernel<<<1, 32, 0, st>>>(q, c->tp, c->rank, c->epoch);
-  rc = check_cuda(cudaGetLastError(), "rs_fp8_publish launch");
-  if (rc != FTB_OK) return rc;
+  // shards per GEMM launch: about 2048 rows, so that a launch fills the SMs a few times over
+  int g = 2048 / c->shard_rows;
+  if (g < 1) g = 1;
+  while (c->tp % g) --g;
+  const int n_groups = c->tp / g;
+  const int own = c->rank / g;
+  __nv_bfloat16* part = reinterpret_cast<__nv_bfloat16*>(c->recv[c->rank]);
+  for (int s = 1; s <= n_groups; ++s) {
+    const int gi = (own + s) % n_groups;
+    const long long row0 = static_cast<long long>(gi) * g * c->shard_rows;
+    rc = gemm_rows(row0, g * c->shard_rows, part + row0 * c->n);
+    if (rc != FTB_OK) return rc;
+    gemm::rs_fp8_publish_kernel<<<1, 32, 0, st>>>(q, gi * g, g, c->rank, c->epoch);
+    rc = check_cuda(cudaGetLastError(), "rs publish launch");
+    if (rc != FTB_OK) return rc;
+  }
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   gemm::rs_fp8_reduce_kernel<<<sms * 2, 256, 0, st>>>(q, reinterpret_cast<const __nv_bfloat16*>(c->mc_recv),
                                                       reinterpret_cast<__nv_bfloat16*>(out), ldo, c->shard_rows, c->n, c->rank,
                                                       c->tp, c->epoch, c->d_counter, status);
-  return check_cuda(cudaGetLastError(), "rs_fp8_reduce launch");
+  return check_cuda(cudaGetLastError(), "rs reduce launch");
+}
+
+extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b, void* out, int k_local,
+                                   int64_t lda, int64_t ldb, int64_t ldo, int32_t* status, void* stream) {
+  if (!c || !a || !b || !out) { set_last_error("ftb_gemm_rs: null pointer"); return FTB_ERR_INVALID; }
+  if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs: out alignment"); return FTB_ERR_INVALID; }
+  if (c->staged) {
+    if (c->form == 1) { set_last_error("ftb_gemm_rs: this context has served fused calls"); return FTB_ERR_INVALID; }
+    c->form = 2;
+    const int n = c->n;
+    auto rows = [&](long long row0, int m_rows, __nv_bfloat16* dst) -> int {
+      ftb_gemm_args g;
+      memset(&g, 0, sizeof(g));
+      g.a = static_cast<const __nv_bfloat16*>(a) + row0 * lda;
+      g.b = b;
+      g.c = dst;
+      g.m = m_rows; g.n = n; g.k = k_local;
+      g.lda = lda; g.ldb = ldb; g.ldc = n;
+      g.status = status;
+      return ftb_gemm_bf16(&g, stream);
+    };
+    return staged_gemm_rs(c, rows, out, ldo, status, reinterpret_cast<cudaStream_t>(stream));
+  }
+  if (c->form == 2) { set_last_error("ftb_gemm_rs: this context serves staged calls (the flag words differ)"); return FTB_ERR_INVALID; }
+  c->form = 1;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  c->epoch += 1;
+  gemm::Params p;
+  memset(&p, 0, sizeof(p));
+  p.tp = c->tp; p.rank = c->rank; p.shard_rows = c->shard_rows; p.blocks_per_shard = c->blocks_per_shard;
+  for (int i = 0; i < c->tp; ++i) {
+    p.recv[i] = reinterpret_cast<__nv_bfloat16*>(c->recv[i]);
+    p.flags[i] = c->flags[i];
+  }
+  p.epoch = c->epoch;
+  const int n_blocks = (c->n + gemm::BN - 1) / gemm::BN;
+  p.flag_target = c->epoch * static_cast<unsigned int>(n_blocks) * 4u;   // 4 epilogue warps per tile
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.counter = c->d_counter;
+  p.status = status;
+  p.mc_part = reinterpret_cast<const __nv_bfloat16*>(c->mc_recv);
+  p.blk_counter = c->d_blk_counter;
+  return launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
+}
+
+extern "C" FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* c, const void* a, const void* b, const float* a_scale,
+                                       const float* b_scale, void* out, int k_local, int64_t lda, int64_t ldb,
+                                       int64_t a_scale_ld, int64_t b_scale_ld, int64_t ldo, int32_t* status, void* stream) {
+  if (!c || !a || !b || !a_scale || !b_scale || !out) { set_last_error("ftb_gemm_rs_fp8: null pointer"); return FTB_ERR_INVALID; }
+  if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs_fp8: out alignment"); return FTB_ERR_INVALID; }
+  if (c->form == 1) { set_last_error("ftb_gemm_rs_fp8: this context serves fused bf16 calls (the flag words differ)"); return FTB_ERR_INVALID; }
+  if ((c->n % 128) || (k_local % 128)) { set_last_error("ftb_gemm_rs_fp8: n and k_local must be multiples of 128"); return FTB_ERR_INVALID; }
+  c->form = 2;
+  const int n = c->n;
+  auto rows = [&](long long row0, int m_rows, __nv_bfloat16* dst) -> int {
+    ftb_gemm_fp8_args g;
+    memset(&g, 0, sizeof(g));
+    g.a = static_cast<const uint8_t*>(a) + row0 * lda;
+    g.b = b;
+    g.c = dst;
+    g.a_scale = a_scale + row0 * a_scale_ld;
+    g.b_scale = b_scale;
+    g.m = m_rows; g.n = n; g.k = k_local;
+    g.lda = lda; g.ldb = ldb; g.ldc = n;
+    g.a_scale_ld = a_scale_ld; g.b_scale_ld = b_scale_ld;
+    g.status = status;
+    return ftb_gemm_fp8_blockscaled(&g, stream);
+  };
+  return staged_gemm_rs(c, rows, out, ldo, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// bf16 calls of this context use the staged protocol (1) or the fused kernel (0, the default).  Must be chosen
+// before the first call: the two use the flag words differently.
+extern "C" FTB_API int ftb_gemm_rs_ctx_set_staged(ftb_gemm_rs_ctx* c, int staged) {
+  if (!c) { set_last_error("ftb_gemm_rs_ctx_set_staged: null context"); return FTB_ERR_INVALID; }
+  if (c->epoch != 0) { set_last_error("ftb_gemm_rs_ctx_set_staged: must be called before the first call"); return FTB_ERR_INVALID; }
+  c->staged = staged ? 1 : 0;
+  return FTB_OK;
 }
 
 // ---- CUDA IPC helpers for callers that do not have a symmetric-memory allocator of their own.

@@ -314,8 +314,18 @@ class GemmRsContext:
         self.protocol = "pull" if int(have_mc.item()) == 1 else "push"
         if protocol == "pull" and self.protocol != "pull":
             raise RuntimeError("gemm_rs: protocol='pull' needs an NVSwitch multicast mapping on every rank")
-        if self.protocol == "pull":
+        # "staged" = GEMM per group of shards + one reduce kernel at the end (in-switch reduction when there is a
+        # multicast mapping, peer loads otherwise); "push" / "pull" = the fused kernel.  Measured at the cfg4
+        # per-rank shape the staged form is the slowest (0.44 ms at tp = 2, 0.48 ms at tp = 8), so "auto"
+        # keeps the fused kernel; the FP8 form always runs staged.
+        self.staged = protocol == "staged"
+        have_mc_any = torch.tensor([1 if self.recv.mc_ptr else 0], device=self.device)
+        dist.all_reduce(have_mc_any, op=dist.ReduceOp.MIN, group=group)
+        if self.protocol == "pull" or (self.staged and int(have_mc_any.item()) == 1):
             _lib.check(lib.ftb_gemm_rs_ctx_set_multicast(ctx, C.c_void_p(self.recv.mc_ptr)), "gemm_rs set_multicast")
+        if self.staged:
+            _lib.check(lib.ftb_gemm_rs_ctx_set_staged(ctx, 1), "gemm_rs set_staged")
+            self.protocol = "staged"
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -180,6 +180,11 @@ FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** ctx, int rank, int tp, int 
  * by pull: partial tiles stay in the producing rank's buffer and each owner fetches the cross-rank sum
  * with in-switch reduction (multimem.ld_reduce, fp32 accumulate).  NULL keeps the push protocol. */
 FTB_API int ftb_gemm_rs_ctx_set_multicast(ftb_gemm_rs_ctx* ctx, void* mc_recv_ptr);
+/* Staged protocol for the bf16 calls of a context (before its first call): the GEMM runs once per group of
+ * row shards in rotated order (own group last), the owners learn after each group that this rank's partial
+ * of their rows is complete, and one reduce kernel (in-switch reduction or peer loads) finishes the rank's
+ * shard.  0 = the fused kernel (default).  The FP8 form always works this way. */
+FTB_API int ftb_gemm_rs_ctx_set_staged(ftb_gemm_rs_ctx* ctx, int staged);
 FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* ctx);
 /* a [m, k_local] bf16, b [k_local, n] bf16, out [m/tp, n] bf16 (this rank's shard). */
 FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* ctx, const void* a, const void* b, void* out, int k_local,
