@@ -17,7 +17,6 @@
 // epilogue of tile i overlaps the MMAs of tile i+1.
 //   A stage: [128 rows x 128 B] K-major, 128B swizzle (one TMA box)
 //   B stage: 4 blocks of [64 k-rows x 128 B] (64 N columns each), used as the MN-major operand.
-#include <cstdlib>
 #include <cstring>
 
 #include "sm100.cuh"
@@ -954,10 +953,11 @@ static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int
   gemm::rs_fp8_wait_kernel<<<1, 32, 0, st>>>(c->flags[c->rank], c->tp, c->tp, c->epoch - 1u, status);
   int rc = check_cuda(cudaGetLastError(), "rs wait launch");
   if (rc != FTB_OK) return rc;
-  // shards per GEMM launch: about 2048 rows, so that a launch fills the SMs a few times over
-  int g = 2048 / c->shard_rows;
-  if (g < 1) g = 1;
-  while (c->tp % g) --g;
+  // Shards per GEMM launch.  Nothing overlaps the exchange in this protocol (a rank's own group comes last, so
+  // no reduce can start before the last launch), and every extra launch costs a partial wave of tiles: at the
+  // cfg4 shape on 8 GPUs one launch took 0.411 ms, two 0.431, four 0.483.  So: one group.  The loop below
+  // stays general for the day the reduce of a finished group runs beside the next launch.
+  int g = c->tp;
   const int n_groups = c->tp / g;
   const int own = c->rank / g;
   __nv_bfloat16* part = reinterpret_cast<__nv_bfloat16*>(c->recv[c->rank]);
