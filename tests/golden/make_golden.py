@@ -145,7 +145,7 @@ def case_paged(mod, seed, batch, h, n_pages, page, seq_len, splits):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the FlagTree checkout whose kernel source is executed")
     args = ap.parse_args()
     mod, tmp = _load_reference_kernels(args.reference)
     try:
