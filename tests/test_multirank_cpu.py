@@ -78,8 +78,23 @@ def _case_reduce_scatter_convention(rank, world):
     assert torch.allclose(out, ref, rtol=1e-6, atol=1e-8)
 
 
+def _case_reduce_scatter_fp8_convention(rank, world):
+    """Block-scaled FP8 form: the oracle's shard of rank r equals the reduce-scatter of the ranks' dequantised
+    partial products (the convention the staged kernels follow: partial per rank, sum over ranks, row shard)."""
+    from oracle.gemm_rs_ref import dequant_block_scaled, gemm_rs_fp8_ref
+    cases = [W.gemm_cfg5(tp=world, rank=r, m=world * 8, n=128, k_total=world * 128) for r in range(world)]
+    ref = gemm_rs_fp8_ref([c.a for c in cases], [c.a_scale for c in cases], [c.b for c in cases],
+                          [c.b_scale for c in cases])[rank]
+    me = cases[rank]
+    part = dequant_block_scaled(me.a, me.a_scale, 1, 128).float() @ dequant_block_scaled(me.b, me.b_scale, 128, 128).float()
+    out = torch.empty(8, 128)
+    dist.reduce_scatter_tensor(out, part)
+    assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
+
+
 @pytest.mark.parametrize("fn,port", [("_case_symmetric_exchange", 29611), ("_case_mla_token_sharding", 29612),
-                                     ("_case_reduce_scatter_convention", 29613)])
+                                     ("_case_reduce_scatter_convention", 29613),
+                                     ("_case_reduce_scatter_fp8_convention", 29614)])
 def test_two_ranks_gloo(fn, port):
     _spawn(fn, 2, port)
 
