@@ -120,6 +120,85 @@ def sparse_mla_fwd(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor,
     return out, lse
 
 
+_HOST_PIPES = {}
+
+
+def sparse_mla_fwd_host(q: torch.Tensor, kv: torch.Tensor, indices: torch.Tensor, sm_scale: Optional[float] = None,
+                        *, out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None,
+                        device: Optional[torch.device] = None, chunk_tokens: int = 512
+                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """`sparse_mla_fwd` for HOST tensors (the form a plugin boundary with host buffers needs): q [S_q, h, 576]
+    bf16, kv [S_kv, 576] bf16, indices [S_q, topk] int32 and the results out [S_q, h, 512] bf16, lse [S_q, h]
+    fp32 live in host memory (pinned memory makes the copies asynchronous).  The query tokens go through the
+    device in chunks of `chunk_tokens` on three streams: the host-to-device copy of chunk i + 1, the kernel of
+    chunk i and the device-to-host copy of chunk i - 1 run at the same time, so that a step costs about the
+    longer of the two copy directions instead of their sum plus the kernel.  The current stream waits for the
+    last copy; the caller synchronises it before reading `out` (as after any asynchronous copy)."""
+    assert not q.is_cuda and not kv.is_cuda and not indices.is_cuda, "host tensors expected"
+    assert q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and indices.dtype == torch.int32
+    if kv.dim() == 3:
+        kv = kv.reshape(kv.shape[0], -1)
+    s_q, h, _ = q.shape
+    topk = indices.shape[1]
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    if sm_scale is None:
+        sm_scale = D_QK ** -0.5
+    if out is None:
+        out = torch.empty(s_q, h, D_V, dtype=torch.bfloat16, pin_memory=True)
+    if lse is None:
+        lse = torch.empty(s_q, h, dtype=torch.float32, pin_memory=True)
+    ct = max(1, min(int(chunk_tokens), s_q))
+    key = (dev.index, ct, h, topk, kv.shape[0])
+    pipe = _HOST_PIPES.get(key)
+    if pipe is None:
+        with torch.cuda.device(dev):
+            pipe = {
+                "q": [torch.empty(ct, h, D_QK, dtype=torch.bfloat16, device=dev) for _ in range(2)],
+                "idx": [torch.empty(ct, topk, dtype=torch.int32, device=dev) for _ in range(2)],
+                "out": [torch.empty(ct, h, D_V, dtype=torch.bfloat16, device=dev) for _ in range(2)],
+                "lse": [torch.empty(ct, h, dtype=torch.float32, device=dev) for _ in range(2)],
+                "kv": torch.empty(kv.shape[0], D_QK, dtype=torch.bfloat16, device=dev),
+                "s_in": torch.cuda.Stream(dev), "s_c": torch.cuda.Stream(dev), "s_out": torch.cuda.Stream(dev),
+            }
+        _HOST_PIPES[key] = pipe
+    s_in, s_c, s_out = pipe["s_in"], pipe["s_c"], pipe["s_out"]
+    cur = torch.cuda.current_stream(dev)
+    for s in (s_in, s_c, s_out):
+        s.wait_stream(cur)          # nothing of this call overtakes earlier work of the caller's stream
+    ev_in = [None, None]            # chunk landed in staging buffer b
+    ev_c = [None, None]             # kernel on staging buffer b finished (its inputs may be overwritten)
+    ev_out = [None, None]           # results of staging buffer b are on their way home (dout[b] may be overwritten)
+    with torch.cuda.stream(s_in):
+        pipe["kv"].copy_(kv, non_blocking=True)
+    n_chunks = (s_q + ct - 1) // ct
+    for i in range(n_chunks):
+        b = i & 1
+        lo, hi = i * ct, min(s_q, (i + 1) * ct)
+        n = hi - lo
+        with torch.cuda.stream(s_in):
+            if ev_c[b] is not None:
+                s_in.wait_event(ev_c[b])
+            pipe["q"][b][:n].copy_(q[lo:hi], non_blocking=True)
+            pipe["idx"][b][:n].copy_(indices[lo:hi], non_blocking=True)
+            ev_in[b] = s_in.record_event()
+        with torch.cuda.stream(s_c):
+            s_c.wait_event(ev_in[b])
+            if ev_out[b] is not None:
+                s_c.wait_event(ev_out[b])
+            sparse_mla_fwd(pipe["q"][b][:n], pipe["kv"], pipe["idx"][b][:n], sm_scale, out=pipe["out"][b][:n],
+                           lse=pipe["lse"][b][:n])
+            ev_c[b] = s_c.record_event()
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_c[b])
+            out[lo:hi].copy_(pipe["out"][b][:n], non_blocking=True)
+            lse[lo:hi].copy_(pipe["lse"][b][:n], non_blocking=True)
+            ev_out[b] = s_out.record_event()
+    cur.wait_stream(s_out)
+    cur.wait_stream(s_c)
+    cur.wait_stream(s_in)
+    return out, lse
+
+
 def sparse_mla_fwd_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Tensor,
                          block_table: torch.Tensor, context_lens: torch.Tensor, indices: torch.Tensor,
                          sm_scale: Optional[float] = None, d_v: int = D_V, page_size: int = 64, *,

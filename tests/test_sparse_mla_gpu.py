@@ -198,6 +198,20 @@ def test_full_size_decode_fp8_sampled_sequences():
         assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
 
 
+def test_host_buffer_form_matches_device_form():
+    """sparse_mla_fwd_host (pinned host tensors in and out, chunks of query tokens pipelined over three streams)
+    gives the same bits as the device form, for a chunk size that does not divide the token count and for
+    two calls in a row on the same staging buffers."""
+    from flagtree_b200 import sparse_mla_fwd_host
+    c = W.mla_cfg2(device="cpu", s_q=700, s_kv=1024, h=128, topk=512)
+    out_d, lse_d = sparse_mla_fwd(c.q.to(DEV), c.kv.to(DEV), c.indices.to(DEV), c.sm_scale, check=True)
+    hq, hkv, hidx = c.q.pin_memory(), c.kv.pin_memory(), c.indices.pin_memory()
+    for _ in range(2):
+        out_h, lse_h = sparse_mla_fwd_host(hq, hkv, hidx, c.sm_scale, device=torch.device(DEV), chunk_tokens=192)
+        torch.cuda.synchronize()
+        assert torch.equal(out_h, out_d.cpu()) and torch.equal(lse_h, lse_d.cpu())
+
+
 def test_more_than_128_heads_and_strided_views():
     g = torch.Generator().manual_seed(11)
     q_big = torch.randn(3, 160, 640, generator=g).bfloat16()
