@@ -503,6 +503,7 @@ int launch_sparse_mla_pair(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_duo(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_duo2(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st);
+int launch_sparse_mla_stream64(const ftb_sparse_mla_args* a, cudaStream_t st);
 }  // namespace ftb
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -538,17 +539,19 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     set_last_error("ftb_sparse_mla_fwd: kv row stride must be a multiple of 8 elements");
     return FTB_ERR_INVALID;
   }
-  if (a->algo_id < 0 || a->algo_id > 6) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
+  if (a->algo_id < 0 || a->algo_id > 7) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
   if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
   // algo 0 = default; algo 1 = one CTA per (token, output half), which is also the kernel of the FP8 paged
   // form, of the split form and of the debug score tap; algo 2 = CTA pair sharing one MMA (cta_group::2);
   // algo 3 = role-split CTA pair (scores in one CTA, values in the other); algo 4 = the same with Q in
-  // tensor memory and TMA row gathers; algo 5 = algo 4 as persistent pairs (the default).
+  // tensor memory and TMA row gathers; algo 5 = algo 4 as persistent pairs (the default); algo 7 = algo 5
+  // with tiles of 64 rows in rings two tiles deep.
   if (!a->kv_is_fp8 && a->dbg_scores == nullptr && a->n_splits <= 1) {
     if (a->algo_id == 2) return launch_sparse_mla_pair(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 3) return launch_sparse_mla_duo(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 4) return launch_sparse_mla_duo2(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 5) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));
+    if (a->algo_id == 7) return launch_sparse_mla_stream64(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 0) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));   // fastest so far
   }
   MlaParams p;

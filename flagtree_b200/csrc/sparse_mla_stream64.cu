@@ -1,0 +1,822 @@
+// Top-k sparse MLA forward, persistent role-split CTA pairs with tiles of 64 rows (bf16 KV).
+//
+// The same pair as in sparse_mla_stream.cu (CTA 0: S = Q.K^T with Q in tensor memory and the softmax; P goes
+// to CTA 1 by bulk copies over distributed shared memory; CTA 1: O += P.V), but a tile is 64 gathered rows
+// instead of 128, so that the rings of both CTAs hold TWO tiles in the same shared memory.  With one tile in
+// the ring a slot can only be refilled after its own MMAs, and the refill (a warp-wide gather4 and its
+// landing, about 4500 cycles) sits on the critical path; with two tiles a slot has two tile periods for it.
+// Everything on the score side exists twice, once per tile parity: K slots, score buffer in tensor memory,
+// MMA issuer warp (one thread cannot issue 128x64x16 MMAs at the tensor rate, two can), softmax group of four
+// warps with one thread per head row.  The running maximum of a head row is handed from tile to tile, i.e.
+// from group to group, through shared memory (m_sh / m_ready); each group keeps its own partial row sum in
+// the reference of the maximum it last used and the two are combined at the end of the token.
+//
+// Warps (608 threads per CTA): CTA 0: 0-3 softmax of even tiles, 4-7 softmax of odd tiles, 8 and 18 MMA
+// issuers (even / odd tiles), 9-17 K producers (16 lanes gather per tile; each also loads its block of Q, 9-12
+// move Q to TMEM).  CTA 1: 0-3 correction, 4 relay, 8 MMA issuer, 9-16 V producers, 0-7 and 9-16 epilogue.
+// Every wait is bounded; a wait that runs out sets the abort flag, after which every later wait returns at
+// once and the status word reports a timeout.
+//
+// Parity waits: a thread may only wait for phase n of a barrier that has completed phase n - 1.  The comments
+// at the waits say why that holds; it is the reason for four (not two) pv_done barriers.
+#include "sm100.cuh"
+#include "tmap.cuh"
+
+namespace ftb {
+
+void set_last_error(const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+
+namespace mla7 {
+
+constexpr int kDqk = 576;
+constexpr int kNChunk = 9;
+constexpr int kNT = 64;                        // gathered rows per tile
+constexpr int kQBlock = 128 * 128;             // 16384: [128 heads x 128 B]
+constexpr int kKSlot = kNT * 128;              // 8192: [64 rows x 128 B]; block c of a tile of parity p sits at c * 16384 + p * 8192
+constexpr int kNV = 4;                         // V ring slabs: two tiles of two slabs; slab s of tile G in slot (G & 1) * 2 + s
+constexpr int kVSlabRows = 32;
+constexpr int kVBlock = kVSlabRows * 128;      // 4096: one 64-column block of a slab
+constexpr int kVSlab = 8 * kVBlock;            // 32768
+constexpr int kPBuf = kQBlock;                 // 16384: P [128 heads x 64 rows] bf16
+constexpr int kNP = 4;                         // P buffers (tile G uses buffer G & 3), here and in CTA 1
+constexpr int kBatch = 64;                     // tokens whose tile counts are found in one go
+// CTA 0 layout: K ring (two tiles) | P staging x 4 | misc (Q block c passes through both slots of block c).
+// CTA 1 layout: V ring (two tiles) | P x 4 | epilogue staging | misc; the epilogue also stages in the P buffer
+// of the token's last tile.
+constexpr int kOff0K = 0;
+constexpr int kOff0P = kOff0K + kNChunk * 2 * kKSlot;      // 147456
+constexpr int kOff0Misc = kOff0P + kNP * kPBuf;            // 212992
+constexpr int kOff1P = kNV * kVSlab;                       // 131072
+constexpr int kOff1E = kOff1P + kNP * kPBuf;               // 196608
+constexpr int kOff1Misc = kOff1E + 4 * 4096;               // 212992
+constexpr int kMiscBytes = 6144;
+constexpr int kSmemBytes = kOff0Misc + kMiscBytes + 1024;   // misc + alignment slack
+constexpr int kThreads = 608;
+constexpr int kWarps = kThreads / 32;
+constexpr uint32_t kColQ = 0;                  // TMEM columns of CTA 0: Q (288), then the two score buffers
+constexpr uint32_t kColS = 320;                // parity p at kColS + 64 p
+
+struct Params {
+  const int32_t* indices;
+  float* lse;
+  int s_q, h, s_kv, topk;
+  long long idx_st, lse_st;
+  float scale_log2;
+  int lse_base2;
+  int* status;
+};
+
+struct Misc0 {   // CTA 0
+  unsigned long long k_full[2][kNChunk];   // one arrival announcing 8 KB of gathers
+  unsigned long long k_free[2][kNChunk];   // tcgen05.commit of the issuer of that parity
+  unsigned long long s_full[2];            // tcgen05.commit
+  unsigned long long s_free[2];            // 4 softmax warps
+  unsigned long long p_free[kNP];          // relay warp of CTA 1 (remote arrival)
+  unsigned long long q_full[kNChunk];      // one arrival announcing the tile load of Q block c
+  unsigned long long q_copied[kNChunk];    // 4 copier warps: Q block c is in TMEM, its slots are free
+  unsigned long long epi_done[2];          // CTA 1 (remote arrival): the epilogue of token t (t % 2) is over
+  unsigned long long m_ready[2][4];        // softmax warp w of group p: m_sh[p] holds the maxima after its tile
+  uint32_t tmem_base;
+  int abort_flag;
+  int bad_index;
+  int pad;
+  uint32_t valid_mask[8][2];               // per tile (mod 8): 64 validity bits
+  unsigned short nt[kBatch];               // tiles per token of the current batch
+  float m_sh[2][128];                      // running maximum of every head row after the last tile of group p
+  float x_m[2][128];                       // token end (t % 2): group 1's reference and partial row sum
+  float x_l[2][128];
+  alignas(16) float alpha_stage[kNP][128]; // rescale factors of a tile on their way to CTA 1 (sent with P)
+};
+struct Misc1 {   // CTA 1
+  unsigned long long v_full[kNV];          // one arrival announcing 32 KB of gathers
+  unsigned long long v_free[kNV];          // tcgen05.commit
+  unsigned long long p_full[kNP];          // 4 softmax warps of CTA 0 (remote arrivals, each expecting its 4 KB bulk copy)
+  unsigned long long corr_done[kNP];       // 4 correction warps
+  unsigned long long pv_done[4];           // tcgen05.commit, tile G on barrier G & 3
+  unsigned long long fin[2];               // 4 softmax warps of CTA 0: 1/l of token t (t % 2) is in place
+  unsigned long long o_free;               // 16 epilogue warps: the accumulator has been read
+  unsigned long long stg_free[8];          // epilogue warp w < 8: its staging piece is free for warp 9 + w
+  unsigned long long stg_back[4];          // epilogue warp 13 + k: staging piece 4 + k is free for warp 4 + k (next token)
+  unsigned long long epi_cnt;              // 16 epilogue warps: the output of the token has left the staging area
+  uint32_t tmem_base;
+  int abort_flag;
+  int pad[2];
+  unsigned short nt[kBatch];
+  alignas(16) float alpha[kNP][128];       // rescale factor of the tile, written by bulk copies from CTA 0
+  float inv_l[2][128];                     // final 1/l of token t (t % 2)
+};
+static_assert(sizeof(Misc0) <= kMiscBytes && sizeof(Misc1) <= kMiscBytes, "misc area");
+static_assert(kOff1Misc == kOff0Misc, "both layouts end at the same offset");
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Four rows (indices r0..r3) x 64 columns starting at column `col` -> 512 contiguous bytes of shared memory.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* tmap, uint32_t bar, int col, int r0, int r1, int r2, int r3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(tmap), "r"(bar), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+      : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Remote arrival that also announces `bytes` of bulk-copy traffic to the barrier of another CTA of the
+// cluster.  Relaxed: everything the waiter reads arrives through the announced bulk copies (the byte count
+// completes the phase); a release at cluster scope made the arriving thread wait about 2000 cycles.
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes) : "memory");
+}
+// Remote arrival that only passes a buffer back (nothing written by this thread has to become visible).
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// bulk copy local shared memory -> shared memory of another CTA; completes (byte count) on that CTA's barrier
+__device__ __forceinline__ void bulk_copy_to_cluster(uint32_t dst_cluster, uint32_t src_cta, uint32_t bytes, uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst_cluster), "r"(src_cta), "r"(bytes), "r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until the bulk stores of this thread have read their shared-memory source
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+// 2^(from - to) for running maxima with from <= to; 0 when nothing has been seen under `from` yet
+__device__ __forceinline__ float rescale(float from, float to) {
+  return (from == -INFINITY) ? 0.0f : ((from == to) ? 1.0f : fast_exp2(from - to));
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+sparse_mla_stream64_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
+                           const __grid_constant__ CUtensorMap tm_o, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - raw_addr);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cta = static_cast<int>(cluster_ctarank());
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  Misc0* m0 = reinterpret_cast<Misc0*>(sm + kOff0Misc);
+  Misc1* m1 = reinterpret_cast<Misc1*>(sm + kOff1Misc);
+  // abort_flag / tmem_base / nt sit at different offsets in the two layouts: pick this CTA's
+  volatile int* abort_flag = cta == 0 ? &m0->abort_flag : &m1->abort_flag;
+  uint32_t* tmem_base_p = cta == 0 ? &m0->tmem_base : &m1->tmem_base;
+  unsigned short* nt = cta == 0 ? m0->nt : m1->nt;
+
+  if (tid == 0) {
+    *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
+    if (cta == 0) {
+      m0->bad_index = 0;
+      for (int q = 0; q < 2; ++q) {
+        for (int i = 0; i < kNChunk; ++i) { mbar_init(smem_u32(&m0->k_full[q][i]), 1); mbar_init(smem_u32(&m0->k_free[q][i]), 1); }
+        mbar_init(smem_u32(&m0->s_full[q]), 1);
+        mbar_init(smem_u32(&m0->s_free[q]), 4);
+        mbar_init(smem_u32(&m0->epi_done[q]), 1);
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&m0->m_ready[q][i]), 1);
+      }
+      for (int i = 0; i < kNChunk; ++i) { mbar_init(smem_u32(&m0->q_full[i]), 1); mbar_init(smem_u32(&m0->q_copied[i]), 4); }
+      for (int i = 0; i < kNP; ++i) mbar_init(smem_u32(&m0->p_free[i]), 1);
+    } else {
+      for (int i = 0; i < kNV; ++i) { mbar_init(smem_u32(&m1->v_full[i]), 1); mbar_init(smem_u32(&m1->v_free[i]), 1); }
+      for (int i = 0; i < kNP; ++i) {
+        mbar_init(smem_u32(&m1->p_full[i]), 4);
+        mbar_init(smem_u32(&m1->corr_done[i]), 4);
+        mbar_init(smem_u32(&m1->pv_done[i]), 1);
+      }
+      for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&m1->fin[i]), 4);
+      mbar_init(smem_u32(&m1->o_free), 16);
+      for (int i = 0; i < 8; ++i) mbar_init(smem_u32(&m1->stg_free[i]), 1);
+      for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&m1->stg_back[i]), 1);
+      mbar_init(smem_u32(&m1->epi_cnt), 16);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (*abort_flag) return;   // an earlier launch failed: both CTAs read the same status word
+
+  if (warp == 8) {
+    tmem_alloc(smem_u32(tmem_base_p), 512u);
+    tmem_relinquish();
+    tc_fence_before();
+  }
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_base_p;
+  // tokens of this pair: pair, pair + n_pairs, ...  (the host launches no more pairs than tokens)
+  const int my_tokens = (p.s_q - pair + n_pairs - 1) / n_pairs;
+  uint32_t gt = 0;   // tiles processed before the current token: every role counts the same way
+
+  for (int batch0 = 0; batch0 < my_tokens; batch0 += kBatch) {
+    const int nb = min(kBatch, my_tokens - batch0);
+    // ------------------------------------------------------------------ tiles per token of this batch
+    for (int t = warp; t < nb; t += kWarps) {
+      const int tok = pair + (batch0 + t) * n_pairs;
+      const int32_t* idx_row = p.indices + static_cast<long long>(tok) * p.idx_st;
+      int local = 0;
+      for (int j = lane; j < p.topk; j += 32)
+        if (idx_row[j] >= 0) local = j + 1;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) local = max(local, __shfl_xor_sync(0xffffffffu, local, o));
+      // at least one tile (entirely masked if the token selects nothing): every stage of the pipeline
+      // then runs once per token and the hand-overs between tokens need no special case
+      if (lane == 0) nt[t] = static_cast<unsigned short>(min(65535, max(1, (local + kNT - 1) / kNT)));
+    }
+    __syncthreads();
+
+    if (cta == 0) {
+      // ===================================================================== CTA 0: scores
+      const uint32_t k_s = base + kOff0K;
+      if (warp < 8) {
+        // -------------------------------------------------------------- softmax: group g takes the tiles of parity g,
+        // thread = head row (TMEM lane), all 64 columns of the tile
+        const int grp = warp >> 2;
+        const int wq = warp & 3;
+        const int rowi = wq * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>(wq * 32);
+        const uint32_t p_remote = mapa_shared(base + kOff1P, 1);
+        const uint32_t p_local = base + kOff0P;
+        const uint32_t alpha_remote = mapa_shared(smem_u32(&m1->alpha[0][0]), 1);
+        const uint32_t invl_remote = mapa_shared(smem_u32(&m1->inv_l[0][0]), 1);
+        const uint32_t p_full_r0 = mapa_shared(smem_u32(&m1->p_full[0]), 1);
+        const uint32_t fin_r[2] = {mapa_shared(smem_u32(&m1->fin[0]), 1), mapa_shared(smem_u32(&m1->fin[1]), 1)};
+        const uint32_t my_ready = smem_u32(&m0->m_ready[grp][wq]);
+        const uint32_t other_ready = smem_u32(&m0->m_ready[grp ^ 1][wq]);
+        const uint32_t s_full = smem_u32(&m0->s_full[grp]), s_free = smem_u32(&m0->s_free[grp]);
+        const uint32_t t_s = tmem_addr(tmem, lane_base, kColS + grp * 64);
+        for (int t = 0; t < nb; ++t) {
+          const int ti = batch0 + t;
+          const int tok = pair + ti * n_pairs;
+          const int n_tiles = nt[t];
+          // 1/l and the `fin` barrier of parity ti % 2 were last used by token ti - 2: its epilogue is over
+          if (ti >= 2) mbar_wait(smem_u32(&m0->epi_done[ti & 1]), ((ti >> 1) - 1) & 1u, abort_flag);
+          float m_mine = -INFINITY, l_run = 0.0f;   // this group's partial row sum, in the reference m_mine
+          for (int i = 0; i < n_tiles; ++i) {
+            const uint32_t G = gt + i;
+            if (static_cast<int>(G & 1u) != grp) continue;
+            const int b = G & 3;
+            mbar_wait(s_full, (G >> 1) & 1u, abort_flag);
+            tc_fence_after();
+            const uint32_t vm0 = m0->valid_mask[G & 7][0], vm1 = m0->valid_mask[G & 7][1];
+            const bool all_valid = (vm0 & vm1) == 0xffffffffu;      // uniform over the group
+            // copy the 64 scores of this row to registers and hand the score buffer back at once
+            uint32_t sr[2][32];
+            tmem_ld32(t_s, sr[0]);
+            tmem_ld32(t_s + 32, sr[1]);
+            tmem_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);
+            float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              if (all_valid) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) mxa[j & 3] = fmaxf(mxa[j & 3], __uint_as_float(sr[q][j]));
+              } else {
+                const uint32_t vm = q == 0 ? vm0 : vm1;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if ((vm >> j) & 1u) mxa[j & 3] = fmaxf(mxa[j & 3], __uint_as_float(sr[q][j]));
+              }
+            }
+            const float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
+            // The maximum after tile G - 1 comes from the other group (same rows, warp wq of that group).  Every
+            // tile waits for its predecessor, the first tile of a token too (it only ignores the value), so
+            // that the barrier is followed phase by phase.
+            if (G >= 1) mbar_wait(other_ready, ((G - 1) >> 1) & 1u, abort_flag);
+            const float m_prev = (i == 0) ? -INFINITY : m0->m_sh[grp ^ 1][rowi];
+            // Lazy maximum: only move the reference when it grows by more than 2^8, so that the
+            // accumulator in the other CTA is rarely rescaled (P stays below 256, exact enough in bf16/fp32).
+            const float m_cand = fmaxf(m_prev, mx * p.scale_log2);
+            float alpha = 1.0f, m_new = m_prev;
+            if (m_cand > m_prev + 8.0f || m_prev == -INFINITY) {
+              alpha = (m_prev == -INFINITY) ? 0.0f : fast_exp2(m_prev - m_cand);
+              m_new = m_cand;
+            }
+            m0->m_sh[grp][rowi] = m_new;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(my_ready);
+            const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+            if (m_mine != m_new) { l_run *= rescale(m_mine, m_new); m_mine = m_new; }
+            // P buffer b of CTA 1 was last read by P.V of tile G-4; the staging buffer b was last sent for
+            // tile G-4 too, and that P.V came after the arrival of the copy.  Buffers b and b ^ 2 belong to
+            // this group alone, so the barrier is followed phase by phase.
+            if (G >= 4) mbar_wait(smem_u32(&m0->p_free[b]), ((G >> 2) - 1) & 1u, abort_flag);
+            float psa[2] = {0.0f, 0.0f};
+            const uint32_t p_row = p_local + b * kPBuf + rowi * 128;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const uint32_t vm = all_valid ? 0xffffffffu : (q == 0 ? vm0 : vm1);
+              uint32_t pk[16];
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                float a0 = fast_exp2(fmaf(__uint_as_float(sr[q][j]), p.scale_log2, -m_use));
+                float a1 = fast_exp2(fmaf(__uint_as_float(sr[q][j + 1]), p.scale_log2, -m_use));
+                if (!all_valid) {
+                  a0 = ((vm >> j) & 1u) ? a0 : 0.0f;
+                  a1 = ((vm >> (j + 1)) & 1u) ? a1 : 0.0f;
+                }
+                psa[(j >> 1) & 1] += a0 + a1;
+                pk[j >> 1] = pack_bf16x2(a0, a1);
+              }
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const int chunk = q * 4 + c;
+                st_shared_v4(p_row + ((chunk ^ (rowi & 7)) << 4), pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+              }
+            }
+            l_run += psa[0] + psa[1];
+            m0->alpha_stage[b][rowi] = alpha;
+            fence_proxy_async_smem();   // the bulk copies read this warp's rows through the async proxy
+            __syncwarp();
+            if (lane == 0) {
+              // this warp's 32 rows are 4 KB in a row, here and in CTA 1; its 32 rescale factors go the same way
+              const uint32_t off = b * kPBuf + lane_base * 128;
+              mbar_arrive_expect_tx_cluster(p_full_r0 + b * 8, 32 * 128 + 128);
+              bulk_copy_to_cluster(p_remote + off, p_local + off, 32 * 128, p_full_r0 + b * 8);
+              bulk_copy_to_cluster(alpha_remote + (b * 128 + lane_base) * 4, smem_u32(&m0->alpha_stage[b][lane_base]), 128, p_full_r0 + b * 8);
+            }
+            __syncwarp();
+          }
+          gt += n_tiles;
+          // end of the token: group 1 hands its reference and partial sum to group 0, which writes 1/l and LSE
+          if (grp == 1) { m0->x_m[ti & 1][rowi] = m_mine; m0->x_l[ti & 1][rowi] = l_run; }
+          named_bar_sync(2, 256);
+          if (grp == 0) {
+            const float m_b = m0->x_m[ti & 1][rowi], l_b = m0->x_l[ti & 1][rowi];
+            const float m_fin = fmaxf(m_mine, m_b);     // the reference of the accumulator: maxima only grow
+            const float l_tot = l_run * rescale(m_mine, m_fin) + l_b * rescale(m_b, m_fin);
+            const float inv_l = (l_tot > 0.0f) ? 1.0f / l_tot : 0.0f;
+            st_cluster_f32(invl_remote + ((ti & 1) * 128 + rowi) * 4, inv_l);
+            if (rowi < p.h) {
+              float v = -INFINITY;
+              if (l_tot > 0.0f) {
+                const float l2 = m_fin + log2f(l_tot);
+                v = p.lse_base2 ? l2 : l2 * 0.6931471805599453f;
+              }
+              p.lse[static_cast<long long>(tok) * p.lse_st + rowi] = v;
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(fin_r[ti & 1]);
+          }
+        }
+      } else if (warp == 8 || warp == 18) {
+        // -------------------------------------------------------------- Q.K^T issuers: warp 8 even tiles, warp 18 odd tiles
+        // Straight-line code per tile (block c of parity par always sits in the same place): the descriptors
+        // differ in their low word only and every offset is a compile-time constant.
+        if (lane == 0) {
+          const int par = warp == 8 ? 0 : 1;
+          constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, kNT, 0, 0);
+          const uint64_t bd0 = smem_desc_sw128(k_s + par * kKSlot, 16, 1024);
+          const uint32_t bd_lo = static_cast<uint32_t>(bd0), bd_hi = static_cast<uint32_t>(bd0 >> 32);
+          const uint32_t t_s = tmem + kColS + par * 64, t_q = tmem + kColQ;
+          const uint32_t k_full0 = smem_u32(&m0->k_full[par][0]), k_free0 = smem_u32(&m0->k_free[par][0]);
+          const uint32_t s_full = smem_u32(&m0->s_full[par]), s_free = smem_u32(&m0->s_free[par]);
+          for (int t = 0; t < nb; ++t) {
+            const int n_tiles = nt[t];
+            for (int i = 0; i < n_tiles; ++i) {
+              const uint32_t G = gt + i;
+              if (static_cast<int>(G & 1u) != par) continue;
+              const uint32_t ph = (G >> 1) & 1u;
+              // the score buffer of this parity: the softmax of tile G-2 has copied it to registers
+              if (G >= 2) mbar_wait(s_free, ph ^ 1u, abort_flag);
+#pragma unroll
+              for (int cc = 0; cc < kNChunk; ++cc) {
+                mbar_wait(k_full0 + cc * 8, ph, abort_flag);
+                tc_fence_after();
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  const uint32_t lo = bd_lo + ((cc * 2 * kKSlot + k * 32) >> 4);
+                  if (cc == 0 && k == 0) umma_f16_ts_lohi<false>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+                  else umma_f16_ts_lohi<true>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+                }
+                umma_commit(k_free0 + cc * 8);
+              }
+              umma_commit(s_full);
+            }
+            gt += n_tiles;
+          }
+        }
+      } else {
+        // -------------------------------------------------------------- K producers (warps 9-17)
+        // warp 9+c fetches 64-column block c of every tile; lane l < 16 owns tile rows 4l..4l+3 (one gather4).
+        // Between tokens the hand-over runs block by block: as soon as block c of the last two tiles (one of
+        // either parity: Q in tensor memory is read by both issuers) has been multiplied, warp 9+c loads
+        // block c of the next token's Q into the two slots of block c (q_full[c]); warps 9-12 (TMEM lane
+        // quarters 1, 2, 3, 0) move it to the Q columns of block c in tensor memory (q_copied[c]), after
+        // which the slots take block c of the next token's first two tiles.  The MMA issuers need no extra
+        // wait: k_full[.][c] of those tiles cannot complete before q_copied[c].
+        const int c = warp - 9;
+        const bool copier = c < 4;
+        const bool gl = lane < 16;
+        for (int t = 0; t < nb; ++t) {
+          const int ti = batch0 + t;
+          const int tok = pair + ti * n_pairs;
+          const int n_tiles = nt[t];
+          const int32_t* idx_row = p.indices + static_cast<long long>(tok) * p.idx_st;
+          int nxt[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) nxt[j] = (gl && 4 * lane + j < p.topk) ? idx_row[4 * lane + j] : -1;
+          // one tile: resolve this lane's four rows, then gather them once the slot is free
+          auto issue_tile = [&](int i) {
+            const uint32_t G = gt + i;
+            const int par = G & 1;
+            int row[4];
+            uint32_t nib = 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const bool ok = nxt[j] >= 0 && nxt[j] < p.s_kv;
+              if (c == 0 && nxt[j] >= p.s_kv) m0->bad_index = 1;
+              row[j] = ok ? nxt[j] : 0;
+              nib |= ok ? (1u << j) : 0u;
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int jn = (i + 1) * kNT + 4 * lane + j;
+              nxt[j] = (gl && i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+            }
+            // the slot held block c of tile G-2 (after a token boundary the Q block passed through it as
+            // well, and the caller has seen q_copied[c]); this warp follows k_free[par][c] phase by phase
+            if (G >= 2) mbar_wait(smem_u32(&m0->k_free[par][c]), ((G >> 1) - 1) & 1u, abort_flag);
+            if (c == 0) {
+              // 64 validity bits of the tile: word w = rows 32w..32w+31 = lanes 8w..8w+7, four bits each
+              // (lanes 16-31 hold no rows and contribute nothing; they fold onto words that nobody writes).
+              // Written after the wait above: block 0 of tile G-2 has been multiplied, so its issuer had seen
+              // the softmax of tile G-4 hand back the score buffer, and that softmax read its mask before;
+              // the mask ring is eight deep.
+              uint32_t v = nib << ((lane & 7) * 4);
+              v |= __shfl_xor_sync(0xffffffffu, v, 1);
+              v |= __shfl_xor_sync(0xffffffffu, v, 2);
+              v |= __shfl_xor_sync(0xffffffffu, v, 4);
+              if (gl && (lane & 7) == 0) m0->valid_mask[G & 7][lane >> 3] = v;
+            }
+            const uint32_t full = smem_u32(&m0->k_full[par][c]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive_expect_tx(full, kKSlot);
+            __syncwarp();
+            if (gl) tma_gather4(k_s + c * 2 * kKSlot + par * kKSlot + lane * 512, &tm_kv, full, c * 64, row[0], row[1], row[2], row[3]);
+            __syncwarp();
+          };
+          // Q block c of this token: both slots of block c and the Q columns of block c are free once block c
+          // of the previous token's last two tiles has been multiplied
+          auto load_q_block = [&]() {
+            if (lane == 0) {
+              if (gt >= 2) mbar_wait(smem_u32(&m0->k_free[(gt - 2) & 1][c]), ((gt - 2) >> 1) & 1u, abort_flag);
+              if (gt >= 1) mbar_wait(smem_u32(&m0->k_free[(gt - 1) & 1][c]), ((gt - 1) >> 1) & 1u, abort_flag);
+              const uint32_t qf = smem_u32(&m0->q_full[c]);
+              mbar_arrive_expect_tx(qf, static_cast<uint32_t>(p.h * 128));
+              tma_load_3d(k_s + c * kQBlock, &tm_q, qf, c * 64, 0, tok);
+            }
+            __syncwarp();
+          };
+          load_q_block();
+          if (!copier) {
+            mbar_wait(smem_u32(&m0->q_copied[c]), ti & 1u, abort_flag);
+            issue_tile(0);
+          } else {
+            // shared memory -> TMEM: thread = head row (TMEM lane quarter = warp % 4); a 32-bit TMEM column
+            // holds two consecutive bf16 of the row; head rows >= h are zero.  The blocks are moved in the
+            // order in which they arrive, and this warp's own first gather goes out as soon as all four
+            // copiers are through with block c.
+            const int row = (warp & 3) * 32 + lane;
+            const uint32_t tq = tmem_addr(tmem, (warp & 3) * 32, kColQ);
+            bool tile0_out = false;
+#pragma unroll 1
+            for (int cc = 0; cc < kNChunk; ++cc) {
+              mbar_wait(smem_u32(&m0->q_full[cc]), ti & 1u, abort_flag);
+              tc_fence_after();
+              uint32_t v[32];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const uint32_t src = k_s + cc * kQBlock + row * 128 + ((q ^ (row & 7)) << 4);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[4 * q]), "=r"(v[4 * q + 1]), "=r"(v[4 * q + 2]), "=r"(v[4 * q + 3]) : "r"(src));
+              }
+              if (row >= p.h) {
+#pragma unroll
+                for (int q = 0; q < 32; ++q) v[q] = 0u;
+              }
+              tmem_st32(tq + cc * 32, v);
+              tmem_wait_st();
+              tc_fence_before();
+              fence_proxy_async_smem();   // the slots read above are next written by TMA (async proxy)
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&m0->q_copied[cc]));
+              if (!tile0_out && cc > c) {
+                uint32_t ok = 0;
+                if (lane == 0) ok = mbar_try_wait(smem_u32(&m0->q_copied[c]), ti & 1u) ? 1u : 0u;
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (ok) { issue_tile(0); tile0_out = true; }
+              }
+            }
+            if (!tile0_out) {
+              mbar_wait(smem_u32(&m0->q_copied[c]), ti & 1u, abort_flag);
+              issue_tile(0);
+            }
+          }
+          for (int i = 1; i < n_tiles; ++i) issue_tile(i);
+          gt += n_tiles;
+        }
+      }
+    } else {
+      // ===================================================================== CTA 1: values
+      const uint32_t v_s = base;
+      const uint32_t p_s = base + kOff1P;
+      const uint32_t e_s = base + kOff1E;
+      const uint32_t epi_done_r[2] = {mapa_shared(smem_u32(&m0->epi_done[0]), 0), mapa_shared(smem_u32(&m0->epi_done[1]), 0)};
+      // ---------------------------------------------------------------- epilogue duty (16 warps: 0-7 and 9-16)
+      // warp -> TMEM lane quarter warp % 4 (head rows 32q .. 32q+31) and column group g (output columns
+      // 128g .. 128g+127): warps 0-3 g = 0, 4-7 g = 1, 9-12 g = 2, 13-16 g = 3.  A warp works alone: it
+      // converts 64 columns of its rows to bf16 into a private 4 KB staging piece ([32 rows x 128 B], the
+      // swizzled tile layout) and sends it with one TMA tile store, twice.  Pieces 0-3 are the P buffer of
+      // the token's last tile (idle until the softmax four tiles later asks for it; the relay holds its
+      // p_free back until the last store has read it), pieces 4-7 an area of their own; the V ring is not
+      // touched, so the gathers of the next token run underneath.  Warp w < 8 and warp 9 + w share piece w:
+      // the V producers come later (they first send out the next token's first gathers) and wait for their
+      // partner (stg_free); in the area of its own the partner of the next token waits in turn (stg_back).
+      auto epilogue_duty = [&](int ti, uint32_t Gl, int tok) {
+        const int q4 = warp & 3;
+        const int grp = warp < 8 ? (warp >> 2) : 2 + ((warp - 9) >> 2);
+        const int piece = warp < 8 ? warp : warp - 9;
+        // `fin` first: P of the last tile was sent after p_free of tile Gl-4, i.e. after that P.V, so that
+        // pv_done[Gl & 3] has completed every phase before the one waited for
+        mbar_wait(smem_u32(&m1->fin[ti & 1]), (ti >> 1) & 1u, abort_flag);
+        mbar_wait(smem_u32(&m1->pv_done[Gl & 3]), (Gl >> 2) & 1u, abort_flag);
+        if (warp >= 9) mbar_wait(smem_u32(&m1->stg_free[piece]), ti & 1u, abort_flag);
+        else if (warp >= 4 && ti >= 1) mbar_wait(smem_u32(&m1->stg_back[piece - 4]), (ti - 1) & 1u, abort_flag);
+        tc_fence_after();
+        const int row = q4 * 32 + lane;
+        const float inv_l = m1->inv_l[ti & 1][row];
+        const uint32_t stg = (piece < 4 ? p_s + (Gl & 3u) * kPBuf + piece * 4096 : e_s + (piece - 4) * 4096) + lane * 128;
+#pragma unroll 1
+        for (int cb = 0; cb < 2; ++cb) {
+#pragma unroll
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t acc[32];
+            tmem_ld32(tmem_addr(tmem, q4 * 32, grp * 128 + cb * 64 + c2 * 32), acc);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              const int chunk = c2 * 4 + (j >> 3);
+              st_shared_v4(stg + ((chunk ^ (lane & 7)) << 4),
+                           pack_bf16x2(__uint_as_float(acc[j]) * inv_l, __uint_as_float(acc[j + 1]) * inv_l),
+                           pack_bf16x2(__uint_as_float(acc[j + 2]) * inv_l, __uint_as_float(acc[j + 3]) * inv_l),
+                           pack_bf16x2(__uint_as_float(acc[j + 4]) * inv_l, __uint_as_float(acc[j + 5]) * inv_l),
+                           pack_bf16x2(__uint_as_float(acc[j + 6]) * inv_l, __uint_as_float(acc[j + 7]) * inv_l));
+            }
+          }
+          if (cb == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&m1->o_free));   // the next token's P.V may overwrite the accumulator
+          }
+          fence_proxy_async_smem();   // the tile store reads the piece through the async proxy
+          __syncwarp();
+          if (lane == 0) {
+            if (q4 * 32 < p.h) tma_store_3d(&tm_o, stg - lane * 128, (grp * 2 + cb) * 64, q4 * 32, tok);
+            bulk_commit();
+            bulk_wait_read_all();
+          }
+          __syncwarp();
+        }
+        if (lane == 0) {
+          if (warp < 8) mbar_arrive(smem_u32(&m1->stg_free[piece]));
+          else if (piece >= 4) mbar_arrive(smem_u32(&m1->stg_back[piece - 4]));
+          mbar_arrive(smem_u32(&m1->epi_cnt));
+        }
+      };
+      if (warp < 8) {
+        const uint32_t p_free_r0 = mapa_shared(smem_u32(&m0->p_free[0]), 0);
+        for (int t = 0; t < nb; ++t) {
+          const int ti = batch0 + t;
+          const int tok = pair + ti * n_pairs;
+          const int n_tiles = nt[t];
+          if (warp < 4) {
+            // ------------------------------------------------------------ correction (thread = head)
+            for (int i = 0; i < n_tiles; ++i) {
+              const uint32_t G = gt + i;
+              const int b = G & 3;
+              mbar_wait(smem_u32(&m1->p_full[b]), (G >> 2) & 1u, abort_flag);
+              const float a = m1->alpha[b][tid];
+              const bool need = (i > 0) && (a != 1.0f);
+              if (__any_sync(0xffffffffu, need)) {
+                // P of tile G was sent after p_free of tile G-4, i.e. after P.V of tile G-5 as well: the
+                // barrier of tile G-1 has completed every phase before the one waited for
+                mbar_wait(smem_u32(&m1->pv_done[(G - 1) & 3]), ((G - 1) >> 2) & 1u, abort_flag);
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < 512; c0 += 32) {
+                  uint32_t o[32];
+                  tmem_ld32(tmem_addr(tmem, warp * 32, c0), o);
+                  tmem_wait_ld();
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * a);
+                  tmem_st32(tmem_addr(tmem, warp * 32, c0), o);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+              }
+              // P arrived through the async proxy (bulk copy), which is also how the MMA reads it: no proxy fence
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(&m1->corr_done[b]));
+            }
+          } else if (warp == 4 && lane == 0) {
+            // ------------------------------------------------------------ relay: P buffer free -> CTA 0
+            // (this thread sees every tile in order: the last one of the token in the epilogue below)
+            for (int i = 0; i + 1 < n_tiles; ++i) {
+              const uint32_t G = gt + i;
+              mbar_wait(smem_u32(&m1->pv_done[G & 3]), (G >> 2) & 1u, abort_flag);
+              mbar_arrive_cluster_relaxed(p_free_r0 + (G & 3u) * 8);
+            }
+          }
+          __syncwarp();
+          gt += n_tiles;
+          epilogue_duty(ti, gt - 1, tok);
+          // the P buffer of the last tile staged the output: it is free for the softmax, and 1/l of this
+          // token may be replaced, once all 16 warps are through
+          if (warp == 4 && lane == 0) {
+            mbar_wait(smem_u32(&m1->epi_cnt), ti & 1u, abort_flag);
+            mbar_arrive_cluster_relaxed(p_free_r0 + ((gt - 1) & 3u) * 8);
+            mbar_arrive_cluster_relaxed(epi_done_r[ti & 1]);
+          }
+        }
+      } else if (warp == 8) {
+        // -------------------------------------------------------------- P.V issuer
+        if (lane == 0) {
+          constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
+          const uint64_t ad0 = smem_desc_sw128(p_s, 16, 1024);
+          const uint64_t bd0 = smem_desc_sw128(v_s, kVBlock, 1024);
+          const uint32_t ad_lo = static_cast<uint32_t>(ad0), ad_hi = static_cast<uint32_t>(ad0 >> 32);
+          const uint32_t bd_lo = static_cast<uint32_t>(bd0), bd_hi = static_cast<uint32_t>(bd0 >> 32);
+          const uint32_t v_full0 = smem_u32(&m1->v_full[0]), v_free0 = smem_u32(&m1->v_free[0]);
+          for (int t = 0; t < nb; ++t) {
+            const int ti = batch0 + t;
+            const int n_tiles = nt[t];
+            // the epilogue of the previous token has read the accumulator
+            if (ti >= 1) mbar_wait(smem_u32(&m1->o_free), (ti - 1) & 1u, abort_flag);
+            for (int i = 0; i < n_tiles; ++i) {
+              const uint32_t G = gt + i;
+              const int b = G & 3;
+              const uint32_t ph = (G >> 1) & 1u;
+              const uint32_t slot0 = (G & 1u) * 2u;
+              mbar_wait(smem_u32(&m1->corr_done[b]), (G >> 2) & 1u, abort_flag);
+              tc_fence_after();
+              const uint32_t a_lo = ad_lo + ((b * kPBuf) >> 4);
+              const uint32_t b_lo = bd_lo + ((slot0 * kVSlab) >> 4);
+#pragma unroll
+              for (int sl = 0; sl < 2; ++sl) {
+                mbar_wait(v_full0 + (slot0 + sl) * 8, ph, abort_flag);
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                  const int j = sl * 2 + kk;   // 16-row step inside the tile
+                  const uint32_t alo = a_lo + ((j * 32) >> 4);
+#pragma unroll
+                  for (int hv = 0; hv < 2; ++hv) {
+                    const uint32_t blo = b_lo + ((sl * kVSlab + hv * 4 * kVBlock + kk * 2048) >> 4);
+                    if (j == 0) {
+                      if (i == 0) umma_f16_ss_lohi<false>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                      else umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                    } else {
+                      umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                    }
+                  }
+                }
+                umma_commit(v_free0 + (slot0 + sl) * 8);
+              }
+              umma_commit(smem_u32(&m1->pv_done[G & 3]));
+            }
+            gt += n_tiles;
+          }
+        }
+      } else if (warp >= 9 && warp < 17) {
+        // -------------------------------------------------------------- V producers (warps 9-16)
+        // warp 9+w fetches 64-column block w of the 512 value columns; lane l < 16 owns tile rows 4l..4l+3,
+        // which are rows 4(l%8).. of slab l/8 of the tile.
+        const int w = warp - 9;
+        const bool gl = lane < 16;
+        for (int t = 0; t < nb; ++t) {
+          const int ti = batch0 + t;
+          const int tok = pair + ti * n_pairs;
+          const int n_tiles = nt[t];
+          const int32_t* idx_row = p.indices + static_cast<long long>(tok) * p.idx_st;
+          int nxt[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) nxt[j] = (gl && 4 * lane + j < p.topk) ? idx_row[4 * lane + j] : -1;
+          auto issue_tile = [&](int i) {
+            const uint32_t G = gt + i;
+            const int slot = (G & 1) * 2 + ((lane >> 3) & 1);
+            int row[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) row[j] = (nxt[j] >= 0 && nxt[j] < p.s_kv) ? nxt[j] : 0;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int jn = (i + 1) * kNT + 4 * lane + j;
+              nxt[j] = (gl && i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+            }
+            if (gl) {
+              if (G >= 2) mbar_wait(smem_u32(&m1->v_free[slot]), ((G >> 1) - 1) & 1u, abort_flag);
+              const uint32_t full = smem_u32(&m1->v_full[slot]);
+              // one arrival per slab announces all 64 gathers of the eight warps (the byte count may run
+              // ahead of the announcement: the phase cannot complete before this arrival)
+              if (w == 0 && (lane & 7) == 0) mbar_arrive_expect_tx(full, kVSlab);
+              tma_gather4(v_s + slot * kVSlab + w * kVBlock + (lane & 7) * 512, &tm_kv, full, w * 64, row[0], row[1], row[2], row[3]);
+            }
+            __syncwarp();
+          };
+          // the first tile goes out before this warp helps with the previous token's epilogue, so that the
+          // gathers run underneath it
+          issue_tile(0);
+          __syncwarp();
+          if (t > 0) epilogue_duty(ti - 1, gt - 1, tok - n_pairs);
+          for (int i = 1; i < n_tiles; ++i) issue_tile(i);
+          gt += n_tiles;
+        }
+        // the last token of the batch: nothing of the next batch is known yet
+        __syncwarp();
+        epilogue_duty(batch0 + nb - 1, gt - 1, pair + (batch0 + nb - 1) * n_pairs);
+      }
+    }
+    __syncthreads();   // nt[] is rewritten by the next batch
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();            // nobody leaves while the peer may still write or signal this CTA
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512u);
+  }
+  if (tid == 0 && p.status != nullptr) {
+    if (*abort_flag) atomicCAS(p.status, 0, FTB_ERR_TIMEOUT);
+    else if (cta == 0 && m0->bad_index) atomicCAS(p.status, 0, FTB_ERR_BAD_INDEX);
+  }
+}
+
+}  // namespace mla7
+
+int launch_sparse_mla_stream64(const ftb_sparse_mla_args* a, cudaStream_t st) {
+  mla7::Params p;
+  p.indices = a->indices;
+  p.lse = a->lse;
+  p.s_q = a->s_q; p.h = a->h; p.s_kv = a->s_kv; p.topk = a->topk;
+  p.idx_st = a->idx_stride_token;
+  p.lse_st = a->lse_stride_token;
+  p.scale_log2 = a->sm_scale * 1.4426950408889634f;
+  p.lse_base2 = a->lse_base2;
+  p.status = a->status;
+  // KV: box = 64 columns x 1 row (tile::gather4 fetches four such rows per instruction);
+  // Q: boxes of [h rows x 64 columns] of one token; O: boxes of [32 rows x 64 columns] (a store that
+  // reaches past row h is clipped)
+  const uint32_t box_h = static_cast<uint32_t>(a->h < 128 ? a->h : 128);
+  CUtensorMap tm_kv, tm_q, tm_o;
+  if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla7::kDqk,
+                    static_cast<uint64_t>(a->kv_stride_row), 1, 64) ||
+      !make_tmap_3d(&tm_q, a->q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mla7::kDqk, static_cast<uint64_t>(a->h),
+                    static_cast<uint64_t>(a->s_q), static_cast<uint64_t>(a->q_stride_head),
+                    static_cast<uint64_t>(a->q_stride_token), 64, box_h) ||
+      !make_tmap_3d(&tm_o, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 512, static_cast<uint64_t>(a->h),
+                    static_cast<uint64_t>(a->s_q), static_cast<uint64_t>(a->out_stride_head),
+                    static_cast<uint64_t>(a->out_stride_token), 64, box_h < 32 ? box_h : 32)) {
+    set_last_error("sparse_mla_stream64: cuTensorMapEncodeTiled failed");
+    return FTB_ERR_CUDA;
+  }
+  cudaError_t e = cudaFuncSetAttribute(mla7::sparse_mla_stream64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla7::kSmemBytes);
+  if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla_stream64)");
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(mla7::kThreads);
+  cfg.dynamicSmemBytes = mla7::kSmemBytes;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // as many pairs as the device holds at once (one per pair of SMs that can host a cluster), cached per device
+  static int pairs_of_device[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  int pairs = (dev >= 0 && dev < 64) ? pairs_of_device[dev] : 0;
+  if (pairs == 0) {
+    cfg.gridDim = dim3(2);
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, mla7::sparse_mla_stream64_kernel, &cfg);
+    if (e != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      int sms = 0;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      n = sms / 2 > 0 ? sms / 2 : 1;
+    }
+    pairs = n;
+    if (dev >= 0 && dev < 64) pairs_of_device[dev] = pairs;
+  }
+  if (pairs > a->s_q) pairs = a->s_q;
+  cfg.gridDim = dim3(static_cast<unsigned>(pairs) * 2u);
+  e = cudaLaunchKernelEx(&cfg, mla7::sparse_mla_stream64_kernel, tm_kv, tm_q, tm_o, p);
+  return check_cuda(e, "sparse_mla_stream64 launch");
+}
+
+}  // namespace ftb

@@ -69,7 +69,8 @@ typedef struct ftb_sparse_mla_args {
                                one shared MMA; 3 = CTA pair, scores / values split;
                                4 = as 3 with Q in tensor memory and TMA row gathers;
                                5 = as 4, persistent pairs that walk through the tokens;
-                               6 = paged FP8 form only: dequantise the selected rows, then 5 */
+                               6 = paged FP8 form only: dequantise the selected rows, then 5;
+                               7 = as 5 with tiles of 64 rows in rings two tiles deep       */
   int32_t* status;          /* optional device int32: kernels OR-in a non-zero FTB_ERR_* code */
   /* Paged FP8 form (kv_is_fp8 != 0): physical row = block_table[seq, p / page] * page + p % page,
    * the rule of test_accuracy_musa_vllm_mla.py:278-283.  Query token t belongs to sequence

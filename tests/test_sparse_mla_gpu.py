@@ -32,6 +32,11 @@ def _errors(out, lse, ref_out, ref_lse):
     return e_out, e_lse
 
 
+# every bf16 kernel behind algo_id: 5 is what algo_id 0 selects
+ALGOS = [1, 2, 3, 4, 5, 7]
+ALGO_IDS = ["single_cta", "cta_pair", "cta_duo", "cta_duo_qtmem", "persistent", "persistent_64row"]
+
+
 def _check(q, kv, idx, sm_scale, name="", algo=0):
     out, lse = sparse_mla_fwd(q.to(DEV), kv.to(DEV), idx.to(DEV), sm_scale, check=True, algo=algo)
     torch.cuda.synchronize()
@@ -63,7 +68,7 @@ def test_scores_tap_matches_qk():
 GOLDEN = sorted(glob.glob(os.path.join(GOLDEN_DIR, "mla_topk_*.npz")))
 
 
-@pytest.mark.parametrize("algo", [1, 2, 3, 4, 5], ids=["single_cta", "cta_pair", "cta_duo", "cta_duo_qtmem", "persistent"])
+@pytest.mark.parametrize("algo", ALGOS, ids=ALGO_IDS)
 @pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[:-4] for p in GOLDEN])
 def test_golden_vectors_from_reference_kernel(path, algo):
     d = np.load(path)
@@ -77,13 +82,13 @@ def test_golden_vectors_from_reference_kernel(path, algo):
     assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
 
 
-@pytest.mark.parametrize("algo", [1, 2, 3, 4, 5], ids=["single_cta", "cta_pair", "cta_duo", "cta_duo_qtmem", "persistent"])
+@pytest.mark.parametrize("algo", ALGOS, ids=ALGO_IDS)
 def test_cfg1_cpu_runnable_case_full(algo):
     c = W.mla_cfg1()
     _check(c.q, c.kv, c.indices, c.sm_scale, c.name, algo)
 
 
-@pytest.mark.parametrize("algo", [1, 2, 3, 4, 5], ids=["single_cta", "cta_pair", "cta_duo", "cta_duo_qtmem", "persistent"])
+@pytest.mark.parametrize("algo", ALGOS, ids=ALGO_IDS)
 @pytest.mark.parametrize("h", [1, 16, 64, 65, 128])
 @pytest.mark.parametrize("topk", [1, 37, 64, 200])
 def test_head_counts_and_ragged_topk(h, topk, algo):
@@ -95,7 +100,7 @@ def test_head_counts_and_ragged_topk(h, topk, algo):
     _check(q, kv, idx, 576 ** -0.5, f"h{h}_topk{topk}_algo{algo}", algo)
 
 
-@pytest.mark.parametrize("algo", [1, 2, 3, 4, 5], ids=["single_cta", "cta_pair", "cta_duo", "cta_duo_qtmem", "persistent"])
+@pytest.mark.parametrize("algo", ALGOS, ids=ALGO_IDS)
 def test_padding_patterns(algo):
     """Trailing -1 padding, a token with no valid entry, one valid entry, and -1 in the middle."""
     g = torch.Generator().manual_seed(7)
@@ -114,7 +119,7 @@ def test_padding_patterns(algo):
     assert torch.equal(out[2].cpu(), kv[idx[2, 0].item(), :512].expand(h, 512))
 
 
-@pytest.mark.parametrize("algo", [1, 2, 3, 4, 5], ids=["single_cta", "cta_pair", "cta_duo", "cta_duo_qtmem", "persistent"])
+@pytest.mark.parametrize("algo", ALGOS, ids=ALGO_IDS)
 def test_causal_prefill_shape_scaled_down(algo):
     c = W.mla_cfg2(s_q=192, s_kv=192, h=128, topk=128)
     _check(c.q, c.kv, c.indices, c.sm_scale, c.name, algo)
