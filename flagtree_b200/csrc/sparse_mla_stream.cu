@@ -334,8 +334,11 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
       } else if (warp == 8) {
         // -------------------------------------------------------------- Q.K^T issuer
         // Straight-line code per tile (block c always sits in slot c): the descriptors differ in their low
-        // word only and every offset is a compile-time constant.
-        if (lane == 0) {
+        // word only and every offset is a compile-time constant.  The whole warp runs the loop and waits;
+        // an elected lane (always the same one, so that its commits cover its MMAs) issues.  With the
+        // control flow and the operands uniform over the warp the issue of an MMA costs far fewer
+        // instructions than from inside a branch that a single lane takes.
+        {
           constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, kNT, 0, 0);
           const uint64_t bd0 = smem_desc_sw128(k_s, 16, 1024);
           const uint32_t bd_lo = static_cast<uint32_t>(bd0), bd_hi = static_cast<uint32_t>(bd0 >> 32);
@@ -353,15 +356,19 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
               for (int cc = 0; cc < kNChunk; ++cc) {
                 mbar_wait(k_full0 + cc * 8, ph, abort_flag);
                 tc_fence_after();
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  const uint32_t lo = bd_lo + ((cc * kKSlot + k * 32) >> 4);
-                  if (cc == 0 && k == 0) umma_f16_ts_lohi<false>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
-                  else umma_f16_ts_lohi<true>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+                  for (int k = 0; k < 4; ++k) {
+                    const uint32_t lo = bd_lo + ((cc * kKSlot + k * 32) >> 4);
+                    if (cc == 0 && k == 0) umma_f16_ts_lohi<false>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+                    else umma_f16_ts_lohi<true>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+                  }
+                  umma_commit(k_free0 + cc * 8);
                 }
-                umma_commit(k_free0 + cc * 8);
+                __syncwarp();
               }
-              umma_commit(s_full);
+              if (elect_one()) umma_commit(s_full);
+              __syncwarp();
             }
             gt += n_tiles;
           }
@@ -594,8 +601,8 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
           }
         }
       } else if (warp == 8) {
-        // -------------------------------------------------------------- P.V issuer
-        if (lane == 0) {
+        // -------------------------------------------------------------- P.V issuer (whole warp, an elected lane issues)
+        {
           constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
           const uint64_t ad0 = smem_desc_sw128(p_s, 16, 1024);
           const uint64_t bd0 = smem_desc_sw128(v_s, kVBlock, 1024);
@@ -618,24 +625,28 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
               for (int sl = 0; sl < kNV; ++sl) {
                 mbar_wait(v_full0 + sl * 8, ph, abort_flag);
                 tc_fence_after();
+                if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < 2; ++kk) {
-                  const int j = sl * 2 + kk;   // 16-row step inside the tile
-                  const uint32_t alo = a_lo + (((j >> 2) * kQBlock + (j & 3) * 32) >> 4);
+                  for (int kk = 0; kk < 2; ++kk) {
+                    const int j = sl * 2 + kk;   // 16-row step inside the tile
+                    const uint32_t alo = a_lo + (((j >> 2) * kQBlock + (j & 3) * 32) >> 4);
 #pragma unroll
-                  for (int hv = 0; hv < 2; ++hv) {
-                    const uint32_t blo = bd_lo + ((sl * kVSlab + hv * 4 * kVBlock + kk * 2048) >> 4);
-                    if (j == 0) {
-                      if (i == 0) umma_f16_ss_lohi<false>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
-                      else umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
-                    } else {
-                      umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                    for (int hv = 0; hv < 2; ++hv) {
+                      const uint32_t blo = bd_lo + ((sl * kVSlab + hv * 4 * kVBlock + kk * 2048) >> 4);
+                      if (j == 0) {
+                        if (i == 0) umma_f16_ss_lohi<false>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                        else umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                      } else {
+                        umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                      }
                     }
                   }
+                  umma_commit(v_free0 + sl * 8);
                 }
-                umma_commit(v_free0 + sl * 8);
+                __syncwarp();
               }
-              umma_commit(smem_u32(&m1->pv_done[b]));
+              if (elect_one()) umma_commit(smem_u32(&m1->pv_done[b]));
+              __syncwarp();
             }
             gt += n_tiles;
           }

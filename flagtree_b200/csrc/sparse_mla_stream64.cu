@@ -366,8 +366,10 @@ sparse_mla_stream64_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gr
       } else if (warp == 8 || warp == 18) {
         // -------------------------------------------------------------- Q.K^T issuers: warp 8 even tiles, warp 18 odd tiles
         // Straight-line code per tile (block c of parity par always sits in the same place): the descriptors
-        // differ in their low word only and every offset is a compile-time constant.
-        if (lane == 0) {
+        // differ in their low word only and every offset is a compile-time constant.  The whole warp runs
+        // the loop and waits; an elected lane (always the same one, so that its commits cover its MMAs)
+        // issues: with control flow and operands uniform over the warp an MMA costs far fewer instructions.
+        {
           const int par = warp == 8 ? 0 : 1;
           constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, kNT, 0, 0);
           const uint64_t bd0 = smem_desc_sw128(k_s + par * kKSlot, 16, 1024);
@@ -387,15 +389,19 @@ sparse_mla_stream64_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gr
               for (int cc = 0; cc < kNChunk; ++cc) {
                 mbar_wait(k_full0 + cc * 8, ph, abort_flag);
                 tc_fence_after();
+                if (elect_one()) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                  const uint32_t lo = bd_lo + ((cc * 2 * kKSlot + k * 32) >> 4);
-                  if (cc == 0 && k == 0) umma_f16_ts_lohi<false>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
-                  else umma_f16_ts_lohi<true>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+                  for (int k = 0; k < 4; ++k) {
+                    const uint32_t lo = bd_lo + ((cc * 2 * kKSlot + k * 32) >> 4);
+                    if (cc == 0 && k == 0) umma_f16_ts_lohi<false>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+                    else umma_f16_ts_lohi<true>(t_s, t_q + cc * 32 + k * 8, lo, bd_hi, kIdesc);
+                  }
+                  umma_commit(k_free0 + cc * 8);
                 }
-                umma_commit(k_free0 + cc * 8);
+                __syncwarp();
               }
-              umma_commit(s_full);
+              if (elect_one()) umma_commit(s_full);
+              __syncwarp();
             }
             gt += n_tiles;
           }
@@ -644,8 +650,8 @@ sparse_mla_stream64_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gr
           }
         }
       } else if (warp == 8) {
-        // -------------------------------------------------------------- P.V issuer
-        if (lane == 0) {
+        // -------------------------------------------------------------- P.V issuer (whole warp, an elected lane issues)
+        {
           constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
           const uint64_t ad0 = smem_desc_sw128(p_s, 16, 1024);
           const uint64_t bd0 = smem_desc_sw128(v_s, kVBlock, 1024);
@@ -670,24 +676,28 @@ sparse_mla_stream64_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gr
               for (int sl = 0; sl < 2; ++sl) {
                 mbar_wait(v_full0 + (slot0 + sl) * 8, ph, abort_flag);
                 tc_fence_after();
+                if (elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < 2; ++kk) {
-                  const int j = sl * 2 + kk;   // 16-row step inside the tile
-                  const uint32_t alo = a_lo + ((j * 32) >> 4);
+                  for (int kk = 0; kk < 2; ++kk) {
+                    const int j = sl * 2 + kk;   // 16-row step inside the tile
+                    const uint32_t alo = a_lo + ((j * 32) >> 4);
 #pragma unroll
-                  for (int hv = 0; hv < 2; ++hv) {
-                    const uint32_t blo = b_lo + ((sl * kVSlab + hv * 4 * kVBlock + kk * 2048) >> 4);
-                    if (j == 0) {
-                      if (i == 0) umma_f16_ss_lohi<false>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
-                      else umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
-                    } else {
-                      umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                    for (int hv = 0; hv < 2; ++hv) {
+                      const uint32_t blo = b_lo + ((sl * kVSlab + hv * 4 * kVBlock + kk * 2048) >> 4);
+                      if (j == 0) {
+                        if (i == 0) umma_f16_ss_lohi<false>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                        else umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                      } else {
+                        umma_f16_ss_lohi<true>(tmem + hv * 256, alo, ad_hi, blo, bd_hi, kIdesc);
+                      }
                     }
                   }
+                  umma_commit(v_free0 + (slot0 + sl) * 8);
                 }
-                umma_commit(v_free0 + (slot0 + sl) * 8);
+                __syncwarp();
               }
-              umma_commit(smem_u32(&m1->pv_done[G & 3]));
+              if (elect_one()) umma_commit(smem_u32(&m1->pv_done[G & 3]));
+              __syncwarp();
             }
             gt += n_tiles;
           }
