@@ -714,31 +714,6 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
 }  // namespace mla5
 
 int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st) {
-  mla5::Params p;
-  p.indices = a->indices;
-  p.lse = a->lse;
-  p.s_q = a->s_q; p.h = a->h; p.s_kv = a->s_kv; p.topk = a->topk;
-  p.idx_st = a->idx_stride_token;
-  p.lse_st = a->lse_stride_token;
-  p.scale_log2 = a->sm_scale * 1.4426950408889634f;
-  p.lse_base2 = a->lse_base2;
-  p.status = a->status;
-  // KV: box = 64 columns x 1 row (tile::gather4 fetches four such rows per instruction);
-  // Q: boxes of [h rows x 64 columns] of one token; O: boxes of [32 rows x 64 columns] (a store that
-  // reaches past row h is clipped)
-  const uint32_t box_h = static_cast<uint32_t>(a->h < 128 ? a->h : 128);
-  CUtensorMap tm_kv, tm_q, tm_o;
-  if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla5::kDqk,
-                    static_cast<uint64_t>(a->kv_stride_row), 1, 64) ||
-      !make_tmap_3d(&tm_q, a->q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mla5::kDqk, static_cast<uint64_t>(a->h),
-                    static_cast<uint64_t>(a->s_q), static_cast<uint64_t>(a->q_stride_head),
-                    static_cast<uint64_t>(a->q_stride_token), 64, box_h) ||
-      !make_tmap_3d(&tm_o, a->out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 512, static_cast<uint64_t>(a->h),
-                    static_cast<uint64_t>(a->s_q), static_cast<uint64_t>(a->out_stride_head),
-                    static_cast<uint64_t>(a->out_stride_token), 64, box_h < 32 ? box_h : 32)) {
-    set_last_error("sparse_mla_stream: cuTensorMapEncodeTiled failed");
-    return FTB_ERR_CUDA;
-  }
   cudaError_t e = cudaFuncSetAttribute(mla5::sparse_mla_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla5::kSmemBytes);
   if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla_stream)");
   cudaLaunchConfig_t cfg = {};
@@ -754,8 +729,8 @@ int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st) {
   static int pairs_of_device[64] = {0};
   int dev = 0;
   cudaGetDevice(&dev);
-  int pairs = (dev >= 0 && dev < 64) ? pairs_of_device[dev] : 0;
-  if (pairs == 0) {
+  int pairs_dev = (dev >= 0 && dev < 64) ? pairs_of_device[dev] : 0;
+  if (pairs_dev == 0) {
     cfg.gridDim = dim3(2);
     int n = 0;
     e = cudaOccupancyMaxActiveClusters(&n, mla5::sparse_mla_stream_kernel, &cfg);
@@ -765,13 +740,52 @@ int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st) {
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
       n = sms / 2 > 0 ? sms / 2 : 1;
     }
-    pairs = n;
-    if (dev >= 0 && dev < 64) pairs_of_device[dev] = pairs;
+    pairs_dev = n;
+    if (dev >= 0 && dev < 64) pairs_of_device[dev] = pairs_dev;
   }
-  if (pairs > a->s_q) pairs = a->s_q;
-  cfg.gridDim = dim3(static_cast<unsigned>(pairs) * 2u);
-  e = cudaLaunchKernelEx(&cfg, mla5::sparse_mla_stream_kernel, tm_kv, tm_q, tm_o, p);
-  return check_cuda(e, "sparse_mla_stream launch");
+  // One launch takes at most kBatch tokens per pair, so that every pair finds its tile counts once and runs
+  // through its tokens without a stop; a longer batch of query tokens is a sequence of such launches on the
+  // stream (a launch boundary every pairs x kBatch tokens costs next to nothing).
+  const long long cap = static_cast<long long>(pairs_dev) * mla5::kBatch;
+  // KV: box = 64 columns x 1 row (tile::gather4 fetches four such rows per instruction);
+  // Q: boxes of [h rows x 64 columns] of one token; O: boxes of [32 rows x 64 columns] (a store that
+  // reaches past row h is clipped)
+  const uint32_t box_h = static_cast<uint32_t>(a->h < 128 ? a->h : 128);
+  CUtensorMap tm_kv;
+  if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla5::kDqk,
+                    static_cast<uint64_t>(a->kv_stride_row), 1, 64)) {
+    set_last_error("sparse_mla_stream: cuTensorMapEncodeTiled failed");
+    return FTB_ERR_CUDA;
+  }
+  for (long long t0 = 0; t0 < a->s_q; t0 += cap) {
+    const int n_tok = static_cast<int>(a->s_q - t0 < cap ? a->s_q - t0 : cap);
+    mla5::Params p;
+    p.indices = a->indices + t0 * a->idx_stride_token;
+    p.lse = a->lse + t0 * a->lse_stride_token;
+    p.s_q = n_tok; p.h = a->h; p.s_kv = a->s_kv; p.topk = a->topk;
+    p.idx_st = a->idx_stride_token;
+    p.lse_st = a->lse_stride_token;
+    p.scale_log2 = a->sm_scale * 1.4426950408889634f;
+    p.lse_base2 = a->lse_base2;
+    p.status = a->status;
+    const void* q0 = static_cast<const __nv_bfloat16*>(a->q) + t0 * a->q_stride_token;
+    void* o0 = static_cast<__nv_bfloat16*>(a->out) + t0 * a->out_stride_token;
+    CUtensorMap tm_q, tm_o;
+    if (!make_tmap_3d(&tm_q, q0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mla5::kDqk, static_cast<uint64_t>(a->h),
+                      static_cast<uint64_t>(n_tok), static_cast<uint64_t>(a->q_stride_head),
+                      static_cast<uint64_t>(a->q_stride_token), 64, box_h) ||
+        !make_tmap_3d(&tm_o, o0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 512, static_cast<uint64_t>(a->h),
+                      static_cast<uint64_t>(n_tok), static_cast<uint64_t>(a->out_stride_head),
+                      static_cast<uint64_t>(a->out_stride_token), 64, box_h < 32 ? box_h : 32)) {
+      set_last_error("sparse_mla_stream: cuTensorMapEncodeTiled failed");
+      return FTB_ERR_CUDA;
+    }
+    const int pairs = pairs_dev < n_tok ? pairs_dev : n_tok;
+    cfg.gridDim = dim3(static_cast<unsigned>(pairs) * 2u);
+    e = cudaLaunchKernelEx(&cfg, mla5::sparse_mla_stream_kernel, tm_kv, tm_q, tm_o, p);
+    if (e != cudaSuccess) return check_cuda(e, "sparse_mla_stream launch");
+  }
+  return FTB_OK;
 }
 
 }  // namespace ftb
