@@ -9,6 +9,10 @@ One "step" is one forward over one batch of synthetic, seed-generated input.  Wi
 rank runs a full-size batch of its own query tokens against the replicated latent KV (tokens
 are independent units, so there is no data-path collective: weak scaling) and the line reports
 total FLOP/s over all ranks divided by the slowest rank's device time.  Prints ONE JSON line.
+Further sections of the same line: the end-to-end form with host buffers, the strong-scaling form
+(one batch split over the ranks), the paged FP8 decode (cfg3), the FP8 cache write path, and the
+second hot path, GEMM + reduce-scatter in bf16 (cfg4) and block-scaled FP8 (cfg5), each with a
+numeric check against an fp32 reduce-scatter and the CPU oracle.
 """
 from __future__ import annotations
 
@@ -28,6 +32,18 @@ if ROOT not in sys.path:
 
 METRIC = "sparse_mla_fwd_tflops"
 UNIT = "TFLOP/s"
+KERNEL_OF_ALGO = {0: "sparse_mla_fifo_kernel", 5: "sparse_mla_stream_kernel", 7: "sparse_mla_stream64_kernel",
+                  8: "sparse_mla_fifo_kernel", 1: "sparse_mla_fwd_kernel"}
+SM_SCALE = 192 ** -0.5
+FLOPS_CFG2 = 2 * (576 + 512) * 128 * 6292480          # sum over tokens of min(t + 1, 2048) valid entries
+
+
+def make_config(s_q: int):
+    """The workload description both arms print: the driver compares it key by key."""
+    return {"workload": "mla_cfg2_prefill_sq4096_skv4096_h128_topk2048_causal", "s_q_per_gpu": s_q,
+            "sharding": "query tokens per rank, latent KV replicated, no collective",
+            "l2": "inputs larger than L2 (q 604 MB per step)", "sm_scale": SM_SCALE,
+            "flops_per_gpu_step": FLOPS_CFG2 if s_q == 4096 else None}
 
 
 def load_peaks():
@@ -92,10 +108,10 @@ class ClockSampler:
 
 
 def cpu_baseline_mla(n_tokens: int, reps: int = 1):
-    """Times the CPU oracle on a bounded, evenly spaced sample of the cfg2 query tokens."""
+    """Times the CPU oracle on a bounded, evenly spaced sample of the cfg2 query tokens (all of them at 4096)."""
     from flagtree_b200 import workloads as W
     from oracle.sparse_mla_ref import sparse_mla_fwd_ref
-    c = W.mla_cfg2(device="cpu", s_q=4096, s_kv=4096, h=128, topk=2048) if n_tokens > 0 else None
+    c = W.mla_cfg2(device="cpu", s_q=4096, s_kv=4096, h=128, topk=2048)
     sel = torch.linspace(0, 4095, n_tokens).round().long()
     q, idx = c.q[sel].contiguous(), c.indices[sel].contiguous()
     flops = 2 * (576 + 512) * 128 * int((idx >= 0).sum())
@@ -111,6 +127,19 @@ def cpu_baseline_mla(n_tokens: int, reps: int = 1):
             "seconds": best, "flops": flops}
 
 
+def _time_events(fn, iters, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
 def bench_mla_decode_fp8(args, dev, peaks):
     """Third workload (a parity-test case with a timing beside it, not the headline): sparse MLA decode over
     the paged FP8 latent cache of cfg3 (64 sequences x 2 query tokens, h = 128, topk = 2048, 64-token pages
@@ -124,23 +153,107 @@ def bench_mla_decode_fp8(args, dev, peaks):
     flops = 2 * (576 + 512) * h * n_valid
     nbytes = n_valid * 576 + c.q.numel() * 2 + b * n_q * h * 512 * 2 + c.indices.numel() * 4
     iters = max(5, min(args.steps, 20))
-    for _ in range(max(3, args.warmup)):
-        sparse_mla_fwd_paged(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens, c.indices, c.sm_scale,
-                             page_size=c.page_size)
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        sparse_mla_fwd_paged(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens, c.indices, c.sm_scale,
-                             page_size=c.page_size)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / iters
+    ms = _time_events(lambda: sparse_mla_fwd_paged(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens, c.indices,
+                                                   c.sm_scale, page_size=c.page_size), iters, max(3, args.warmup))
     return {"workload": c.name, "dtype": "fp8 e4m3 KV (bf16 math)", "ms": ms, "iters": iters, "flops": flops,
             "tflops": flops / (ms * 1e-3) / 1e12, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
             "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
             "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-            "l2": "gathered rows (151 MB) larger than L2", "kernel": "mla_dequant_rows_kernel + sparse_mla_stream_kernel"}
+            "l2": "gathered rows (151 MB) larger than L2", "kernel": "mla_dequant_rows_kernel + persistent sparse-MLA kernel"}
+
+
+def bench_kv_cache_write(args, dev, peaks):
+    """The producer of cfg3's cache format: 262144 new latent rows (4096 pages of 64 tokens) quantised to e4m3
+    with per-page scales and scattered into a cache of 8192 pages.  Bound by device memory: per row 1152 bytes
+    are read (twice: once for the page maximum, once to quantise) and 576 written; the algorithmic figure counts
+    one read and one write.  The rows (302 MB) exceed L2."""
+    from flagtree_b200 import kv_cache_write_fp8
+    g = torch.Generator(device=dev)
+    g.manual_seed(3100)
+    page, n_pages, n_rows = 64, 8192, 4096 * 64
+    rows = torch.randn(n_rows, 576, generator=g, device=dev).bfloat16()
+    pages = torch.randperm(n_pages, generator=g, device=dev)[:n_rows // page]
+    slots = (pages[:, None] * page + torch.arange(page, device=dev)[None, :]).reshape(-1).int()
+    cache = torch.zeros(n_pages, page, 576, dtype=torch.uint8, device=dev)
+    scale = torch.zeros(n_pages, device=dev)
+    iters = max(5, min(args.steps, 20))
+
+    def step():
+        scale.zero_()                       # every timed call fills empty pages (no requantisation pass)
+        kv_cache_write_fp8(rows, slots, cache, scale, page)
+
+    ms = _time_events(step, iters)
+    nbytes = n_rows * (1152 + 576) + n_rows * 4
+    return {"workload": f"kv_cache_write_fp8_rows{n_rows}_pages{n_pages}x{page}", "ms": ms, "iters": iters,
+            "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "bound": "hbm", "kernels": "row_amax_kernel + page_settle_kernel + row_store_kernel",
+            "l2": "new rows (302 MB) larger than L2"}
+
+
+def bench_fp8_dense_peak(dev):
+    """A plain library FP8 GEMM (cuBLASLt through torch._scaled_mm, e4m3 x e4m3 -> bf16, 8192^3) timed once as the
+    dense FP8 figure to hold the block-scaled FP8 kernels against; None when this torch has no such op."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()       # column-major second operand
+        one = torch.ones((), device=dev)
+        ms = _time_events(lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16), 10)
+        return {"tflops": 2 * n ** 3 / (ms * 1e-3) / 1e12, "ms": ms, "shape": f"{n}^3", "kind": "cuBLASLt e4m3 GEMM via torch._scaled_mm"}
+    except Exception as e:                                                 # noqa: BLE001
+        return {"tflops": None, "unavailable": repr(e)[:200]}
+
+
+def _timed_collective(fn, iters, flush, dist, sync_word, dev):
+    """Median over `iters` of per-iteration CUDA-event times, L2 flushed and the ranks' streams aligned before
+    each start event; max over ranks."""
+    for _ in range(3):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush.fill_(1)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if dist is not None:
+            dist.all_reduce(sync_word)      # aligns the ranks' streams on the device before the start event
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    t = torch.tensor([ts[len(ts) // 2]], dtype=torch.float64, device=dev)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t[0])
+
+
+def _parity_vs_fp32_reduce_scatter(out, partial_fp32, world, dist, dev, oracle_rows=None):
+    """Numeric check of a fused GEMM + reduce-scatter result, outside every timed loop: against NCCL's
+    reduce_scatter_tensor of the ranks' fp32 partial products (all rows) and, on rank 0, against the CPU oracle
+    on a few rows.  The bound is the one of the parity tests: every partial is rounded to bf16 (2^-9 of a value
+    that may be as large as the sum) and the fp32 sum once more."""
+    ref = torch.empty(out.shape, dtype=torch.float32, device=dev)
+    dist.reduce_scatter_tensor(ref, partial_fp32)
+    err = (out.float() - ref).abs().max()
+    scale = ref.abs().max()
+    tol = (world + 1) * 2 ** -8 * float(scale)
+    res = {"max_abs_err": float(err), "tol": tol, "max_abs_ref": float(scale)}
+    if oracle_rows is not None:
+        rows, want = oracle_rows
+        e2 = float((out[rows].float().cpu() - want).abs().max())
+        res["oracle_rows"] = len(rows)
+        res["oracle_max_abs_err"] = e2
+        err = torch.maximum(err, torch.tensor(e2, device=dev))
+    ok = torch.tensor([1 if float(err) <= tol else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    worst = err.clone().double()
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    res["max_abs_err_all_ranks"] = float(worst)
+    res["ok"] = bool(int(ok.item()) == 1)
+    return res
 
 
 def bench_gemm_rs(args, dev, rank, world, dist, peaks):
@@ -157,39 +270,14 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
     iters = max(5, min(args.steps, 20))
     sync_word = torch.zeros(1, device=dev)
 
-    def timed(fn):
-        for _ in range(3):
-            fn()
-        ts = []
-        for _ in range(iters):
-            flush.fill_(1)
-            if dist is not None:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            if dist is not None:
-                dist.all_reduce(sync_word)      # aligns the ranks' streams on the device before the start event
-            e0.record()
-            fn()
-            e1.record()
-            torch.cuda.synchronize()
-            ts.append(e0.elapsed_time(e1))
-        ts.sort()
-        t = torch.tensor([ts[len(ts) // 2]], dtype=torch.float64, device=dev)
-        if os.environ.get("FTB_BENCH_PER_RANK"):
-            print(f"[rank {rank}] median {float(t[0]):.4f} ms", file=sys.stderr, flush=True)
-        if dist is not None:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
-
-    t_gemm = timed(lambda: matmul(case.a, case.b, out=c_full))
+    t_gemm = _timed_collective(lambda: matmul(case.a, case.b, out=c_full), iters, flush, dist, sync_word, dev)
     res = {"workload": f"gemm_rs_cfg4_per_rank_m{m}_n{n}_klocal{k_loc}_tp{world}", "tp": world, "dtype": "bf16",
            "flops_per_gpu": flops, "gemm_only_ms": t_gemm, "gemm_only_tflops_per_gpu": flops / t_gemm / 1e9,
            "l2": "256 MB flush write between timed iterations", "iters": iters, "timing": "median per rank, max over ranks"}
     if world > 1:
-        ctx = GemmRsContext(m, n, None, dev, "auto", os.environ.get("FTB_RS_PROTOCOL", "auto"))
+        ctx = GemmRsContext(m, n, None, dev, "auto", args.rs_protocol)
         out = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)
-        t_fused = timed(lambda: ctx(case.a, case.b, out))
+        t_fused = _timed_collective(lambda: ctx(case.a, case.b, out), iters, flush, dist, sync_word, dev)
         ctx.check()
         nccl_out = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)
 
@@ -197,21 +285,74 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
             matmul(case.a, case.b, out=c_full)
             dist.reduce_scatter_tensor(nccl_out, c_full)
 
-        t_nccl = timed(nccl_path)
+        t_nccl = _timed_collective(nccl_path, iters, flush, dist, sync_word, dev)
+        # numeric check of the fused result, not timed
+        oracle_rows = None
+        if rank == 0:
+            from oracle.gemm_rs_ref import gemm_rs_rows_ref
+            rows = torch.tensor([0, 1, 127, 128, 511, m // world - 1])      # rank 0 owns global rows [0, m / world)
+            all_r = [W.gemm_cfg4(device="cpu", tp=world, rank=r, m=m, n=n, k_total=k_loc * world) for r in range(world)]
+            want = gemm_rs_rows_ref([c.a for c in all_r], [c.b for c in all_r], rows)
+            del all_r
+            oracle_rows = (rows, want)
+        ctx(case.a, case.b, out)
+        torch.cuda.synchronize()
+        parity = _parity_vs_fp32_reduce_scatter(out, case.a.float() @ case.b.float(), world, dist, dev, oracle_rows)
         pushed = (world - 1) / world * m * n * 2
         res.update({"fused_ms": t_fused, "tflops_per_gpu": flops / t_fused / 1e9,
                     "frac_of_peak": flops / t_fused / 1e9 / peaks["bf16_tflops"],
                     "exposed_comm": t_fused / t_gemm - 1.0, "gemm_plus_nccl_rs_ms": t_nccl,
                     "pushed_bytes_per_gpu": pushed, "nvlink_floor_ms": pushed / 770e9 * 1e3,
-                    "symm_provider": ctx.recv.provider, "protocol": ctx.protocol})
+                    "symm_provider": ctx.recv.provider, "protocol": ctx.protocol, "parity": parity})
         ctx.close()
     else:
         res.update({"tflops_per_gpu": flops / t_gemm / 1e9, "frac_of_peak": flops / t_gemm / 1e9 / peaks["bf16_tflops"]})
     return res
 
 
+def bench_gemm_rs_fp8(args, dev, rank, world, dist, peaks):
+    """cfg5: block-scaled FP8 GEMM + reduce-scatter, tp = number of GPUs, M in {1024, 4096, 16384}, N = 8192,
+    K = 28672 / tp per rank.  tp = 1 times the block-scaled GEMM alone."""
+    from flagtree_b200 import GemmRsContext, matmul_fp8_blockscaled
+    from flagtree_b200 import workloads as W
+    n, k_total = 8192, 28672
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    sync_word = torch.zeros(1, device=dev)
+    iters = max(5, min(args.steps, 10))
+    sweep = []
+    for m in (1024, 4096, 16384):
+        case = W.gemm_cfg5(device=dev, tp=world, rank=rank, m=m, n=n, k_total=k_total)
+        flops = case.flops
+        c_full = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        t_gemm = _timed_collective(lambda: matmul_fp8_blockscaled(case.a, case.a_scale, case.b, case.b_scale, out=c_full),
+                                   iters, flush, dist, sync_word, dev)
+        row = {"m": m, "n": n, "k_local": k_total // world, "flops_per_gpu": flops, "gemm_only_ms": t_gemm,
+               "gemm_only_tflops_per_gpu": flops / t_gemm / 1e9}
+        if world > 1:
+            ctx = GemmRsContext(m, n, None, dev, "auto", "auto")
+            out = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)
+            t_fused = _timed_collective(lambda: ctx.fp8(case.a, case.a_scale, case.b, case.b_scale, out), iters, flush, dist, sync_word, dev)
+            ctx.check()
+            ctx.fp8(case.a, case.a_scale, case.b, case.b_scale, out)
+            torch.cuda.synchronize()
+            # fp32 partial of this rank from the dequantised operands, on the device
+            a_s = case.a_scale.repeat_interleave(128, dim=1)
+            b_s = case.b_scale.repeat_interleave(128, dim=0).repeat_interleave(128, dim=1)
+            part = (case.a.view(torch.float8_e4m3fn).float() * a_s) @ (case.b.view(torch.float8_e4m3fn).float() * b_s)
+            parity = _parity_vs_fp32_reduce_scatter(out, part, world, dist, dev)
+            del part, a_s, b_s
+            row.update({"fused_ms": t_fused, "tflops_per_gpu": flops / t_fused / 1e9, "exposed_comm": t_fused / t_gemm - 1.0,
+                        "protocol": ctx.protocol, "parity": parity})
+            ctx.close()
+        sweep.append(row)
+        del case, c_full
+    res = {"workload": f"gemm_rs_fp8_cfg5_n{n}_k{k_total}_tp{world}", "tp": world, "dtype": "fp8 e4m3, fp32 block scales (1x128, 128x128)",
+           "sweep": sweep, "iters": iters, "l2": "256 MB flush write between timed iterations"}
+    return res
+
+
 def run_reference(args, rank, world):
-    """CPU arm: the restatement of the reference's torch idiom on the box's host cores."""
+    """CPU arm: the restatement of the reference's torch idiom on the box's host cores, same workload."""
     if rank != 0:
         return
     n_tok = args.ref_tokens
@@ -223,11 +364,13 @@ def run_reference(args, rank, world):
             times.append(res["seconds"])
     t = sum(times) / len(times)
     val = res["flops"] / t / 1e12
+    cfg = make_config(args.s_q)
+    if n_tok != 4096:
+        cfg["sample_tokens"] = n_tok
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "mla_cfg2_prefill_sq4096_skv4096_h128_topk2048_causal", "sample_tokens": n_tok},
+        "dtype": "bf16", "data": "synthetic", "config": cfg,
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": res["cores"], "kind": "port", "sample": res["sample"]},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -240,13 +383,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--ref-tokens", type=int, default=512, help="query tokens per step of the CPU arm")
+    ap.add_argument("--ref-tokens", type=int, default=4096, help="query tokens per step of the CPU arm (4096 = the whole batch)")
     ap.add_argument("--cpu-tokens", type=int, default=4096, help="query tokens of the cpu_baseline sample")
     ap.add_argument("--s-q", type=int, default=4096, help="query tokens per rank (default = full cfg2)")
+    ap.add_argument("--algo", type=int, default=0, help="algo_id of the sparse-MLA kernel (0 = the library's default)")
+    ap.add_argument("--rs-protocol", default="auto", choices=["auto", "push", "pull", "staged"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM + reduce-scatter section")
-    ap.add_argument("--no-decode", action="store_true", help="skip the paged FP8 decode section (cfg3)")
+    ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM + reduce-scatter sections (cfg4, cfg5)")
+    ap.add_argument("--no-fp8-sweep", action="store_true", help="skip the cfg5 sweep")
+    ap.add_argument("--no-decode", action="store_true", help="skip the paged FP8 decode and cache-write sections (cfg3)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -271,6 +417,7 @@ def main():
 
     from flagtree_b200 import sparse_mla_fwd
     from flagtree_b200 import workloads as W
+    peaks = load_peaks()
 
     case = W.mla_cfg2(device=dev, s_q=args.s_q, s_kv=4096, h=128, topk=2048, rank=rank)
     flops_rank = case.flops
@@ -283,7 +430,7 @@ def main():
         torch.cuda.synchronize()
 
     def step():
-        sparse_mla_fwd(case.q, case.kv, case.indices, case.sm_scale, out=out, lse=lse)
+        sparse_mla_fwd(case.q, case.kv, case.indices, case.sm_scale, out=out, lse=lse, algo=args.algo)
 
     for _ in range(args.warmup):
         step()
@@ -317,6 +464,26 @@ def main():
     ms_per_step = total_ms_max / args.steps
     value = flops_all / (ms_per_step * 1e-3) / 1e12
 
+    # ---- strong scaling: ONE cfg2 batch (rank 0's) split over the ranks, tokens dealt round-robin so that the
+    # short early tokens of the causal batch are spread evenly; same kernel, max over ranks
+    strong = None
+    if world > 1 and args.s_q == 4096:
+        c0 = W.mla_cfg2(device=dev, s_q=4096, s_kv=4096, h=128, topk=2048, rank=0)
+        sq, sidx = c0.q[rank::world].contiguous(), c0.indices[rank::world].contiguous()
+        so = torch.empty(sq.shape[0], 128, 512, dtype=torch.bfloat16, device=dev)
+        sl = torch.empty(sq.shape[0], 128, dtype=torch.float32, device=dev)
+        del c0
+        barrier()
+        ms_s = _time_events(lambda: sparse_mla_fwd(sq, case.kv, sidx, case.sm_scale, out=so, lse=sl, algo=args.algo),
+                            max(5, min(args.steps, 20)))
+        ts = torch.tensor([ms_s], dtype=torch.float64, device=dev)
+        dist.all_reduce(ts, op=dist.ReduceOp.MAX)
+        one_gpu_ms = total_ms_max / args.steps          # a full batch on one GPU takes what a weak-scaling step takes
+        strong = {"s_q_per_gpu": 4096 // world, "ms_per_step": float(ts[0]), "value": FLOPS_CFG2 / (float(ts[0]) * 1e-3) / 1e12,
+                  "unit": UNIT, "efficiency_vs_full_batch_on_one_gpu": one_gpu_ms / (world * float(ts[0])),
+                  "sharding": "query tokens of one batch dealt round-robin over the ranks"}
+        del sq, sidx, so, sl
+
     # ---- end-to-end through the public API with host buffers (pinned), copies inside the timed region
     e2e = None
     if not args.no_e2e:
@@ -347,23 +514,57 @@ def main():
         e2e_ms = float(te[0]) / n_e2e
         h2d = hq.numel() * 2 + hkv.numel() * 2 + hidx.numel() * 4
         d2h = hout.numel() * 2 + hlse.numel() * 4
-        e2e = {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e}
+        # what the host link gives this step at best: the same bytes, one pinned copy each way at the same time
+        # (all ranks at once), no kernel in between
+        s_up, s_dn = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
-    decode_fp8 = None
+        def link_only():
+            cur = torch.cuda.current_stream(dev)
+            s_up.wait_stream(cur); s_dn.wait_stream(cur)
+            with torch.cuda.stream(s_up):
+                case.q.copy_(hq, non_blocking=True)
+                case.indices.copy_(hidx, non_blocking=True)
+            with torch.cuda.stream(s_dn):
+                hout.copy_(out, non_blocking=True)
+                hlse.copy_(lse, non_blocking=True)
+            cur.wait_stream(s_up); cur.wait_stream(s_dn)
+
+        barrier()
+        link_ms = _time_events(link_only, 3, 1)
+        tl = torch.tensor([link_ms], dtype=torch.float64, device=dev)
+        if dist is not None:
+            dist.all_reduce(tl, op=dist.ReduceOp.MAX)
+        link_ms = float(tl[0])
+        e2e = {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e,
+               "host_link_floor_ms": link_ms, "host_link_h2d_gbs": h2d / link_ms / 1e6, "host_link_d2h_gbs": d2h / link_ms / 1e6,
+               "frac_of_host_link_floor": link_ms / e2e_ms,
+               "note": "the step is bound by the host link: the floor is the same bytes copied both ways at once with no kernel"}
+        del hq, hkv, hidx, hout, hlse
+
+    decode_fp8 = kv_write = None
     if world == 1 and not args.no_decode:
-        decode_fp8 = bench_mla_decode_fp8(args, dev, load_peaks())
-    gemm_rs = None
+        decode_fp8 = bench_mla_decode_fp8(args, dev, peaks)
+        kv_write = bench_kv_cache_write(args, dev, peaks)
+    del case, out, lse
+    torch.cuda.empty_cache()
+    gemm_rs = gemm_rs_fp8 = fp8_peak = None
     if not args.no_gemm:
-        gemm_rs = bench_gemm_rs(args, dev, rank, world, dist, load_peaks())
+        gemm_rs = bench_gemm_rs(args, dev, rank, world, dist, peaks)
+        if not args.no_fp8_sweep:
+            if world == 1:
+                fp8_peak = bench_fp8_dense_peak(dev)
+            gemm_rs_fp8 = bench_gemm_rs_fp8(args, dev, rank, world, dist, peaks)
+            if fp8_peak is not None:
+                gemm_rs_fp8["fp8_dense_peak"] = fp8_peak
 
     if rank == 0:
-        peaks = load_peaks()
         avg_launch_ms = sum(per_launch_ms) / len(per_launch_ms)
         achieved = flops_rank / (avg_launch_ms * 1e-3) / 1e12
         peak = peaks["bf16_tflops"]
+        kernel = KERNEL_OF_ALGO.get(args.algo, "sparse_mla kernel")
         prof_traffic = None
-        tpath = os.path.join(ROOT, "profiles", "sparse_mla_stream_kernel_cfg2_traffic.txt")   # figures of the ncu capture, JSON text
+        tpath = os.path.join(ROOT, "profiles", f"{kernel}_cfg2_traffic.txt")   # figures of the ncu capture, JSON text
         if os.path.exists(tpath):
             try:
                 with open(tpath) as f:
@@ -372,7 +573,7 @@ def main():
                 prof_traffic = None
         roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                     "traffic": prof_traffic, "peak_source": f"bf16_tflops (burst) of {peaks['source']} MEASURED_PEAKS.json",
-                    "kernel": "sparse_mla_stream_kernel", "flops_per_launch": flops_rank, "avg_launch_ms": avg_launch_ms}
+                    "kernel": kernel, "flops_per_launch": flops_rank, "avg_launch_ms": avg_launch_ms}
         cpu_b = None
         if not args.no_cpu_baseline:
             cpu_b = cpu_baseline_mla(args.cpu_tokens, reps=3)
@@ -381,13 +582,11 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "mla_cfg2_prefill_sq4096_skv4096_h128_topk2048_causal", "s_q_per_gpu": args.s_q,
-                       "sharding": "query tokens per rank, latent KV replicated, no collective",
-                       "l2": "inputs larger than L2 (q 604 MB per step)", "sm_scale": case.sm_scale,
-                       "flops_per_gpu_step": flops_rank},
+            "config": make_config(args.s_q),
             "roofline": roofline, "cpu_baseline": cpu_b, "e2e": e2e, "gpu_launches": args.steps,
-            "gemm_rs": gemm_rs,
-            "mla_decode_fp8": decode_fp8,
+            "strong_scaling": strong,
+            "gemm_rs": gemm_rs, "gemm_rs_fp8": gemm_rs_fp8,
+            "mla_decode_fp8": decode_fp8, "kv_cache_write": kv_write,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -49,6 +49,24 @@ class GemmFp8Args(C.Structure):
                 ("status", C.c_void_p)]
 
 
+class SparseMlaMergeArgs(C.Structure):
+    """Mirror of `ftb_sparse_mla_merge_args`."""
+    _fields_ = [("part_out", C.c_void_p), ("part_lse", C.c_void_p), ("out", C.c_void_p), ("lse", C.c_void_p),
+                ("s_q", C.c_int32), ("h", C.c_int32), ("n_parts", C.c_int32),
+                ("part_is_fp32", C.c_int32), ("lse_base2", C.c_int32),
+                ("part_stride_part", C.c_int64), ("part_stride_token", C.c_int64), ("part_stride_head", C.c_int64),
+                ("lse_stride_part", C.c_int64), ("lse_stride_part_token", C.c_int64),
+                ("out_stride_token", C.c_int64), ("out_stride_head", C.c_int64), ("lse_stride_token", C.c_int64)]
+
+
+class KvCacheWriteArgs(C.Structure):
+    """Mirror of `ftb_kv_cache_write_args`."""
+    _fields_ = [("rows", C.c_void_p), ("slot_mapping", C.c_void_p), ("kv_cache", C.c_void_p), ("kv_scale", C.c_void_p),
+                ("n_rows", C.c_int32), ("num_pages", C.c_int32), ("page_size", C.c_int32),
+                ("row_stride", C.c_int64), ("workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
+                ("status", C.c_void_p)]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -83,6 +101,14 @@ def load() -> C.CDLL:
                 raise RuntimeError("ftb_sparse_mla_args layout differs between the header and the Python mirror")
             if lib.ftb_sizeof_gemm_args() != C.sizeof(GemmArgs):
                 raise RuntimeError("ftb_gemm_args layout differs between the header and the Python mirror")
+            if lib.ftb_sizeof_sparse_mla_merge_args() != C.sizeof(SparseMlaMergeArgs):
+                raise RuntimeError("ftb_sparse_mla_merge_args layout differs between the header and the Python mirror")
+            lib.ftb_sparse_mla_merge.argtypes = [C.POINTER(SparseMlaMergeArgs), C.c_void_p]
+            if lib.ftb_sizeof_kv_cache_write_args() != C.sizeof(KvCacheWriteArgs):
+                raise RuntimeError("ftb_kv_cache_write_args layout differs between the header and the Python mirror")
+            lib.ftb_kv_cache_write_fp8.argtypes = [C.POINTER(KvCacheWriteArgs), C.c_void_p]
+            lib.ftb_kv_cache_write_workspace_bytes.argtypes = [C.c_int32]
+            lib.ftb_kv_cache_write_workspace_bytes.restype = C.c_int64
             lib.ftb_gemm_bf16.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
             if lib.ftb_sizeof_gemm_fp8_args() != C.sizeof(GemmFp8Args):
                 raise RuntimeError("ftb_gemm_fp8_args layout differs between the header and the Python mirror")
@@ -93,6 +119,7 @@ def load() -> C.CDLL:
             lib.ftb_gemm_rs_ctx_destroy.argtypes = [C.c_void_p]
             lib.ftb_gemm_rs_ctx_set_multicast.argtypes = [C.c_void_p, C.c_void_p]
             lib.ftb_gemm_rs_ctx_set_staged.argtypes = [C.c_void_p, C.c_int]
+            lib.ftb_gemm_rs_ctx_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
             lib.ftb_gemm_rs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
                                         C.c_int64, C.c_void_p, C.c_void_p]
             lib.ftb_gemm_rs_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,

@@ -67,8 +67,26 @@ struct Params {
   // pull mode
   const __nv_bfloat16* mc_part;      // multicast address of the ranks' partial buffers [m, n] (NULL = push mode)
   unsigned int* blk_counter;         // per 128-row block: epilogue-warp arrivals, monotonic over calls
+  long long wait_limit;              // cycles after which a wait for another rank gives up (status = timeout)
 };
 
+
+// SS-form MMA (one CTA or a pair) with the descriptors as 32-bit halves and a compile-time accumulate flag
+template <int NCTA, bool kAccumulate>
+__device__ __forceinline__ void umma_ss_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc) {
+  if constexpr (NCTA == 1) {
+    umma_f16_ss_lohi<kAccumulate>(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc);
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 ad, bd;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 ad, {%1, %2};\n\t"
+        "mov.b64 bd, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], ad, bd, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "n"(kAccumulate ? 1 : 0)
+        : "memory");
+  }
+}
 
 struct Bars {
   unsigned long long full[MAX_STAGES];
@@ -329,40 +347,61 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (even CTA only)
-    if (lane == 0 && cta == 0) {
+    // The whole warp runs the loop and waits; an elected lane (always the same one, so that its commits cover
+    // its MMAs) issues.  Descriptors: only the low word (address) changes, by constants per k step.
+    if (cta == 0) {
       constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, BM * NCTA, BN, 0, 1);
-      uint32_t it = 0, local = 0;
+      const uint64_t ad0 = smem_desc_sw128(base, 16, 1024);
+      const uint64_t bd0 = smem_desc_sw128(base + A_BYTES, B_BLOCK_BYTES, 1024);
+      const uint32_t ad_lo0 = static_cast<uint32_t>(ad0), ad_hi = static_cast<uint32_t>(ad0 >> 32);
+      const uint32_t bd_lo0 = static_cast<uint32_t>(bd0), bd_hi = static_cast<uint32_t>(bd0 >> 32);
+      const uint32_t full0 = smem_u32(&bars->full[0]);
+      const uint32_t empty_own = NCTA == 1 ? smem_u32(&bars->empty[0]) : mapa_shared(smem_u32(&bars->empty[0]), 0);
+      const uint32_t empty_peer = NCTA == 1 ? 0u : mapa_shared(smem_u32(&bars->empty[0]), 1);
+      const uint32_t accf_own = NCTA == 1 ? smem_u32(&bars->acc_full[0]) : mapa_shared(smem_u32(&bars->acc_full[0]), 0);
+      const uint32_t accf_peer = NCTA == 1 ? 0u : mapa_shared(smem_u32(&bars->acc_full[0]), 1);
+      uint32_t s = 0, ph = 0, local = 0;     // stage and its phase bit, tiles done by this group
       for (int t = group; t < p.n_tiles; t += n_groups, ++local) {
         const uint32_t acc = local & 1u;
         mbar_wait(smem_u32(&bars->acc_empty[acc]), ((local >> 1) & 1u) ^ 1u, abort_flag);
         tc_fence_after();
-        for (int kb = 0; kb < kb_total; ++kb, ++it) {
-          const int s = it % STAGES;
-          mbar_wait(smem_u32(&bars->full[s]), (it / STAGES) & 1u, abort_flag);
+        const uint32_t d = tmem + acc * BN;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          mbar_wait(full0 + s * 8, ph, abort_flag);
           tc_fence_after();
-          const uint32_t a_s = base + s * STAGE_BYTES;
-          const uint32_t b_s = a_s + A_BYTES;
+          const uint32_t a_lo = ad_lo0 + ((s * STAGE_BYTES) >> 4);
+          const uint32_t b_lo = bd_lo0 + ((s * STAGE_BYTES) >> 4);
+          if (elect_one()) {
+            if (kb == 0) {
+              umma_ss_lohi<NCTA, false>(d, a_lo, ad_hi, b_lo, bd_hi, kIdesc);
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t ad = smem_desc_sw128(a_s + k * 32, 16, 1024);
-            const uint64_t bd = smem_desc_sw128(b_s + k * 2048, B_BLOCK_BYTES, 1024);
-            if constexpr (NCTA == 1) umma_f16_ss(tmem + acc * BN, ad, bd, kIdesc, (kb | k) != 0 ? 1u : 0u);
-            else umma_f16_ss_pair(tmem + acc * BN, ad, bd, kIdesc, (kb | k) != 0 ? 1u : 0u);
+              for (int k = 1; k < BK / 16; ++k)
+                umma_ss_lohi<NCTA, true>(d, a_lo + ((k * 32) >> 4), ad_hi, b_lo + ((k * 2048) >> 4), bd_hi, kIdesc);
+            } else {
+#pragma unroll
+              for (int k = 0; k < BK / 16; ++k)
+                umma_ss_lohi<NCTA, true>(d, a_lo + ((k * 32) >> 4), ad_hi, b_lo + ((k * 2048) >> 4), bd_hi, kIdesc);
+            }
+            // stage free (in every CTA of the group) once these MMAs have read it
+            if constexpr (NCTA == 1) {
+              umma_commit(empty_own + s * 8);
+            } else {
+              umma_commit_pair(empty_own + s * 8);
+              umma_commit_pair(empty_peer + s * 8);
+            }
           }
-          // stage free (in every CTA of the group) once these MMAs have read it
+          __syncwarp();
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (elect_one()) {
           if constexpr (NCTA == 1) {
-            umma_commit(smem_u32(&bars->empty[s]));
+            umma_commit(accf_own + acc * 8);
           } else {
-            umma_commit_pair(mapa_shared(smem_u32(&bars->empty[s]), 0));
-            umma_commit_pair(mapa_shared(smem_u32(&bars->empty[s]), 1));
+            umma_commit_pair(accf_own + acc * 8);
+            umma_commit_pair(accf_peer + acc * 8);
           }
         }
-        if constexpr (NCTA == 1) {
-          umma_commit(smem_u32(&bars->acc_full[acc]));
-        } else {
-          umma_commit_pair(mapa_shared(smem_u32(&bars->acc_full[acc]), 0));
-          umma_commit_pair(mapa_shared(smem_u32(&bars->acc_full[acc]), 1));
-        }
+        __syncwarp();
       }
     }
   } else if (warp < 6) {
@@ -394,7 +433,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const long long t0 = clock64();
             while (ld_acquire_sys(done) + 1u < p.epoch) {
               if (*abort_flag) break;
-              if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; break; }
+              if (clock64() - t0 > p.wait_limit) { *abort_flag = 1; break; }
             }
           }
         }
@@ -408,7 +447,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const long long t0 = clock64();
             while (ld_acquire_sys(done) + 1u < p.epoch) {
               if (*abort_flag) break;
-              if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; break; }
+              if (clock64() - t0 > p.wait_limit) { *abort_flag = 1; break; }
             }
           }
         }
@@ -432,7 +471,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               const long long t0 = clock64();
               while (ld_acquire_sys(f) < p.flag_target) {
                 if (*abort_flag) break;
-                if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; break; }
+                if (clock64() - t0 > p.wait_limit) { *abort_flag = 1; break; }
               }
             }
           }
@@ -598,7 +637,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
               const long long t0 = clock64();
               while (ld_acquire_sys(f) < p.epoch) {
                 if (*abort_flag) break;
-                if (clock64() - t0 > kWaitLimitCycles) { *abort_flag = 1; break; }
+                if (clock64() - t0 > p.wait_limit) { *abort_flag = 1; break; }
                 __nanosleep(100);
               }
             }
@@ -691,14 +730,20 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b, cons
   return check_cuda(e, "gemm launch");
 }
 
-static int launch_gemm(const void* a, const void* b, int m, int n, int k, long long lda, long long ldb,
-                       gemm::Params& p, cudaStream_t st) {
+static int gemm_operands_ok(const void* a, const void* b, int m, int n, int k, long long lda, long long ldb) {
   if (m <= 0 || n <= 0 || k <= 0) { set_last_error("gemm: bad sizes m=%d n=%d k=%d", m, n, k); return FTB_ERR_INVALID; }
   if ((n % 8) || (k % 8) || (lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(a) & 15) ||
       (reinterpret_cast<uintptr_t>(b) & 15)) {
     set_last_error("gemm: n, k and the leading dimensions must be multiples of 8 and pointers 16-byte aligned");
     return FTB_ERR_INVALID;
   }
+  return FTB_OK;
+}
+
+static int launch_gemm(const void* a, const void* b, int m, int n, int k, long long lda, long long ldb,
+                       gemm::Params& p, cudaStream_t st) {
+  const int ok = gemm_operands_ok(a, b, m, n, k, lda, ldb);
+  if (ok != FTB_OK) return ok;
   CUtensorMap tm_a, tm_b;
   if (!make_tmap_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, m, k, lda, gemm::BM, gemm::BK) ||
       !make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, n, ldb, gemm::BK, 64)) {
@@ -746,6 +791,7 @@ struct ftb_gemm_rs_ctx {
   unsigned int epoch;
   int form;                      // 0 = not used yet, 1 = fused bf16 calls, 2 = staged calls (bf16 or FP8): the flag words differ
   int staged;                    // bf16 calls: 0 = fused kernel (push or pull), 1 = staged (GEMM per shard group + one reduce)
+  long long wait_limit;          // cycles a device-side wait for another rank may last
 };
 
 extern "C" FTB_API int ftb_gemm_rs_workspace_bytes(int m, int n, int tp, int64_t* recv_bytes, int64_t* flag_bytes) {
@@ -773,19 +819,26 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
   c->epoch = 0;
   c->form = 0;
   c->staged = 0;
+  c->wait_limit = kWaitLimitCycles;
   for (int i = 0; i < tp; ++i) {
     if (!recv_ptrs[i] || !flag_ptrs[i]) { delete c; set_last_error("ftb_gemm_rs_ctx_create: null peer pointer"); return FTB_ERR_INVALID; }
     c->recv[i] = recv_ptrs[i];
     c->flags[i] = reinterpret_cast<unsigned int*>(flag_ptrs[i]);
   }
   c->mc_recv = nullptr;
+  c->d_counter = nullptr;
   c->d_blk_counter = nullptr;
   const int m_blocks = m / gemm::BM;
   cudaError_t e = cudaMalloc(&c->d_counter, sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMemset(c->d_counter, 0, sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMalloc(&c->d_blk_counter, sizeof(unsigned int) * m_blocks);
   if (e == cudaSuccess) e = cudaMemset(c->d_blk_counter, 0, sizeof(unsigned int) * m_blocks);
-  if (e != cudaSuccess) { delete c; return check_cuda(e, "ftb_gemm_rs_ctx_create"); }
+  if (e != cudaSuccess) {
+    cudaFree(c->d_counter);        // cudaFree(nullptr) is a no-op
+    cudaFree(c->d_blk_counter);
+    delete c;
+    return check_cuda(e, "ftb_gemm_rs_ctx_create");
+  }
   *out = c;
   return FTB_OK;
 }
@@ -794,6 +847,12 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_set_multicast(ftb_gemm_rs_ctx* c, void* m
   if (!c) { set_last_error("ftb_gemm_rs_ctx_set_multicast: null context"); return FTB_ERR_INVALID; }
   if (c->epoch != 0) { set_last_error("ftb_gemm_rs_ctx_set_multicast: must be called before the first ftb_gemm_rs"); return FTB_ERR_INVALID; }
   c->mc_recv = mc_recv_ptr;
+  return FTB_OK;
+}
+
+extern "C" FTB_API int ftb_gemm_rs_ctx_set_wait_limit(ftb_gemm_rs_ctx* c, int64_t cycles) {
+  if (!c || cycles <= 0) { set_last_error("ftb_gemm_rs_ctx_set_wait_limit: need a context and a positive cycle count"); return FTB_ERR_INVALID; }
+  c->wait_limit = cycles;
   return FTB_OK;
 }
 
@@ -821,13 +880,13 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* c) {
 namespace ftb {
 namespace gemm {
 
-__global__ void rs_fp8_wait_kernel(const unsigned int* flags, int first, int tp, unsigned int target, int* status) {
+__global__ void rs_fp8_wait_kernel(const unsigned int* flags, int first, int tp, unsigned int target, int* status, long long wait_limit) {
   const int i = threadIdx.x;
   if (i >= tp) return;
   if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
   const long long t0 = clock64();
   while (ld_acquire_sys(flags + first + i) < target) {
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > wait_limit) {
       if (status != nullptr) atomicCAS(status, 0, FTB_ERR_TIMEOUT);
       return;
     }
@@ -840,16 +899,18 @@ struct RsFp8Ptrs {
 };
 
 // ranks d0 .. d0 + nd - 1 learn that this rank's partial of their rows is complete
-__global__ void rs_fp8_publish_kernel(RsFp8Ptrs q, int d0, int nd, int word, unsigned int value) {
+__global__ void rs_fp8_publish_kernel(RsFp8Ptrs q, int d0, int nd, int word, unsigned int value, const int* status) {
   const int d = d0 + static_cast<int>(threadIdx.x);
   if (static_cast<int>(threadIdx.x) >= nd) return;
+  // after a timeout the partial of this call may be incomplete: the peers must not be told otherwise
+  if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
   __threadfence_system();
   st_release_sys(q.flags[d] + word, value);
 }
 
 __global__ void __launch_bounds__(256) rs_fp8_reduce_kernel(RsFp8Ptrs q, const __nv_bfloat16* mc_part, __nv_bfloat16* out,
                                                            long long ldo, int shard_rows, int n, int rank, int tp,
-                                                           unsigned int epoch, unsigned int* counter, int* status) {
+                                                           unsigned int epoch, unsigned int* counter, int* status, long long wait_limit) {
   __shared__ int s_abort;
   if (threadIdx.x == 0) s_abort = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
   __syncthreads();
@@ -857,7 +918,7 @@ __global__ void __launch_bounds__(256) rs_fp8_reduce_kernel(RsFp8Ptrs q, const _
     // partial `epoch` of every rank is complete
     const long long t0 = clock64();
     while (ld_acquire_sys(q.flags[rank] + threadIdx.x) < epoch) {
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > wait_limit) {
         s_abort = 1;
         if (status != nullptr) atomicCAS(status, 0, FTB_ERR_TIMEOUT);
         break;
@@ -950,7 +1011,7 @@ static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int
     q.recv[i] = reinterpret_cast<const __nv_bfloat16*>(c->recv[i]);
   }
   // every peer has read the partial of the call before (their words start at [tp])
-  gemm::rs_fp8_wait_kernel<<<1, 32, 0, st>>>(c->flags[c->rank], c->tp, c->tp, c->epoch - 1u, status);
+  gemm::rs_fp8_wait_kernel<<<1, 32, 0, st>>>(c->flags[c->rank], c->tp, c->tp, c->epoch - 1u, status, c->wait_limit);
   int rc = check_cuda(cudaGetLastError(), "rs wait launch");
   if (rc != FTB_OK) return rc;
   // Shards per GEMM launch.  Nothing overlaps the exchange in this protocol (a rank's own group comes last, so
@@ -966,7 +1027,7 @@ static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int
     const long long row0 = static_cast<long long>(gi) * g * c->shard_rows;
     rc = gemm_rows(row0, g * c->shard_rows, part + row0 * c->n);
     if (rc != FTB_OK) return rc;
-    gemm::rs_fp8_publish_kernel<<<1, 32, 0, st>>>(q, gi * g, g, c->rank, c->epoch);
+    gemm::rs_fp8_publish_kernel<<<1, 32, 0, st>>>(q, gi * g, g, c->rank, c->epoch, status);
     rc = check_cuda(cudaGetLastError(), "rs publish launch");
     if (rc != FTB_OK) return rc;
   }
@@ -975,7 +1036,7 @@ static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   gemm::rs_fp8_reduce_kernel<<<sms * 2, 256, 0, st>>>(q, reinterpret_cast<const __nv_bfloat16*>(c->mc_recv),
                                                       reinterpret_cast<__nv_bfloat16*>(out), ldo, c->shard_rows, c->n, c->rank,
-                                                      c->tp, c->epoch, c->d_counter, status);
+                                                      c->tp, c->epoch, c->d_counter, status, c->wait_limit);
   return check_cuda(cudaGetLastError(), "rs reduce launch");
 }
 
@@ -983,6 +1044,9 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
                                    int64_t lda, int64_t ldb, int64_t ldo, int32_t* status, void* stream) {
   if (!c || !a || !b || !out) { set_last_error("ftb_gemm_rs: null pointer"); return FTB_ERR_INVALID; }
   if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs: out alignment"); return FTB_ERR_INVALID; }
+  // a rejected call must leave the call counter alone: the peers' flag targets are derived from it
+  const int ok = gemm_operands_ok(a, b, c->m, c->n, k_local, lda, ldb);
+  if (ok != FTB_OK) return ok;
   if (c->staged) {
     if (c->form == 1) { set_last_error("ftb_gemm_rs: this context has served fused calls"); return FTB_ERR_INVALID; }
     c->form = 2;
@@ -1020,6 +1084,7 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
   p.status = status;
   p.mc_part = reinterpret_cast<const __nv_bfloat16*>(c->mc_recv);
   p.blk_counter = c->d_blk_counter;
+  p.wait_limit = c->wait_limit;
   return launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
 }
 
@@ -1030,6 +1095,10 @@ extern "C" FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* c, const void* a, const 
   if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs_fp8: out alignment"); return FTB_ERR_INVALID; }
   if (c->form == 1) { set_last_error("ftb_gemm_rs_fp8: this context serves fused bf16 calls (the flag words differ)"); return FTB_ERR_INVALID; }
   if ((c->n % 128) || (k_local % 128)) { set_last_error("ftb_gemm_rs_fp8: n and k_local must be multiples of 128"); return FTB_ERR_INVALID; }
+  if (k_local <= 0 || (lda % 16) || (ldb % 16) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) {
+    set_last_error("ftb_gemm_rs_fp8: operands must be 16-byte aligned with leading dimensions that are multiples of 16");
+    return FTB_ERR_INVALID;
+  }
   c->form = 2;
   const int n = c->n;
   auto rows = [&](long long row0, int m_rows, __nv_bfloat16* dst) -> int {

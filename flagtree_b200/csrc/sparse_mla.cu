@@ -72,19 +72,26 @@ struct MiscSmem {
   float row_scale[kBN];         // per-row dequantisation scale (FP8 form)
 };
 
-__device__ __forceinline__ int resolve_row(const MlaParams& p, int token, int logical, bool& ok, float& scale) {
-  // Returns the physical row for a top-k entry; ok = false for padding / out-of-range entries.
+__device__ __forceinline__ int resolve_row(const MlaParams& p, int token, int logical, bool& ok, float& scale, bool& bad) {
+  // Returns the physical row for a top-k entry; ok = false for padding (-1, or at / past the context length);
+  // bad = true for an entry that is neither padding nor a row of the cache (never dereferenced).
   scale = 1.0f;
-  if (logical < 0) { ok = false; return 0; }
+  ok = false;
+  bad = false;
+  if (logical < 0) { bad = logical < -1; return 0; }
   if (p.block_table == nullptr) {
     ok = logical < p.s_kv;
+    bad = !ok;
     return ok ? logical : 0;
   }
   const int seq = token / p.q_per_seq;
-  if (logical >= p.context_lens[seq]) { ok = false; return 0; }
-  const int page = p.block_table[seq * p.bt_stride + logical / p.page_size];
+  if (logical >= p.context_lens[seq]) return 0;
+  const int slot = logical / p.page_size;
+  if (slot >= p.bt_stride) { bad = true; return 0; }      // a context length longer than the table's row
+  const int page = p.block_table[seq * p.bt_stride + slot];
   const int row = page * p.page_size + logical % p.page_size;
-  ok = row >= 0 && row < p.s_kv;
+  ok = page >= 0 && row >= 0 && row < p.s_kv;
+  bad = !ok;
   if (ok && p.kv_scale != nullptr) scale = p.kv_scale[page];
   return ok ? row : 0;
 }
@@ -103,11 +110,20 @@ __global__ void __launch_bounds__(256) mla_dequant_rows_kernel(const MlaParams p
     const int token = static_cast<int>(r / p.topk);
     const int j = static_cast<int>(r - static_cast<long long>(token) * p.topk);
     const int logical = p.indices[static_cast<long long>(token) * p.idx_st + j];
-    bool ok;
+    bool ok, bad;
     float sc;
-    const int row = resolve_row(p, token, logical, ok, sc);
+    const int row = resolve_row(p, token, logical, ok, sc, bad);
+    if (bad && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, FTB_ERR_BAD_INDEX);
     if (lane == 0) out_idx[r] = ok ? static_cast<int32_t>(r) : -1;
-    if (!ok) continue;
+    if (!ok) {
+      // the attention kernel fetches table row 0 for every masked entry (and multiplies it by zero): that row
+      // must hold finite numbers even when its own entry is masked
+      if (r == 0) {
+        uint4* z = reinterpret_cast<uint4*>(table);
+        for (int c16 = lane; c16 < kDqk * 2 / 16; c16 += 32) z[c16] = make_uint4(0, 0, 0, 0);
+      }
+      continue;
+    }
     const uint8_t* src = kvp + static_cast<long long>(row) * p.kv_sr;
     uint32_t* dst = reinterpret_cast<uint32_t*>(table + r * kDqk);
     // 36 chunks of 16 bytes: every lane one, lanes 0-3 a second one
@@ -223,10 +239,10 @@ __global__ void __launch_bounds__(kThreads, 1) sparse_mla_fwd_kernel(const MlaPa
       const int j = tile * kBN + tid;
       int logical = -1;
       if (j < p.topk) logical = p.indices[static_cast<long long>(token) * p.idx_st + j];
-      bool ok;
+      bool ok, bad;
       float sc;
-      const int row = resolve_row(p, token, logical, ok, sc);
-      if (!ok && logical >= 0 && p.block_table == nullptr) misc->bad_index = 1;
+      const int row = resolve_row(p, token, logical, ok, sc, bad);
+      if (bad) misc->bad_index = 1;
       misc->rows[tid] = row;
       misc->row_scale[tid] = sc;
       const uint32_t m = __ballot_sync(0xffffffffu, ok);
@@ -490,6 +506,71 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const float* __re
   }
 }
 
+
+// The same merge for partial results that come from outside the library: the outputs and log-sum-exps of
+// several sparse-MLA forwards over disjoint parts of the key/value rows (a long context sharded over GPUs, or
+// a caller's own split of the top-k list).  part k of (token, head): `part_out + k * ps + token * ts + head * hs`
+// (T = bf16, what ftb_sparse_mla_fwd writes, or fp32), its log-sum-exp `part_lse + k * lps + token * lts + head`
+// (natural log, or base 2 when lse_base2; -inf = the part saw no valid row).  One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(256) sparse_mla_merge_parts_kernel(const T* __restrict__ part_out, const float* __restrict__ part_lse,
+                                                                     __nv_bfloat16* out, float* lse, int s_q, int h, int n_parts,
+                                                                     long long ps, long long ts, long long hs, long long lps,
+                                                                     long long lts, long long out_st, long long out_sh,
+                                                                     long long lse_st, int lse_base2) {
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (w >= s_q * h) return;
+  const int token = w / h, head = w - token * h;
+  const float to2 = lse_base2 ? 1.0f : 1.4426950408889634f;      // natural log -> base 2
+  const float* lrow = part_lse + static_cast<long long>(token) * lts + head;
+  float mx = -INFINITY;
+  for (int k = 0; k < n_parts; ++k) mx = fmaxf(mx, lrow[k * lps] * to2);
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.0f;
+  float wsum = 0.0f;
+  if (mx != -INFINITY) {
+    for (int k = 0; k < n_parts; ++k) {
+      const float l2 = lrow[k * lps] * to2;
+      if (l2 == -INFINITY) continue;
+      const float wk = exp2f(l2 - mx);
+      wsum += wk;
+      const T* src = part_out + k * ps + static_cast<long long>(token) * ts + static_cast<long long>(head) * hs + lane * 16;
+      if constexpr (sizeof(T) == 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 v = reinterpret_cast<const float4*>(src)[j];
+          acc[4 * j] += wk * v.x; acc[4 * j + 1] += wk * v.y; acc[4 * j + 2] += wk * v.z; acc[4 * j + 3] += wk * v.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint4 v = reinterpret_cast<const uint4*>(src)[j];
+          const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[8 * j + 2 * e] += wk * __uint_as_float(u[e] << 16);
+            acc[8 * j + 2 * e + 1] += wk * __uint_as_float(u[e] & 0xffff0000u);
+          }
+        }
+      }
+    }
+  }
+  const float inv = wsum > 0.0f ? 1.0f / wsum : 0.0f;
+  uint4 o[2];
+  uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) ow[j] = pack_bf16x2(acc[2 * j] * inv, acc[2 * j + 1] * inv);
+  uint4* dst = reinterpret_cast<uint4*>(out + token * out_st + head * out_sh + lane * 16);
+  dst[0] = o[0];
+  dst[1] = o[1];
+  if (lane == 0) {
+    const float l2 = wsum > 0.0f ? mx + log2f(wsum) : -INFINITY;
+    lse[token * lse_st + head] = (lse_base2 || l2 == -INFINITY) ? l2 : l2 * 0.6931471805599453f;
+  }
+}
+
 }  // namespace ftb
 
 // --------------------------------------------------------------------------------- host side
@@ -499,11 +580,9 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_kernel(const float* __re
 namespace ftb {
 void set_last_error(const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
-int launch_sparse_mla_pair(const ftb_sparse_mla_args* a, cudaStream_t st);
-int launch_sparse_mla_duo(const ftb_sparse_mla_args* a, cudaStream_t st);
-int launch_sparse_mla_duo2(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_stream64(const ftb_sparse_mla_args* a, cudaStream_t st);
+int launch_sparse_mla_fifo(const ftb_sparse_mla_args* a, cudaStream_t st);
 }  // namespace ftb
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -539,19 +618,20 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     set_last_error("ftb_sparse_mla_fwd: kv row stride must be a multiple of 8 elements");
     return FTB_ERR_INVALID;
   }
-  if (a->algo_id < 0 || a->algo_id > 7) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
+  if (a->algo_id < 0 || a->algo_id > 8) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
   if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
   // algo 0 = default; algo 1 = one CTA per (token, output half), which is also the kernel of the FP8 paged
-  // form, of the split form and of the debug score tap; algo 2 = CTA pair sharing one MMA (cta_group::2);
-  // algo 3 = role-split CTA pair (scores in one CTA, values in the other); algo 4 = the same with Q in
-  // tensor memory and TMA row gathers; algo 5 = algo 4 as persistent pairs (the default); algo 7 = algo 5
-  // with tiles of 64 rows in rings two tiles deep.
+  // form, of the split form and of the diagnostic score tap; algo 5 = persistent role-split CTA pairs (scores
+  // in one CTA, values in the other, Q in tensor memory, TMA row gathers); algo 7 = algo 5 with tiles of 64
+  // rows in rings two tiles deep; algo 8 = algo 5 with every ring slot refilled by all gather warps together.
+  if (a->algo_id == 2 || a->algo_id == 3 || a->algo_id == 4) {
+    set_last_error("ftb_sparse_mla_fwd: algo_id %d (an earlier CTA-pair kernel) is no longer part of the library", a->algo_id);
+    return FTB_ERR_UNSUPPORTED;
+  }
   if (!a->kv_is_fp8 && a->dbg_scores == nullptr && a->n_splits <= 1) {
-    if (a->algo_id == 2) return launch_sparse_mla_pair(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 3) return launch_sparse_mla_duo(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 4) return launch_sparse_mla_duo2(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 5) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 7) return launch_sparse_mla_stream64(a, reinterpret_cast<cudaStream_t>(stream));
+    if (a->algo_id == 8) return launch_sparse_mla_fifo(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 0) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));   // fastest so far
   }
   MlaParams p;
@@ -698,4 +778,38 @@ extern "C" FTB_API int ftb_sparse_mla_fwd_static_scratch(const ftb_sparse_mla_ar
     b.workspace_bytes = 0;
   }
   return ftb_sparse_mla_fwd(&b, stream);
+}
+
+
+extern "C" FTB_API int ftb_sparse_mla_merge(const ftb_sparse_mla_merge_args* a, void* stream) {
+  using namespace ftb;
+  if (a == nullptr) { set_last_error("ftb_sparse_mla_merge: args is NULL"); return FTB_ERR_INVALID; }
+  if (a->s_q < 0 || a->h <= 0 || a->n_parts <= 0) {
+    set_last_error("ftb_sparse_mla_merge: bad sizes s_q=%d h=%d n_parts=%d", a->s_q, a->h, a->n_parts);
+    return FTB_ERR_INVALID;
+  }
+  if (a->s_q == 0) return FTB_OK;
+  if (!a->part_out || !a->part_lse || !a->out || !a->lse) { set_last_error("ftb_sparse_mla_merge: null pointer"); return FTB_ERR_INVALID; }
+  if (a->part_is_fp32 != 0 && a->part_is_fp32 != 1) { set_last_error("ftb_sparse_mla_merge: part_is_fp32 must be 0 or 1"); return FTB_ERR_INVALID; }
+  const int el = a->part_is_fp32 ? 4 : 8;      // elements per 16 bytes
+  if (!aligned16(a->part_out) || !aligned16(a->out) || (a->part_stride_part % el) || (a->part_stride_token % el) ||
+      (a->part_stride_head % el) || (a->out_stride_token % 8) || (a->out_stride_head % 8)) {
+    set_last_error("ftb_sparse_mla_merge: part_out / out must be 16-byte aligned with strides that keep rows 16-byte aligned");
+    return FTB_ERR_INVALID;
+  }
+  if (static_cast<long long>(a->s_q) * a->h > (1LL << 26)) { set_last_error("ftb_sparse_mla_merge: s_q * h too large for one launch"); return FTB_ERR_UNSUPPORTED; }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int warps = a->s_q * a->h;
+  const unsigned blocks = static_cast<unsigned>((static_cast<long long>(warps) * 32 + 255) / 256);
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(a->out);
+  if (a->part_is_fp32) {
+    sparse_mla_merge_parts_kernel<float><<<blocks, 256, 0, st>>>(reinterpret_cast<const float*>(a->part_out), a->part_lse, out, a->lse, a->s_q, a->h,
+        a->n_parts, a->part_stride_part, a->part_stride_token, a->part_stride_head, a->lse_stride_part, a->lse_stride_part_token,
+        a->out_stride_token, a->out_stride_head, a->lse_stride_token, a->lse_base2);
+  } else {
+    sparse_mla_merge_parts_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(a->part_out), a->part_lse, out, a->lse,
+        a->s_q, a->h, a->n_parts, a->part_stride_part, a->part_stride_token, a->part_stride_head, a->lse_stride_part,
+        a->lse_stride_part_token, a->out_stride_token, a->out_stride_head, a->lse_stride_token, a->lse_base2);
+  }
+  return check_cuda(cudaGetLastError(), "sparse_mla_merge launch");
 }

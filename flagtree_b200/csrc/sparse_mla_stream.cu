@@ -1,6 +1,6 @@
 // Top-k sparse MLA forward, persistent role-split CTA pairs (bf16 KV).
 //
-// The pair works as in sparse_mla_duo2.cu: CTA 0 computes S = Q.K^T (Q in tensor memory, K column blocks
+// A pair of CTAs (a cluster of 2) splits the roles: CTA 0 computes S = Q.K^T (Q in tensor memory, K column blocks
 // in a 9-slot ring filled by TMA gather4) and the softmax, P travels to CTA 1 by bulk copies over
 // distributed shared memory, CTA 1 accumulates O += P.V in tensor memory.  Here one pair does not serve
 // one query token and exit; the grid holds as many pairs as fit on the device at once and pair k walks
@@ -399,7 +399,7 @@ sparse_mla_stream_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const bool ok = nxt[j] >= 0 && nxt[j] < p.s_kv;
-              if (c == 0 && nxt[j] >= p.s_kv) m0->bad_index = 1;
+              if (c == 0 && (nxt[j] >= p.s_kv || nxt[j] < -1)) m0->bad_index = 1;
               row[j] = ok ? nxt[j] : 0;
               nib |= ok ? (1u << j) : 0u;
             }

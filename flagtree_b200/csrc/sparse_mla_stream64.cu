@@ -435,7 +435,7 @@ sparse_mla_stream64_kernel(const __grid_constant__ CUtensorMap tm_kv, const __gr
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const bool ok = nxt[j] >= 0 && nxt[j] < p.s_kv;
-              if (c == 0 && nxt[j] >= p.s_kv) m0->bad_index = 1;
+              if (c == 0 && (nxt[j] >= p.s_kv || nxt[j] < -1)) m0->bad_index = 1;
               row[j] = ok ? nxt[j] : 0;
               nib |= ok ? (1u << j) : 0u;
             }

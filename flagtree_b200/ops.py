@@ -292,6 +292,82 @@ def decode_attention_fwd(q, k_buffer, v_buffer, o, req_to_token, b_seq_len, attn
     return o
 
 
+def sparse_mla_merge(part_out: torch.Tensor, part_lse: torch.Tensor, *, lse_base2: bool = False,
+                     out: Optional[torch.Tensor] = None, lse: Optional[torch.Tensor] = None
+                     ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Merge partial sparse-MLA results over disjoint sets of key/value rows by their log-sum-exps: the
+    reference's second launch (`_decode_softmax_reducev_fwd`, test_accuracy_musa_vllm_mla.py:480-510, kernel
+    :426-477) as an operation of its own.
+
+    part_out [n_parts, S_q, h, 512] bf16 (outputs of `sparse_mla_fwd`) or fp32; part_lse [n_parts, S_q, h] fp32
+    (natural log unless `lse_base2`; -inf marks a part without a valid row).  Returns (out [S_q, h, 512] bf16,
+    lse [S_q, h] fp32).  Use: a context whose latent rows are sharded over GPUs -- every rank runs
+    `sparse_mla_fwd` with `shard_indices(indices, lo, hi)`, the parts are all-gathered, this merges them."""
+    _require_cuda(part_out, part_lse)
+    assert part_out.dim() == 4 and part_lse.dim() == 3 and part_out.shape[3] == D_V
+    assert part_out.dtype in (torch.bfloat16, torch.float32) and part_lse.dtype == torch.float32
+    n_parts, s_q, h, _ = part_out.shape
+    assert part_lse.shape == (n_parts, s_q, h)
+    assert part_out.stride(3) == 1 and part_lse.stride(2) == 1, "innermost dimension must be contiguous"
+    if out is None:
+        out = torch.empty(s_q, h, D_V, dtype=torch.bfloat16, device=part_out.device)
+    if lse is None:
+        lse = torch.empty(s_q, h, dtype=torch.float32, device=part_out.device)
+    assert out.shape == (s_q, h, D_V) and out.dtype == torch.bfloat16 and out.stride(2) == 1
+    assert lse.shape == (s_q, h) and lse.dtype == torch.float32 and lse.stride(1) == 1
+    a = _lib.SparseMlaMergeArgs()
+    a.part_out, a.part_lse, a.out, a.lse = part_out.data_ptr(), part_lse.data_ptr(), out.data_ptr(), lse.data_ptr()
+    a.s_q, a.h, a.n_parts = s_q, h, n_parts
+    a.part_is_fp32, a.lse_base2 = int(part_out.dtype == torch.float32), int(lse_base2)
+    a.part_stride_part, a.part_stride_token, a.part_stride_head = part_out.stride(0), part_out.stride(1), part_out.stride(2)
+    a.lse_stride_part, a.lse_stride_part_token = part_lse.stride(0), part_lse.stride(1)
+    a.out_stride_token, a.out_stride_head, a.lse_stride_token = out.stride(0), out.stride(1), lse.stride(0)
+    with torch.cuda.device(part_out.device):
+        rc = _lib.load().ftb_sparse_mla_merge(C.byref(a), C.c_void_p(_stream_ptr(part_out.device)))
+    _lib.check(rc, "sparse_mla_merge")
+    return out, lse
+
+
+def shard_indices(indices: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
+    """Index list of a rank that holds latent rows [lo, hi) of the context: entries inside the range become
+    local row numbers, all others -1 (padding).  The -1 entries may sit anywhere in the list."""
+    inside = (indices >= lo) & (indices < hi)
+    return torch.where(inside, indices - lo, torch.full_like(indices, -1))
+
+
+def kv_cache_write_fp8(rows: torch.Tensor, slot_mapping: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Tensor,
+                       page_size: int = 64, *, check: bool = False) -> None:
+    """Quantise new latent rows to e4m3 with one fp32 scale per page and scatter them into the paged cache, in
+    place: the producer of the format `sparse_mla_fwd_paged` reads.  Analogue of the reference's quantising
+    cache writer `destindex_copy_quantize_int4kv_init`
+    (third_party/hcu/python/test/unit/sglang/decode_attention_int4kv.py:934).
+
+    rows [n, 576] bf16; slot_mapping [n] int32, slot = page * page_size + position (-1 skips the row; slots of
+    one call must be distinct); kv_cache [num_pages, page_size, 576] e4m3 bytes; kv_scale [num_pages] fp32, 0 for
+    a page that holds nothing yet.  A page's scale only grows: max(old, max|new rows| / 448); when it grows for
+    a page that already held rows, those bytes are requantised to the new scale first."""
+    _require_cuda(rows, slot_mapping, kv_cache, kv_scale)
+    assert rows.dim() == 2 and rows.shape[1] == D_QK and rows.dtype == torch.bfloat16 and rows.stride(1) == 1
+    assert slot_mapping.dtype == torch.int32 and slot_mapping.shape == (rows.shape[0],) and slot_mapping.is_contiguous()
+    assert kv_cache.dtype in (torch.uint8, torch.float8_e4m3fn) and kv_cache.is_contiguous()
+    assert kv_cache.dim() == 3 and kv_cache.shape[1] == page_size and kv_cache.shape[2] == D_QK
+    assert kv_scale.dtype == torch.float32 and kv_scale.shape == (kv_cache.shape[0],) and kv_scale.is_contiguous()
+    lib = _lib.load()
+    num_pages = kv_cache.shape[0]
+    ws = torch.empty(int(lib.ftb_kv_cache_write_workspace_bytes(num_pages)), dtype=torch.uint8, device=rows.device)
+    status = torch.zeros(1, dtype=torch.int32, device=rows.device) if check else None
+    a = _lib.KvCacheWriteArgs()
+    a.rows, a.slot_mapping, a.kv_cache, a.kv_scale = rows.data_ptr(), slot_mapping.data_ptr(), kv_cache.data_ptr(), kv_scale.data_ptr()
+    a.n_rows, a.num_pages, a.page_size = rows.shape[0], num_pages, page_size
+    a.row_stride = rows.stride(0)
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.status = status.data_ptr() if status is not None else None
+    with torch.cuda.device(rows.device):
+        rc = lib.ftb_kv_cache_write_fp8(C.byref(a), C.c_void_p(_stream_ptr(rows.device)))
+    _lib.check(rc, "kv_cache_write_fp8")
+    _check_status(status, "kv_cache_write_fp8")
+
+
 # ------------------------------------------------------------------------------------- GEMM
 def matmul(a: torch.Tensor, b: torch.Tensor, acc_dtype=None, input_precision=None, fp8_fast_accum=True,
            output_dtype=None, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -450,27 +526,70 @@ class GemmRsContext:
         _lib.check(rc, "gemm_rs_fp8")
         return out
 
+    def set_wait_limit(self, cycles: int):
+        """Longest device-side wait for another rank, in SM clock cycles (default about one second)."""
+        _lib.check(_lib.load().ftb_gemm_rs_ctx_set_wait_limit(self._ctx, int(cycles)), "gemm_rs set_wait_limit")
+
     def check(self):
+        """Reads the device status word (one host synchronisation) and raises RuntimeError on a timeout.  After a
+        timeout the context is dead on every rank: close it and create a new one."""
         _check_status(self.status, "gemm_rs")
 
     def close(self):
+        """Collective over the group.  A peer's kernel may still read this rank's partial or store its `done`
+        word into this rank's flags after this rank's own stream has drained, so the buffers are only released
+        between two barriers: every rank idle, peers' mappings closed, then the memory itself."""
         if self._ctx is not None:
+            import torch.distributed as dist
             torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
             _lib.load().ftb_gemm_rs_ctx_destroy(self._ctx)
             self._ctx = None
+            self.recv.close_peers()
+            self.flags.close_peers()
+            dist.barrier(self.group)
             self.recv.close()
             self.flags.close()
 
 
-_RS_CONTEXTS = {}
+_RS_CONTEXTS = {}     # (form, M, N, device, group key) -> (group, context); holding the group keeps its id unique
 
 
-def gemm_rs(a: torch.Tensor, b: torch.Tensor, group=None, *, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def _rs_context(form: str, m: int, n: int, group, device) -> "GemmRsContext":
+    key = (form, m, n, device.index, id(group))
+    hit = _RS_CONTEXTS.get(key)
+    if hit is None or hit[0] is not group:
+        hit = _RS_CONTEXTS[key] = (group, GemmRsContext(m, n, group, device))
+    return hit[1]
+
+
+def gemm_rs_close_all():
+    """Closes every workspace that `gemm_rs` / `gemm_rs_fp8` created (collective over their groups)."""
+    for key in sorted(_RS_CONTEXTS, key=lambda k: (k[0], k[1], k[2], k[3])):
+        _RS_CONTEXTS[key][1].close()
+    _RS_CONTEXTS.clear()
+
+
+def gemm_rs(a: torch.Tensor, b: torch.Tensor, group=None, *, out: Optional[torch.Tensor] = None,
+            check: bool = False) -> torch.Tensor:
     """Row-parallel GEMM fused with reduce-scatter: rank r passes A_r [M, K/tp] and B_r [K/tp, N] and gets
     rows [r*M/tp, (r+1)*M/tp) of sum_r A_r @ B_r as bf16.  Collective over `group`; the workspace of each
-    (M, N, group) is created on first use and cached."""
-    key = (a.shape[0], b.shape[1], id(group), a.device.index)
-    ctx = _RS_CONTEXTS.get(key)
-    if ctx is None:
-        ctx = _RS_CONTEXTS[key] = GemmRsContext(a.shape[0], b.shape[1], group, a.device)
-    return ctx(a, b, out)
+    (M, N, group) is created on first use and cached (`gemm_rs_close_all` releases them).  `check=True` reads the
+    device status word after the call (one host synchronisation) and raises on a device-side timeout."""
+    ctx = _rs_context("bf16", a.shape[0], b.shape[1], group, a.device)
+    res = ctx(a, b, out)
+    if check:
+        ctx.check()
+    return res
+
+
+def gemm_rs_fp8(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tensor, b_scale: torch.Tensor, group=None, *,
+                out: Optional[torch.Tensor] = None, check: bool = False) -> torch.Tensor:
+    """Block-scaled FP8 form of `gemm_rs`: rank r passes A_r [M, K/tp] e4m3 with fp32 scales per 1 x 128 block
+    ([M, (K/tp)/128]) and B_r [K/tp, N] e4m3 with fp32 scales per 128 x 128 block, and gets its rows of the sum of
+    the dequantised products as bf16.  Workspaces are cached per (M, N, group), apart from those of `gemm_rs`."""
+    ctx = _rs_context("fp8", a.shape[0], b.shape[1], group, a.device)
+    res = ctx.fp8(a, a_scale, b, b_scale, out)
+    if check:
+        ctx.check()
+    return res

@@ -112,12 +112,21 @@ class SymmetricBuffer:
     def local_ptr(self) -> int:
         return self.ptrs[self.rank]
 
-    def close(self):
+    def close_peers(self):
+        """Drops this process's mappings of the peers' buffers (the owners still hold the memory).  Callers put a
+        group barrier before this (no kernel of any rank touches the buffers any more) and another one between
+        this and `close` (no peer still maps the memory that is about to be freed)."""
         if self.provider == "cuda_ipc":
             from . import _lib
             lib = _lib.load()
             for p in self._opened:
                 lib.ftb_ipc_close(C.c_void_p(p))
-            if self._owned is not None:
-                lib.ftb_ipc_free(C.c_void_p(self._owned))
-        self._opened, self._owned, self._keep = [], None, None
+        self._opened = []
+
+    def close(self):
+        """Releases this rank's own buffer (and, if `close_peers` was not called, the peers' mappings first)."""
+        self.close_peers()
+        if self.provider == "cuda_ipc" and self._owned is not None:
+            from . import _lib
+            _lib.load().ftb_ipc_free(C.c_void_p(self._owned))
+        self._owned, self._keep = None, None

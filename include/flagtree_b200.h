@@ -31,7 +31,7 @@ enum {
   FTB_ERR_INVALID = 1,     /* bad argument: shape, stride, alignment, null pointer           */
   FTB_ERR_CUDA = 2,        /* a CUDA runtime call failed (see ftb_last_error_string)          */
   FTB_ERR_TIMEOUT = 3,     /* a bounded device-side wait ran out                              */
-  FTB_ERR_BAD_INDEX = 4,   /* an index outside [0,S_kv) other than the -1 padding was seen    */
+  FTB_ERR_BAD_INDEX = 4,   /* an index other than the -1 padding that names no row (never read) */
   FTB_ERR_UNSUPPORTED = 5
 };
 
@@ -65,12 +65,12 @@ typedef struct ftb_sparse_mla_args {
   int64_t lse_stride_token;
   float sm_scale;
   int32_t lse_base2;        /* 0: lse = log sum exp(s);  1: log2 sum 2^(s*log2 e)            */
-  int32_t algo_id;          /* 0 = default; 1 = one CTA per (token, output half); 2 = CTA pair,
-                               one shared MMA; 3 = CTA pair, scores / values split;
-                               4 = as 3 with Q in tensor memory and TMA row gathers;
-                               5 = as 4, persistent pairs that walk through the tokens;
-                               6 = paged FP8 form only: dequantise the selected rows, then 5;
-                               7 = as 5 with tiles of 64 rows in rings two tiles deep       */
+  int32_t algo_id;          /* 0 = default; 1 = one CTA per (token, output half); 5 = persistent
+                               role-split CTA pairs that walk through the tokens (scores in one
+                               CTA, values in the other); 6 = paged FP8 form only: dequantise the
+                               selected rows, then the persistent kernel; 7 = as 5 with tiles of 64
+                               rows in rings two tiles deep; 8 = as 5 with every ring slot refilled
+                               by all gather warps together, in the order of use (2-4: retired)  */
   int32_t* status;          /* optional device int32: kernels OR-in a non-zero FTB_ERR_* code */
   /* Paged FP8 form (kv_is_fp8 != 0): physical row = block_table[seq, p / page] * page + p % page,
    * the rule of test_accuracy_musa_vllm_mla.py:278-283.  Query token t belongs to sequence
@@ -81,7 +81,8 @@ typedef struct ftb_sparse_mla_args {
   const int32_t* context_lens;  /* int32 [n_seq]                                              */
   int32_t page_size, q_per_seq;
   int64_t block_table_stride;
-  /* Optional debug tap: fp32 [s_q, 128, topk_padded_to_64] raw (unscaled) scores. NULL = off. */
+  /* Diagnostic tap of the library's own tests, not part of the stable interface: fp32
+   * [s_q, 128, topk_padded_to_64] raw (unscaled) scores of the one-CTA kernel.  Pass NULL. */
   float* dbg_scores;
   /* Split of the top-k axis (for few query tokens, e.g. decode): n_splits > 1 makes every split write a
    * partial result to `workspace` (ftb_sparse_mla_workspace_bytes() bytes of device memory, contents
@@ -114,6 +115,58 @@ FTB_API int ftb_sparse_mla_fwd_static_scratch(const ftb_sparse_mla_args* args, v
 FTB_API int64_t ftb_sparse_mla_static_scratch_bytes(void);
 /* sizeof(ftb_sparse_mla_args) as compiled into the library (for bindings to check their mirror). */
 FTB_API int ftb_sizeof_sparse_mla_args(void);
+
+/* Merge of partial sparse-MLA results over disjoint sets of key/value rows: the reference's second launch,
+ *   third_party/mthreads/python/test/wmma/test_accuracy_musa_vllm_mla.py:426-477 (_fwd_kernel_stage2) with its
+ *   launcher :480-510, as an operation of its own.  The parts are outputs of ftb_sparse_mla_fwd (bf16, each
+ *   normalised by its own sum) or fp32 partials, with their log-sum-exps; typical callers shard a long context
+ *   over GPUs (each rank runs the forward on its rows, the parts are gathered, this merges them) or split the
+ *   top-k list themselves.  out = sum_k w_k part_k / sum_k w_k with w_k = exp(lse_k - max lse); the merged
+ *   log-sum-exp, which the reference does not store, is written too.  A part with lse = -inf (no valid row)
+ *   has weight 0; if every part is empty the result is out = 0, lse = -inf. */
+typedef struct ftb_sparse_mla_merge_args {
+  const void* part_out;      /* bf16 or fp32: part k, token t, head a at k*part_stride_part + t*part_stride_token
+                                + a*part_stride_head (elements), 512 contiguous values                        */
+  const float* part_lse;     /* fp32: k*lse_stride_part + t*lse_stride_part_token + a                          */
+  void* out;                 /* bf16 [s_q, h, 512]                                                             */
+  float* lse;                /* fp32 [s_q, h]                                                                  */
+  int32_t s_q, h, n_parts;
+  int32_t part_is_fp32;      /* 0: part_out is bf16, 1: fp32                                                   */
+  int32_t lse_base2;         /* 0: part_lse and lse are natural logs, 1: base 2 (as ftb_sparse_mla_args)       */
+  int64_t part_stride_part, part_stride_token, part_stride_head;
+  int64_t lse_stride_part, lse_stride_part_token;
+  int64_t out_stride_token, out_stride_head, lse_stride_token;
+} ftb_sparse_mla_merge_args;
+FTB_API int ftb_sparse_mla_merge(const ftb_sparse_mla_merge_args* args, void* stream);
+FTB_API int ftb_sizeof_sparse_mla_merge_args(void);
+
+/* ------------------------------------------------------------------------------------------
+ * Write path of the paged FP8 latent cache (the producer of the format the paged forward reads):
+ * new latent rows are quantised to e4m3 with one fp32 scale per page and scattered into their slots.
+ * Analogue of the reference's quantising cache writer
+ *   third_party/hcu/python/test/unit/sglang/decode_attention_int4kv.py:934
+ *   (destindex_copy_quantize_int4kv_init; its reader is the dequantiser at :821), with e4m3 values and a
+ *   per-page scale in place of int4 values and per-group scale / zero point.
+ * slot = page * page_size + position in the page; -1 skips the row; slots of one call must be distinct.
+ * kv_scale[page] == 0 marks an empty page.  A call raises the scale of each page it touches to
+ * max(old, max|new rows| / 448) (at least 1e-12 / 448); where that raises the scale of a page that already
+ * held rows, the page's bytes are requantised, e4m3(decode(byte) * old / new), before the new rows are
+ * written.  `workspace`: ftb_kv_cache_write_workspace_bytes(num_pages) bytes, contents arbitrary.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ftb_kv_cache_write_args {
+  const void* rows;              /* bf16 [n_rows, 576], row_stride elements between rows              */
+  const int32_t* slot_mapping;   /* int32 [n_rows]                                                    */
+  void* kv_cache;                /* e4m3 [num_pages * page_size, 576], contiguous                      */
+  float* kv_scale;               /* fp32 [num_pages]                                                  */
+  int32_t n_rows, num_pages, page_size;
+  int64_t row_stride;
+  void* workspace;
+  int64_t workspace_bytes;
+  int32_t* status;               /* optional: FTB_ERR_BAD_INDEX for a slot past the last page          */
+} ftb_kv_cache_write_args;
+FTB_API int ftb_kv_cache_write_fp8(const ftb_kv_cache_write_args* args, void* stream);
+FTB_API int64_t ftb_kv_cache_write_workspace_bytes(int32_t num_pages);
+FTB_API int ftb_sizeof_kv_cache_write_args(void);
 
 /* ------------------------------------------------------------------------------------------
  * Dense GEMM  C[M,N] = A[M,K] . B[K,N]  (bf16 in, fp32 accumulate, bf16 out; row-major).
@@ -186,6 +239,11 @@ FTB_API int ftb_gemm_rs_ctx_set_multicast(ftb_gemm_rs_ctx* ctx, void* mc_recv_pt
  * of their rows is complete, and one reduce kernel (in-switch reduction or peer loads) finishes the rank's
  * shard.  0 = the fused kernel (default).  The FP8 form always works this way. */
 FTB_API int ftb_gemm_rs_ctx_set_staged(ftb_gemm_rs_ctx* ctx, int staged);
+/* Longest time, in SM clock cycles, that a kernel of this context waits for another rank before it gives up,
+ * sets FTB_ERR_TIMEOUT in the status word and returns (default about one second).  After a timeout the
+ * context is dead: later calls return at once with the status word unchanged; destroy it and create a new one
+ * on every rank. */
+FTB_API int ftb_gemm_rs_ctx_set_wait_limit(ftb_gemm_rs_ctx* ctx, int64_t cycles);
 FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* ctx);
 /* a [m, k_local] bf16, b [k_local, n] bf16, out [m/tp, n] bf16 (this rank's shard). */
 FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* ctx, const void* a, const void* b, void* out, int k_local,

@@ -41,6 +41,16 @@ def gemm_rs_ref(a_ranks: Sequence[torch.Tensor], b_ranks: Sequence[torch.Tensor]
     return list(total.chunk(tp, dim=0))
 
 
+def gemm_rs_rows_ref(a_ranks: Sequence[torch.Tensor], b_ranks: Sequence[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
+    """Rows `rows` (global row numbers) of C = sum_r A_r @ B_r in fp32, rank order: the same definition as
+    `gemm_rs_ref`, for spot checks at sizes where the whole product is too much CPU work."""
+    total = None
+    for a, b in zip(a_ranks, b_ranks):
+        part = torch.matmul(_f32(a[rows]), _f32(b))
+        total = part if total is None else total + part
+    return total
+
+
 def dequant_block_scaled(x_u8: torch.Tensor, scale: torch.Tensor, block_r: int, block_c: int) -> torch.Tensor:
     """e4m3 bytes [R, C] with one fp32 scale per (block_r x block_c) block -> fp32 [R, C]."""
     if x_u8.dtype != torch.uint8:

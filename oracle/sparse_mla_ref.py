@@ -160,3 +160,56 @@ def sparse_mla_flops(indices: torch.Tensor, h: int, s_kv: Optional[int] = None) 
     if s_kv is not None:
         valid = valid & (indices < s_kv)
     return 2 * (D_QK + D_V) * h * int(valid.sum())
+
+
+E4M3_MAX = 448.0
+
+
+def quantize_pages_e4m3_ref(kv_pages_f32: torch.Tensor):
+    """[num_pages, page, d] fp32 -> (e4m3 bytes uint8, per-page scale = amax / 448 fp32, at least 1e-12 / 448):
+    the definition of the paged FP8 cache format (value = e4m3 * scale[page]).  No reference kernel produces
+    this format; the nearest is the int4 writer with per-group scale and zero point,
+    third_party/hcu/python/test/unit/sglang/decode_attention_int4kv.py:934."""
+    x = _as_f32(kv_pages_f32)
+    amax = x.abs().amax(dim=(1, 2)).clamp(min=1e-12)
+    scale = (amax / E4M3_MAX).to(torch.float32)
+    qv = (x / scale[:, None, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn)
+    return qv.view(torch.uint8), scale
+
+
+def kv_cache_write_fp8_ref(rows: torch.Tensor, slot_mapping: torch.Tensor, kv_cache_u8: torch.Tensor,
+                           kv_scale: torch.Tensor, page_size: int = 64):
+    """CPU restatement of the cache write path; returns new (kv_cache_u8, kv_scale), inputs untouched.
+
+    rows [n, d] (bf16 or fp32), slot_mapping [n] int (slot = page * page_size + position, -1 = skip, distinct),
+    kv_cache_u8 [num_pages, page, d] e4m3 bytes, kv_scale [num_pages] fp32 with 0 = empty page.
+    Per touched page: new = max(old, max|new rows of the page| / 448) with the maximum floored at 1e-12; if
+    new > old and old > 0 every byte of the page is requantised as e4m3(decode(byte) * old / new); then the new
+    rows are stored as e4m3(clamp(x / new, +-448)).  All arithmetic in fp32, divisions IEEE, conversion to e4m3
+    round-to-nearest-even."""
+    x = _as_f32(rows)
+    slots = slot_mapping.detach().to("cpu").to(torch.int64)
+    cache = kv_cache_u8.detach().to("cpu").clone()
+    if cache.dtype != torch.uint8:
+        cache = cache.view(torch.uint8)
+    scale = _as_f32(kv_scale).clone()
+    n_pages, page, d = cache.shape
+    assert page == page_size
+    keep = slots >= 0
+    pages = slots[keep] // page_size
+    row_amax = x[keep].abs().amax(dim=1).clamp(min=1e-12)
+    cand = torch.zeros(n_pages, dtype=torch.float32)
+    cand.scatter_reduce_(0, pages, (row_amax / E4M3_MAX).to(torch.float32), reduce="amax", include_self=True)
+    for pg in torch.unique(pages).tolist():
+        old, new = scale[pg].item(), cand[pg].item()
+        if not new > old:
+            continue
+        if old > 0:
+            dec = cache[pg].view(torch.float8_e4m3fn).to(torch.float32)
+            re = ((dec * torch.tensor(old, dtype=torch.float32)) / torch.tensor(new, dtype=torch.float32))
+            cache[pg] = re.clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
+        scale[pg] = new
+    flat = cache.view(n_pages * page, d)
+    qv = (x[keep] / scale[pages][:, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
+    flat[slots[keep]] = qv
+    return cache, scale

@@ -50,9 +50,9 @@ def _load_reference_kernels(ref_root: str):
     src = "import triton\nimport triton.language as tl\n\n"
     for name in ("tanh", "_fwd_grouped_kernel_stage1", "_fwd_kernel_stage2"):
         src += block(name) + "\n\n"
-    work = os.path.join(HERE, "..", "..", "_work")
-    os.makedirs(work, exist_ok=True)
-    mod_path = os.path.join(work, "_ref_kernels_tmp.py")   # scratch, git-ignored, removed below
+    import tempfile
+    work = tempfile.mkdtemp(prefix="ref_kernels_")          # scratch outside the repository, removed below
+    mod_path = os.path.join(work, "_ref_kernels_tmp.py")
     with open(mod_path, "w") as f:
         f.write(src)
     import importlib.util
@@ -161,7 +161,8 @@ def main():
         np.savez_compressed(os.path.join(HERE, "mla_paged16_b3_h16_len73.npz"), **d)
         print("wrote paged", {k: getattr(v, "shape", v) for k, v in d.items()})
     finally:
-        os.remove(tmp)
+        import shutil
+        shutil.rmtree(os.path.dirname(tmp), ignore_errors=True)
 
 
 if __name__ == "__main__":

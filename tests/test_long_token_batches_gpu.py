@@ -6,7 +6,6 @@ indices, out and lse.  Long prefill is the normal case for sparse attention, so 
 test of its own: 4936 tokens (two launches), compared token by token with the one-CTA-per-token kernel (a
 different code path with no notion of token ranges) and, on a sample of tokens from both ranges, with the
 CPU oracle.  Causal top-k with -1 padding, so the first tokens of the batch are short and the rest full.
-The file name sorts last on purpose: a run that stops at the first failure has executed every other test.
 """
 import pytest
 import torch
@@ -24,7 +23,7 @@ DEV = "cuda:0"
 S_Q = 74 * 64 + 200
 
 
-@pytest.mark.parametrize("algo", [0, 7], ids=["default", "persistent_64row"])
+@pytest.mark.parametrize("algo", [0, 7, 8], ids=["default", "persistent_64row", "persistent_ordered_gathers"])
 def test_more_tokens_than_one_launch_takes(algo):
     c = W.mla_cfg2(device=DEV, s_q=S_Q, s_kv=2048, h=64, topk=128)
     out, lse = sparse_mla_fwd(c.q, c.kv, c.indices, c.sm_scale, check=True, algo=algo)

@@ -92,9 +92,35 @@ def _case_reduce_scatter_fp8_convention(rank, world):
     assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
 
 
+def _case_mla_sequence_sharded_kv(rank, world):
+    """A context whose latent rows are sharded over the ranks: each rank runs the forward over its own rows with
+    `shard_indices` (entries outside its range become padding), the (out, lse) parts are all-gathered, and the
+    split merge of the reference's second launch gives the result of the unsharded forward."""
+    from flagtree_b200.ops import shard_indices
+    from oracle.sparse_mla_ref import merge_splits_ref, sparse_mla_fwd_ref
+    c = W.mla_cfg1(s_q=6, h=4, s_kv=64 * world, topk=40)
+    c.indices[1, 10:] = -1
+    c.indices[2] = torch.arange(40, dtype=torch.int32)              # every row of this token lives on rank 0
+    lo, hi = W.shard_bounds(c.kv.shape[0], world, rank)
+    local = shard_indices(c.indices, lo, hi)
+    assert ((local >= 0) == ((c.indices >= lo) & (c.indices < hi))).all() and int(local.max()) < hi - lo
+    out, lse = sparse_mla_fwd_ref(c.q, c.kv[lo:hi], local, c.sm_scale)
+    parts = [None] * world
+    dist.all_gather_object(parts, (out, lse))
+    po = torch.stack([p[0] for p in parts], dim=2)                  # [s_q, h, world, 512]
+    pl = torch.stack([p[1] for p in parts], dim=2)
+    m_out, m_lse = merge_splits_ref(po, pl)
+    full_out, full_lse = sparse_mla_fwd_ref(c.q, c.kv, c.indices, c.sm_scale)
+    assert torch.allclose(m_out, full_out, rtol=1e-5, atol=1e-5)
+    assert torch.allclose(m_lse, full_lse, rtol=1e-5, atol=1e-5)
+    if rank != 0:
+        assert torch.isinf(lse[2]).all() and (out[2] == 0).all()    # an empty part: weight 0 in the merge
+
+
 @pytest.mark.parametrize("fn,port", [("_case_symmetric_exchange", 29611), ("_case_mla_token_sharding", 29612),
                                      ("_case_reduce_scatter_convention", 29613),
-                                     ("_case_reduce_scatter_fp8_convention", 29614)])
+                                     ("_case_reduce_scatter_fp8_convention", 29614),
+                                     ("_case_mla_sequence_sharded_kv", 29615)])
 def test_two_ranks_gloo(fn, port):
     _spawn(fn, 2, port)
 

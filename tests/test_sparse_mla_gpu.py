@@ -33,8 +33,8 @@ def _errors(out, lse, ref_out, ref_lse):
 
 
 # every bf16 kernel behind algo_id: 5 is what algo_id 0 selects
-ALGOS = [1, 2, 3, 4, 5, 7]
-ALGO_IDS = ["single_cta", "cta_pair", "cta_duo", "cta_duo_qtmem", "persistent", "persistent_64row"]
+ALGOS = [1, 5, 7, 8]
+ALGO_IDS = ["single_cta", "persistent", "persistent_64row", "persistent_ordered_gathers"]
 
 
 def _check(q, kv, idx, sm_scale, name="", algo=0):
@@ -127,18 +127,74 @@ def test_causal_prefill_shape_scaled_down(algo):
     _check(c.q, c.kv, c.indices, c.sm_scale, c.name, algo)
 
 
-def test_large_scores_are_stable():
+def _stepped_scores_case(order, n_tiles=5, h=128, s_q=3, seed=3):
+    """Inputs whose scores climb (or fall) from one tile of 128 selected rows to the next by far more than the
+    2^8 that the kernels let the running maximum lag: kv row j = c_j * u + noise with c_j growing along the index
+    list, every q row a positive multiple a_h of u plus noise, so that score(h, j) ~ 12 * a_h * c_j (natural
+    units, sm_scale = 1) and the per-tile maximum of every head with a_h >= 1 grows by >= 17 in the log2 domain
+    per tile.  `order`: "up" = every tile after the first rescales the accumulator, "down" = none does,
+    "mixed" = only the heads with a large a_h do (the others have a_h = 0.01 and stay within the lag).
+    The values stay O(1) so that the absolute output tolerance keeps its meaning."""
+    g = torch.Generator().manual_seed(seed)
+    topk = 128 * n_tiles
+    s_kv = topk + 64
+    u = (torch.randint(0, 2, (576,), generator=g).float() * 2 - 1)
+    c = torch.arange(s_kv, dtype=torch.float32) / 128.0                  # + 1 per tile of 128 rows
+    kv = (0.5 * c[:, None] * u[None, :] + 0.1 * torch.randn(s_kv, 576, generator=g)).bfloat16()
+    a = 1.0 + torch.rand(s_q, h, generator=g)
+    if order == "mixed":
+        a[:, ::2] = 0.01
+    q = (a[:, :, None] * u[None, None, :] / 24.0 + 0.02 * torch.randn(s_q, h, 576, generator=g)).bfloat16()
+    rows = torch.arange(topk, dtype=torch.int32)
+    if order == "down":
+        rows = rows.flip(0)
+    idx = rows[None, :].repeat(s_q, 1).contiguous()
+    idx[1, topk - 100:] = -1                                              # a ragged last tile
+    return q, kv, idx
+
+
+@pytest.mark.parametrize("algo", [0, 5, 7, 8, 1], ids=["default", "persistent", "persistent_64row", "persistent_ordered_gathers", "single_cta"])
+@pytest.mark.parametrize("order", ["up", "down", "mixed"])
+def test_running_maximum_steps_across_tiles(order, algo):
+    """The online softmax (test_accuracy_musa_vllm_mla.py:313-320) rescales its accumulator whenever the row
+    maximum moves.  The persistent kernels move their reference maximum only when it grows by more than 2^8 and
+    rescale the accumulator in tensor memory in a separate role; this drives that path on every tile after the
+    first ("up"), on none ("down"), and on half of the heads of a warp only ("mixed")."""
+    q, kv, idx = _stepped_scores_case(order)
+    # make sure the construction does what it says: per-tile maxima of a rescaling head, log2 domain
+    s = (q[0, 1].float() @ kv[idx[0].clamp(min=0).long()].float().T) * 1.4426950408889634
+    tile_max = s.view(-1, 128).amax(dim=1)
+    steps = tile_max[1:] - tile_max[:-1]
+    assert (steps > 8).all() if order != "down" else (steps < -8).all(), steps
+    _check(q, kv, idx, 1.0, f"stepped_{order}_algo{algo}", algo)
+
+
+def test_large_random_scores_are_stable():
     g = torch.Generator().manual_seed(3)
     # scores with a standard deviation near 100: the softmax is close to one-hot and the running
     # maximum moves by large steps between tiles (kv stays N(0,1) so that the absolute output
     # tolerance keeps its meaning)
     q = (torch.randn(3, 128, 576, generator=g) * 8).bfloat16()
-    kv = torch.randn(256, 576, generator=g).bfloat16()
-    idx = torch.stack([torch.randperm(256, generator=g)[:128] for _ in range(3)]).int()
-    _check(q, kv, idx, 0.5, "large_scores_pair", 2)
-    _check(q, kv, idx, 0.5, "large_scores_duo", 3)
-    _check(q, kv, idx, 0.5, "large_scores_duo_qtmem", 4)
-    _check(q, kv, idx, 0.5, "large_scores_single", 1)
+    kv = torch.randn(700, 576, generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(700, generator=g)[:640] for _ in range(3)]).int()
+    for algo in (0, 7, 8, 1):
+        _check(q, kv, idx, 0.5, f"large_scores_algo{algo}", algo)
+
+
+@pytest.mark.parametrize("algo", [0, 7, 8, 1], ids=["default", "persistent_64row", "persistent_ordered_gathers", "single_cta"])
+def test_base2_lse_convention(algo):
+    """lse_base2: the log-sum-exp in base-2 units of score * log2(e), the convention of the reference's dense
+    attention (python/triton/ops/flash_attention.py:103) = natural-log LSE / ln 2; the output does not change."""
+    c = W.mla_cfg2(s_q=70, s_kv=400, h=128, topk=300)
+    c.indices[5, :] = -1
+    out, lse2 = sparse_mla_fwd(c.q.to(DEV), c.kv.to(DEV), c.indices.to(DEV), c.sm_scale, check=True, algo=algo, lse_base2=True)
+    ref_out, ref_lse = sparse_mla_fwd_ref(c.q, c.kv, c.indices, c.sm_scale)
+    e_out, e_lse = _errors(out, lse2, ref_out, ref_lse / 0.6931471805599453)
+    assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL, (e_out, e_lse)
+    if algo == 1:
+        _, lse_s = sparse_mla_fwd(c.q.to(DEV), c.kv.to(DEV), c.indices.to(DEV), c.sm_scale, check=True, num_splits=3, lse_base2=True)
+        _, e_lse = _errors(out, lse_s, ref_out, ref_lse / 0.6931471805599453)
+        assert e_lse <= LSE_RTOL
 
 
 def test_order_invariance_determinism_and_token_sharding():
@@ -238,6 +294,16 @@ def test_bad_index_is_reported_not_read():
         sparse_mla_fwd(q, kv, idx, 0.1, check=True)
 
 
+def test_negative_index_other_than_padding_is_reported():
+    g = torch.Generator().manual_seed(2)
+    q = torch.randn(2, 16, 576, generator=g).bfloat16().to(DEV)
+    kv = torch.randn(32, 576, generator=g).bfloat16().to(DEV)
+    idx = torch.tensor([[0, 1, -2, 3], [4, -1, 5, 6]], dtype=torch.int32, device=DEV)
+    for algo in (0, 7, 8, 1):
+        with pytest.raises(RuntimeError, match="BAD_INDEX"):
+            sparse_mla_fwd(q, kv, idx, 0.1, check=True, algo=algo)
+
+
 def test_decode_attention_fwd_shim_matches_reference_signature():
     d = np.load(os.path.join(GOLDEN_DIR, "mla_topk_ragged_sq6_h16_topk96.npz"))
     q = torch.from_numpy(d["q"]).to(torch.bfloat16).to(DEV)
@@ -307,3 +373,36 @@ def test_paged_fp8_decode_with_splits():
     for o, l in ((out, lse), (out4, lse4)):
         e_out, e_lse = _errors(o, l, ref_out, ref_lse)
         assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+
+
+def test_paged_two_pass_with_masked_first_entry_over_poisoned_scratch():
+    """The two-pass path gathers row 0 of its compact table for every masked entry (and multiplies it by zero).
+    When the very first entry is itself masked nothing used to write that row: with NaN patterns left in the
+    scratch the whole result turned NaN.  Here entry (token 0, slot 0) is padding, sequence 0 has context length
+    0, and the scratch memory is filled with 0xFF bytes just before the call."""
+    c = W.mla_cfg3(batch=3, n_q=2, h=128, topk=256, len_lo=300, len_hi=900)
+    c.indices[0, 0, 0] = -1
+    c.context_lens[0] = 0
+    args = [t.to(DEV) for t in (c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens, c.indices)]
+    from flagtree_b200 import _lib
+    need = int(_lib.load().ftb_sparse_mla_dequant_workspace_bytes(6, 256))
+    poison = torch.full((need,), 0xFF, dtype=torch.uint8, device=DEV)
+    torch.cuda.synchronize()
+    del poison                                   # the caching allocator hands the same block to the next request
+    out, lse = sparse_mla_fwd_paged(*args, c.sm_scale, page_size=c.page_size, check=True, num_splits=1, two_pass=True)
+    ref_out, ref_lse = sparse_mla_fwd_paged_ref(c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens,
+                                                c.indices, c.sm_scale, page_size=c.page_size)
+    assert torch.isfinite(out.float()).all()
+    e_out, e_lse = _errors(out, lse, ref_out, ref_lse)
+    assert e_out <= OUT_ATOL and e_lse <= LSE_RTOL
+    assert (out[0] == 0).all() and torch.isinf(lse[0]).all()
+
+
+def test_paged_context_longer_than_block_table_is_reported():
+    c = W.mla_cfg3(batch=2, n_q=1, h=16, topk=64, len_lo=100, len_hi=200)
+    c.context_lens[1] = c.block_table.shape[1] * c.page_size + 500       # claims pages the table does not have
+    c.indices[1, 0, 0] = c.block_table.shape[1] * c.page_size + 3
+    args = [t.to(DEV) for t in (c.q, c.kv_cache, c.kv_scale, c.block_table, c.context_lens, c.indices)]
+    for two_pass in (False, True):
+        with pytest.raises(RuntimeError, match="BAD_INDEX"):
+            sparse_mla_fwd_paged(*args, c.sm_scale, page_size=c.page_size, check=True, num_splits=1, two_pass=two_pass)

@@ -5,13 +5,16 @@ CUDA allocator is hooked or forbidden, cannot hand this library a freshly alloca
 split sparse-MLA forward keeps its per-split partials in a fixed 32 MiB array inside the library.  This
 test drives that entry point through the C ABI twice in a row (the array keeps the first call's contents,
 so the second call also proves that stale data does no harm) and compares each result with the regular
-entry point, which gets its workspace from the caller.  The file name sorts last on purpose: a run that
+entry point, which gets its workspace from the caller, and with the CPU oracle, so that the entry point is
+checked on its own and not only against its sibling.  The file name sorts last on purpose: a run that
 stops at the first failure has already executed every other test.
 """
 import ctypes as C
 
 import pytest
 import torch
+
+from oracle.sparse_mla_ref import sparse_mla_fwd_ref   # the checker
 
 pytestmark = pytest.mark.gpu
 
@@ -58,6 +61,11 @@ def test_static_scratch_entry_matches_regular_entry_twice():
         print(f"call {call}: out diff {err:.3e}, lse diff {lerr:.3e}")
         assert err <= 2e-2 and lerr <= 1e-3          # the tolerances of the other sparse-MLA tests
         assert torch.isfinite(out_b.float()).all()
+        ref_out, ref_lse = sparse_mla_fwd_ref(q.cpu(), kv.cpu(), idx.cpu(), 0.05)
+        o_err = (out_b.float().cpu() - ref_out).abs().max().item()
+        l_err = ((lse_b.cpu() - ref_lse).abs() / ref_lse.abs().clamp(min=1.0)).max().item()
+        print(f"call {call}: against the oracle: out {o_err:.3e}, lse {l_err:.3e}")
+        assert o_err <= 2e-2 and l_err <= 1e-3
 
 
 def test_static_scratch_rejects_oversized_problems():
