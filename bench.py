@@ -32,8 +32,8 @@ if ROOT not in sys.path:
 
 METRIC = "sparse_mla_fwd_tflops"
 UNIT = "TFLOP/s"
-KERNEL_OF_ALGO = {0: "sparse_mla_fifo_kernel", 5: "sparse_mla_stream_kernel", 7: "sparse_mla_stream64_kernel",
-                  8: "sparse_mla_fifo_kernel", 1: "sparse_mla_fwd_kernel"}
+KERNEL_OF_ALGO = {0: "sparse_mla_stream_kernel", 5: "sparse_mla_stream_kernel", 7: "sparse_mla_stream64_kernel",
+                  9: "sparse_mla_wide_kernel", 1: "sparse_mla_fwd_kernel"}
 SM_SCALE = 192 ** -0.5
 FLOPS_CFG2 = 2 * (576 + 512) * 128 * 6292480          # sum over tokens of min(t + 1, 2048) valid entries
 
@@ -387,7 +387,7 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=4096, help="query tokens of the cpu_baseline sample")
     ap.add_argument("--s-q", type=int, default=4096, help="query tokens per rank (default = full cfg2)")
     ap.add_argument("--algo", type=int, default=0, help="algo_id of the sparse-MLA kernel (0 = the library's default)")
-    ap.add_argument("--rs-protocol", default="auto", choices=["auto", "push", "pull", "staged"])
+    ap.add_argument("--rs-protocol", default="auto", choices=["auto", "push", "pull", "staged", "copy"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM + reduce-scatter sections (cfg4, cfg5)")

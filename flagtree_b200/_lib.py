@@ -120,6 +120,7 @@ def load() -> C.CDLL:
             lib.ftb_gemm_rs_ctx_set_multicast.argtypes = [C.c_void_p, C.c_void_p]
             lib.ftb_gemm_rs_ctx_set_staged.argtypes = [C.c_void_p, C.c_int]
             lib.ftb_gemm_rs_ctx_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
+            lib.ftb_gemm_rs_ctx_set_copy_engine.argtypes = [C.c_void_p, C.c_int]
             lib.ftb_gemm_rs.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
                                         C.c_int64, C.c_void_p, C.c_void_p]
             lib.ftb_gemm_rs_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,

@@ -68,6 +68,11 @@ struct Params {
   const __nv_bfloat16* mc_part;      // multicast address of the ranks' partial buffers [m, n] (NULL = push mode)
   unsigned int* blk_counter;         // per 128-row block: epilogue-warp arrivals, monotonic over calls
   long long wait_limit;              // cycles after which a wait for another rank gives up (status = timeout)
+  // copy-engine exchange: every tile is stored into the local partial (c / ldc); when the last tile of a row
+  // shard has been stored its word in ce_ready takes the call number, which a stream memory operation waits for
+  unsigned int* ce_ready;            // [tp] (NULL = another protocol)
+  unsigned int* ce_cnt;              // [tp] epilogue-warp arrivals per row shard, monotonic over calls
+  unsigned int ce_target;            // value ce_cnt[d] reaches in this call
 };
 
 
@@ -423,7 +428,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       tile_coords<NCTA, PULL>(p, t, cta, m_blk, n_blk, dst);
       const uint32_t acc = local & 1u;
       const int row = m_blk * BM + lg * 32 + lane;
-      const bool remote = !PULL && p.tp > 1 && dst != p.rank;
+      const bool ce = !PULL && p.ce_ready != nullptr;
+      const bool remote = !PULL && !ce && p.tp > 1 && dst != p.rank;
       if constexpr (PULL) {
         // Before overwriting a row block of the partial buffer make sure its owner has fetched the
         // previous call's sum (the owner's done[] word in this rank's flag buffer).
@@ -452,7 +458,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
         __syncwarp();
-      } else if (!PULL && p.tp > 1) {
+      } else if (!PULL && !ce && p.tp > 1) {
         // Own rows: every other rank's partial tile must have landed in this rank's receive slots.
         if (lane == 0) {
           // Never enter this wait while holding back a release of our own (peers wait for it too).
@@ -568,7 +574,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           pending_flag = p.flags[dst] + p.rank * p.blocks_per_shard + blk;
         }
         __syncwarp();
-      } else if (!PULL && p.tp > 1) {
+      } else if (!PULL && !ce && p.tp > 1) {
         const int rl = row - dst * p.shard_rows;
         __nv_bfloat16* orow = p.out + static_cast<long long>(rl) * p.ldo + n_blk * BN;
         const long long slot = static_cast<long long>(p.shard_rows) * p.n;
@@ -611,8 +617,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
         tc_fence_before();
-        __syncwarp();
-        if (lane == 0) release_acc(acc);
+        __syncwarp();                  // orders the 32 lanes' stores before lane 0's fence below
+        if (lane == 0) {
+          release_acc(acc);
+          if (ce) {
+            // count the tile for its row shard; the last warp of the shard on this rank publishes "shard complete"
+            __threadfence_system();
+            const unsigned int cnt = atomicAdd(p.ce_cnt + dst, 1u) + 1u;
+            if (cnt == p.ce_target) st_release_sys(p.ce_ready + dst, p.epoch);
+          }
+        }
       }
     }
     if (lane == 0) {
@@ -680,7 +694,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     else tmem_dealloc_pair(tmem, 512);
   }
   if (tid == 0 && p.status != nullptr && bars->abort_flag) atomicCAS(p.status, 0, FTB_ERR_TIMEOUT);
-  if (tid == 0 && p.tp > 1) {
+  if (tid == 0 && p.tp > 1 && p.ce_ready == nullptr) {
     // The last CTA to finish tells every peer that this rank's receive slots may be overwritten.
     __threadfence();
     const unsigned int prev = atomicAdd(p.counter, 1u);
@@ -697,6 +711,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
 // ------------------------------------------------------------------------------------- host side
 using namespace ftb;
+
+// Stream memory operations (driver entry points, looked up through the runtime like cuTensorMapEncodeTiled).
+typedef CUresult (*StreamValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+static StreamValue32Fn get_stream_memop(const char* name) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+    return reinterpret_cast<StreamValue32Fn>(p);
+  return nullptr;
+}
 
 template <int NCTA, bool PULL>
 static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const gemm::Params& p, int sms, cudaStream_t st) {
@@ -792,6 +816,13 @@ struct ftb_gemm_rs_ctx {
   int form;                      // 0 = not used yet, 1 = fused bf16 calls, 2 = staged calls (bf16 or FP8): the flag words differ
   int staged;                    // bf16 calls: 0 = fused kernel (push or pull), 1 = staged (GEMM per shard group + one reduce)
   long long wait_limit;          // cycles a device-side wait for another rank may last
+  // copy-engine exchange
+  int copy_engine;               // bf16 calls: the exchange runs on the copy engines beside the GEMM
+  void* part;                    // this rank's partial product [m, n] bf16 (local memory)
+  unsigned int* d_ready;         // [tp] "shard d of the partial is complete" (call number)
+  unsigned int* d_shard_cnt;     // [tp]
+  cudaStream_t comm;             // stream of the copies
+  cudaEvent_t ev_fork, ev_join;
 };
 
 extern "C" FTB_API int ftb_gemm_rs_workspace_bytes(int m, int n, int tp, int64_t* recv_bytes, int64_t* flag_bytes) {
@@ -820,6 +851,8 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
   c->form = 0;
   c->staged = 0;
   c->wait_limit = kWaitLimitCycles;
+  c->copy_engine = 0;
+  c->part = nullptr; c->d_ready = nullptr; c->d_shard_cnt = nullptr; c->comm = nullptr; c->ev_fork = nullptr; c->ev_join = nullptr;
   for (int i = 0; i < tp; ++i) {
     if (!recv_ptrs[i] || !flag_ptrs[i]) { delete c; set_last_error("ftb_gemm_rs_ctx_create: null peer pointer"); return FTB_ERR_INVALID; }
     c->recv[i] = recv_ptrs[i];
@@ -860,6 +893,12 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* c) {
   if (!c) return FTB_OK;
   cudaFree(c->d_counter);
   cudaFree(c->d_blk_counter);
+  cudaFree(c->part);
+  cudaFree(c->d_ready);
+  cudaFree(c->d_shard_cnt);
+  if (c->comm) cudaStreamDestroy(c->comm);
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
   delete c;
   return FTB_OK;
 }
@@ -1040,6 +1079,85 @@ static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int
   return check_cuda(cudaGetLastError(), "rs reduce launch");
 }
 
+// Copy-engine exchange.  One persistent GEMM launch in the push protocol's tile order (the other ranks' row shards
+// first, rotated by rank, the own shard last) stores every tile into this rank's local partial [m, n] and, when
+// the last tile of a shard is stored, publishes the call number in ready[shard].  A second stream waits for that
+// word with a stream memory operation, makes sure the owner has finished reading the previous call's partial (a
+// bounded one-thread kernel: that wait is on another GPU), copies the 2 * n * m / tp bytes of the shard into the
+// owner's receive slot with an ordinary device-to-device copy, which the copy engines carry out, and raises the
+// owner's flag.  No SM moves exchange data, so the GEMM keeps its operand loads to itself.  After the GEMM the
+// main stream sets every ready word itself (the waits of the second stream end whatever became of the GEMM),
+// and the reduce kernel waits for the peers' flags and sums the tp partials of the own shard from local memory.
+static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b, void* out, int k_local, int64_t lda,
+                               int64_t ldb, int64_t ldo, int32_t* status, cudaStream_t st) {
+  using namespace ftb;
+  if (c->form == 1) { set_last_error("ftb_gemm_rs: this context has served fused calls"); return FTB_ERR_INVALID; }
+  static StreamValue32Fn wait32 = get_stream_memop("cuStreamWaitValue32");
+  static StreamValue32Fn write32 = get_stream_memop("cuStreamWriteValue32");
+  if (!wait32 || !write32) { set_last_error("ftb_gemm_rs: stream memory operations are not available"); return FTB_ERR_UNSUPPORTED; }
+  c->form = 2;
+  c->epoch += 1;
+  const unsigned int epoch = c->epoch;
+  const int tp = c->tp, rank = c->rank;
+  const long long slot = static_cast<long long>(c->shard_rows) * c->n;       // elements of one row shard
+  __nv_bfloat16* part = reinterpret_cast<__nv_bfloat16*>(c->part);
+  cudaError_t e = cudaEventRecord(c->ev_fork, st);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm, c->ev_fork, 0);
+  if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine fork");
+  // ---- GEMM into the local partial
+  gemm::Params p;
+  memset(&p, 0, sizeof(p));
+  p.tp = tp; p.rank = rank; p.shard_rows = c->shard_rows; p.blocks_per_shard = c->blocks_per_shard;
+  p.epoch = epoch;
+  p.c = part; p.ldc = c->n;
+  p.status = status;
+  p.wait_limit = c->wait_limit;
+  p.ce_ready = c->d_ready;
+  p.ce_cnt = c->d_shard_cnt;
+  const int n_blocks = (c->n + gemm::BN - 1) / gemm::BN;
+  p.ce_target = epoch * static_cast<unsigned int>(c->blocks_per_shard) * static_cast<unsigned int>(n_blocks) * 4u;
+  int rc = launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
+  if (rc != FTB_OK) return rc;
+  // ---- exchange on the second stream, destination after destination in the order in which the shards complete
+  gemm::RsFp8Ptrs q;
+  memset(&q, 0, sizeof(q));
+  for (int i = 0; i < tp; ++i) {
+    q.flags[i] = c->flags[i];
+    // the reduce kernel addresses source i as base + (rank * shard_rows + r) * n: the peers' shards sit in this
+    // rank's receive slots, its own in the local partial
+    const __nv_bfloat16* base = (i == rank) ? part : reinterpret_cast<const __nv_bfloat16*>(c->recv[rank]) + (i - rank) * slot;
+    q.recv[i] = base;
+  }
+  for (int s = 1; s < tp; ++s) {
+    const int d = (rank + s) % tp;
+    CUresult r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_ready + d), epoch, CU_STREAM_WAIT_VALUE_GEQ);
+    if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWaitValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
+    // rank d has read the partial of the call before (its word [tp + d] in this rank's flags)
+    gemm::rs_fp8_wait_kernel<<<1, 32, 0, c->comm>>>(c->flags[rank], tp + d, 1, epoch - 1u, status, c->wait_limit);
+    e = cudaMemcpyAsync(reinterpret_cast<__nv_bfloat16*>(c->recv[d]) + rank * slot, part + d * slot,
+                        static_cast<size_t>(slot) * 2, cudaMemcpyDeviceToDevice, c->comm);
+    if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine copy");
+    gemm::rs_fp8_publish_kernel<<<1, 32, 0, c->comm>>>(q, d, 1, rank, epoch, status);
+  }
+  e = cudaEventRecord(c->ev_join, c->comm);
+  if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine join");
+  // ---- after the GEMM: every ready word has its final value whatever happened, the own flag is up
+  for (int d = 0; d < tp; ++d) {
+    CUresult r = write32(reinterpret_cast<CUstream>(st), reinterpret_cast<CUdeviceptr>(c->d_ready + d), epoch, CU_STREAM_WRITE_VALUE_DEFAULT);
+    if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWriteValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
+  }
+  gemm::rs_fp8_publish_kernel<<<1, 32, 0, st>>>(q, rank, 1, rank, epoch, status);
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  gemm::rs_fp8_reduce_kernel<<<sms * 2, 256, 0, st>>>(q, nullptr, reinterpret_cast<__nv_bfloat16*>(out), ldo, c->shard_rows, c->n, rank,
+                                                      tp, epoch, c->d_counter, status, c->wait_limit);
+  rc = check_cuda(cudaGetLastError(), "rs reduce launch");
+  if (rc != FTB_OK) return rc;
+  // the next call's GEMM overwrites the partial: not before this call's copies have read it
+  return check_cuda(cudaStreamWaitEvent(st, c->ev_join, 0), "gemm_rs copy-engine join wait");
+}
+
 extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b, void* out, int k_local,
                                    int64_t lda, int64_t ldb, int64_t ldo, int32_t* status, void* stream) {
   if (!c || !a || !b || !out) { set_last_error("ftb_gemm_rs: null pointer"); return FTB_ERR_INVALID; }
@@ -1047,6 +1165,7 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
   // a rejected call must leave the call counter alone: the peers' flag targets are derived from it
   const int ok = gemm_operands_ok(a, b, c->m, c->n, k_local, lda, ldb);
   if (ok != FTB_OK) return ok;
+  if (c->copy_engine) return copy_engine_gemm_rs(c, a, b, out, k_local, lda, ldb, ldo, status, reinterpret_cast<cudaStream_t>(stream));
   if (c->staged) {
     if (c->form == 1) { set_last_error("ftb_gemm_rs: this context has served fused calls"); return FTB_ERR_INVALID; }
     c->form = 2;
@@ -1116,6 +1235,26 @@ extern "C" FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* c, const void* a, const 
     return ftb_gemm_fp8_blockscaled(&g, stream);
   };
   return staged_gemm_rs(c, rows, out, ldo, status, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// bf16 calls of this context exchange their partials on the copy engines (1) or inside the GEMM kernel (0).  Must be
+// chosen before the first call.  Allocates the local partial [m, n] and the second stream.
+extern "C" FTB_API int ftb_gemm_rs_ctx_set_copy_engine(ftb_gemm_rs_ctx* c, int on) {
+  if (!c) { set_last_error("ftb_gemm_rs_ctx_set_copy_engine: null context"); return FTB_ERR_INVALID; }
+  if (c->epoch != 0) { set_last_error("ftb_gemm_rs_ctx_set_copy_engine: must be called before the first call"); return FTB_ERR_INVALID; }
+  if (on && c->part == nullptr) {
+    cudaError_t e = cudaMalloc(&c->part, static_cast<size_t>(c->m) * c->n * 2);
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_ready, sizeof(unsigned int) * gemm::MAX_TP);
+    if (e == cudaSuccess) e = cudaMemset(c->d_ready, 0, sizeof(unsigned int) * gemm::MAX_TP);
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_shard_cnt, sizeof(unsigned int) * gemm::MAX_TP);
+    if (e == cudaSuccess) e = cudaMemset(c->d_shard_cnt, 0, sizeof(unsigned int) * gemm::MAX_TP);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->comm, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming);
+    if (e != cudaSuccess) return check_cuda(e, "ftb_gemm_rs_ctx_set_copy_engine");
+  }
+  c->copy_engine = on ? 1 : 0;
+  return FTB_OK;
 }
 
 // bf16 calls of this context use the staged protocol (1) or the fused kernel (0, the default).  Must be chosen

@@ -582,7 +582,7 @@ void set_last_error(const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_stream64(const ftb_sparse_mla_args* a, cudaStream_t st);
-int launch_sparse_mla_fifo(const ftb_sparse_mla_args* a, cudaStream_t st);
+int launch_sparse_mla_wide(const ftb_sparse_mla_args* a, cudaStream_t st);
 }  // namespace ftb
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -618,20 +618,20 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     set_last_error("ftb_sparse_mla_fwd: kv row stride must be a multiple of 8 elements");
     return FTB_ERR_INVALID;
   }
-  if (a->algo_id < 0 || a->algo_id > 8) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
+  if (a->algo_id < 0 || a->algo_id > 9) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
   if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
   // algo 0 = default; algo 1 = one CTA per (token, output half), which is also the kernel of the FP8 paged
   // form, of the split form and of the diagnostic score tap; algo 5 = persistent role-split CTA pairs (scores
   // in one CTA, values in the other, Q in tensor memory, TMA row gathers); algo 7 = algo 5 with tiles of 64
-  // rows in rings two tiles deep; algo 8 = algo 5 with every ring slot refilled by all gather warps together.
-  if (a->algo_id == 2 || a->algo_id == 3 || a->algo_id == 4) {
-    set_last_error("ftb_sparse_mla_fwd: algo_id %d (an earlier CTA-pair kernel) is no longer part of the library", a->algo_id);
+  // rows in rings two tiles deep; algo 9 = algo 5 with two gather warps per ring slot (28 warps per CTA, registers rebalanced between the roles).
+  if (a->algo_id == 2 || a->algo_id == 3 || a->algo_id == 4 || a->algo_id == 8) {
+    set_last_error("ftb_sparse_mla_fwd: algo_id %d (an earlier kernel) is no longer part of the library", a->algo_id);
     return FTB_ERR_UNSUPPORTED;
   }
   if (!a->kv_is_fp8 && a->dbg_scores == nullptr && a->n_splits <= 1) {
     if (a->algo_id == 5) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 7) return launch_sparse_mla_stream64(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 8) return launch_sparse_mla_fifo(a, reinterpret_cast<cudaStream_t>(stream));
+    if (a->algo_id == 9) return launch_sparse_mla_wide(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 0) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));   // fastest so far
   }
   MlaParams p;

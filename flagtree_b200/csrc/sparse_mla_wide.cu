@@ -1,31 +1,36 @@
-// Top-k sparse MLA forward, persistent role-split CTA pairs (bf16 KV), gathers issued in the order of use.
+// Top-k sparse MLA forward, persistent role-split CTA pairs (bf16 KV), two gather warps per ring slot.
 //
 // One pair of CTAs (a cluster of 2) walks through query tokens pair, pair + pairs, ...  CTA 0 computes
 // S = Q.K^T (Q in tensor memory, K column blocks in a 9-slot ring filled by TMA gather4) and the softmax;
 // P travels to CTA 1 by bulk copies over distributed shared memory; CTA 1 accumulates O += P.V in tensor
 // memory.  Every barrier keeps counting across tokens and the stages overlap across the token boundary:
 //   * Q of the next token passes through the ring slots on its way to TMEM block by block, each block as
-//     soon as the same block of the current token's last tile has been multiplied;
+//     soon as the same block of the current token's last tile has been multiplied (and is asked into L2 a
+//     whole token ahead);
 //   * the epilogue of CTA 1 runs on 16 warps while CTA 0 already computes the first scores of the next
 //     token: the rows leave through the P buffer of the last tile by TMA tile stores.
 //
 // Gathers.  A ring holds exactly one tile, so a slot is refilled while the MMAs of the same tile still
-// run, and what matters is how soon after its release a slot is full again.  One warp gets a gather4 out
-// every 67 cycles or so, lane after lane, while the TMA unit takes one every 12: a warp that fetches a
-// whole slot by itself (32 gathers) needs over 2000 cycles for it, and nine such warps at once interleave
-// so that every slot of the tile is full only at the very end.  Here every slot is refilled by ALL gather
-// warps together, four (K) or eight (V) lanes each, in the order in which the MMAs use the slots: the
-// warps wait for slot c, issue their share of it, and go on to slot c + 1, so that the slot used first is
-// also full first.
+// run, and the time from a slot's release to its being full again is on the critical path.  A warp
+// hands the TMA unit one gather4 every 65 to 70 cycles, lane after lane, plus about 170 cycles per
+// instruction (measured: 2240 cycles for a 32-lane instruction, 1260 for 16 lanes, 770 for 8), while the
+// unit itself takes far more: twelve warps together get one out every 7.4 cycles.  So the refill time
+// of a slot is set by how many warps share it.  Here every K slot (128 rows x 64 columns) belongs to two
+// warps, one per half of the rows, 16 lanes each, and every V slab to sixteen warps with 8 lanes each
+// (two slabs per warp); the kernel runs 28 warps per CTA, with the registers moved from the gather warps
+// to the softmax / correction warps (setmaxnreg).
 //
 // The number of tiles of a token (last non-negative index, rounded up to 128 rows, at least one) is
 // found for 64 tokens at a time by all warps of a CTA, with a CTA barrier on either side.
 //
-// Warps (576 threads per CTA): CTA 0: 0-7 softmax (two threads per head row), 8 MMA issuer, 9-16 K gathers
-// (warp 9 + w owns rows 16w .. 16w + 15 of every tile; 9-12 also move Q to TMEM), 17 Q loads.  CTA 1: 0-3
-// correction, 4 relay, 8 MMA issuer, 9-16 V gathers (warp 9 + w owns 64-column block w), 0-7 and 9-16
-// epilogue.  Every wait is bounded; a wait that runs out sets the abort flag, after which every later wait
-// returns at once and the status word reports a timeout.
+// Warps (896 threads per CTA).  CTA 0: 0-7 softmax (two threads per head row), 8 MMA issuer, 9-26 K
+// gathers (warp 9 + c + 9 hf: block c, rows 64 hf .. 64 hf + 63; warp 9 + c also loads block c of Q, 9-12
+// move Q to TMEM).  CTA 1: 0-3 correction, 4 relay, 8 MMA issuer, 9-24 V gathers (warp 9 + w + 8 hf:
+// 64-column block w, slabs 2 hf and 2 hf + 1), 0-7 and 9-16 epilogue.  Every wait is bounded; a wait that
+// runs out sets the abort flag, after which every later wait returns at once and the status word reports
+// a timeout.
+#include <type_traits>
+
 #include "sm100.cuh"
 #include "tmap.cuh"
 
@@ -34,7 +39,7 @@ namespace ftb {
 void set_last_error(const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 
-namespace mla8 {
+namespace mla9 {
 
 constexpr int kDqk = 576;
 constexpr int kNChunk = 9;
@@ -56,7 +61,7 @@ constexpr int kOff0Misc = kOff0P + 2 * kPBuf;              // 212992
 constexpr int kOff1P = kNV * kVSlab;                       // 131072
 constexpr int kOff1Misc = kOff1P + 2 * kPBuf;              // 196608
 constexpr int kSmemBytes = kOff0Misc + 4096 + 1024;        // the larger of the two + misc + alignment slack
-constexpr int kThreads = 576;
+constexpr int kThreads = 896;
 constexpr int kWarps = kThreads / 32;
 constexpr uint32_t kColQ = 0;                  // TMEM columns of CTA 0: Q (288), then S
 constexpr uint32_t kColS = 320;
@@ -72,7 +77,7 @@ struct Params {
 };
 
 struct Misc0 {   // CTA 0
-  unsigned long long k_full[kNK];   // 8 gather warps, each announcing its 2 KB of the slot
+  unsigned long long k_full[kNK];   // 2 gather warps, each announcing its 8 KB of the slot
   unsigned long long k_free[kNK];   // tcgen05.commit
   unsigned long long s_full;        // tcgen05.commit
   unsigned long long s_free;        // 8 softmax warps
@@ -140,7 +145,7 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
+sparse_mla_wide_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_constant__ CUtensorMap tm_q,
                          const __grid_constant__ CUtensorMap tm_o, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -160,7 +165,7 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
     *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     if (cta == 0) {
       m0->bad_index = 0;
-      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), 8); mbar_init(smem_u32(&m0->k_free[i]), 1); }
+      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), 2); mbar_init(smem_u32(&m0->k_free[i]), 1); }
       mbar_init(smem_u32(&m0->s_full), 1);
       mbar_init(smem_u32(&m0->s_free), 8);
       for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->q_full[i]), 1); mbar_init(smem_u32(&m0->q_copied[i]), 4); }
@@ -207,6 +212,11 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
   const int my_tokens = (p.s_q - pair + n_pairs - 1) / n_pairs;
   uint32_t gt = 0;   // tiles processed before the current token: every role counts the same way
 
+  // The body of the kernel as a function of the warp group it is compiled for (0: warps 0-7, 1: warps 8-19,
+  // 2: warps 20-27): every group runs the same batch loop, but each copy only holds its own roles, so that the
+  // register budget set for the group applies to exactly the code that the group executes.
+  auto run = [&](auto group_tag) {
+  constexpr int GRP = decltype(group_tag)::value;
   for (int batch0 = 0; batch0 < my_tokens; batch0 += kBatch) {
     const int nb = min(kBatch, my_tokens - batch0);
     // ------------------------------------------------------------------ tiles per token of this batch
@@ -227,7 +237,7 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
     if (cta == 0) {
       // ===================================================================== CTA 0: scores
       const uint32_t k_s = base + kOff0K;
-      if (warp < 8) {
+      if constexpr (GRP == 0) {
         // -------------------------------------------------------------- softmax (two threads per head row)
         // thread tid: head row = tid % 128 (TMEM lane), columns 64*(tid/128) .. +63 of the tile
         const int rowi = tid & 127;
@@ -348,7 +358,7 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(fin_r[ti & 1]);
         }
-      } else if (warp == 8) {
+      } else if (GRP == 1 && warp == 8) {
         // -------------------------------------------------------------- Q.K^T issuer
         // Straight-line code per tile (block c always sits in slot c): the descriptors differ in their low
         // word only and every offset is a compile-time constant.  The whole warp runs the loop and waits;
@@ -390,42 +400,39 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
             gt += n_tiles;
           }
         }
-      } else if (warp < 17) {
-        // -------------------------------------------------------------- K gathers (warps 9-16)
-        // Warp 9 + w owns rows 16w .. 16w + 15 of every tile: lanes 0-3 hold four consecutive rows each and
-        // send one gather4 per 64-column block, block after block, each as soon as its slot is free.  All
-        // eight warps work on the same slot at the same time, so a slot is full again a few hundred cycles
-        // after its release, and the slots fill in the order in which the MMAs use them.  Every warp
-        // announces its own 2 KB on the slot's barrier; the arrival for block 0 also publishes the warp's
-        // 16 validity bits of the tile.
-        // Warps 9-12 (TMEM lane quarters 1, 2, 3, 0) also move Q to tensor memory between tokens: block c
-        // of the next token's Q arrives in slot c (q_full[c], asked for by warp 17 as soon as block c of the
-        // last tile has been multiplied), the four warps copy it to the Q columns of block c (q_copied[c]),
-        // after which slot c takes block c of the next token's first tile.  The MMA issuer needs no extra
-        // wait: k_full[c] of that tile cannot complete before q_copied[c].
-        const int w = warp - 9;
-        const bool mover = w < 4;
-        const bool glane = lane < 4;
-        const int r0 = 16 * w + 4 * (lane & 3);          // first tile row of this lane's gather
-        const uint32_t k_dst = k_s + static_cast<uint32_t>(r0) * 128u;
-        const int q_row = (warp & 3) * 32 + lane;
-        const uint32_t tq = tmem_addr(tmem, (warp & 3) * 32, kColQ);
+      } else if (warp < 27) {
+        // -------------------------------------------------------------- K gathers (warps 9-26)
+        // warp 9 + c + 9 hf fetches rows 64 hf .. 64 hf + 63 of 64-column block c of every tile: lane l < 16 owns
+        // tile rows 64 hf + 4l .. + 3 (one gather4).  Each of the two warps of a slot announces its own 8 KB;
+        // the arrivals on slot 0 also publish the warp's 64 validity bits of the tile.
+        // Between tokens the hand-over runs block by block: as soon as block c of the last tile has been
+        // multiplied (k_free[c]), warp 9 + c loads block c of the next token's Q into slot c (q_full[c]);
+        // warps 9-12 (TMEM lane quarters 1, 2, 3, 0) move it to the Q columns of block c in tensor memory
+        // (q_copied[c]), after which slot c takes block c of the next token's first tile.  The MMA issuer
+        // needs no extra wait: k_full[c] of that tile cannot complete before q_copied[c].
+        const int pi = warp - 9;
+        const int c = pi % 9, hf = pi / 9;
+        const bool copier = GRP == 1 && pi < 4;
+        const bool glane = lane < 16;
+        const int r0 = 64 * hf + 4 * (lane & 15);        // first tile row of this lane's gather
+        const uint32_t k_dst = k_s + c * kKSlot + static_cast<uint32_t>(r0) * 128u;
         for (int t = 0; t < nb; ++t) {
           const int ti = batch0 + t;
           const int tok = pair + ti * n_pairs;
           const int n_tiles = nt[t];
           const int32_t* idx_row = p.indices + static_cast<long long>(tok) * p.idx_st;
-          int nxt[4], row[4];
+          int nxt[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) nxt[j] = (glane && r0 + j < p.topk) ? idx_row[r0 + j] : -1;
-          // this lane's four rows of tile i (the indices of tile i + 1 are requested at once)
-          auto resolve = [&](int i) {
+          // one tile: resolve this lane's four rows, then gather them once slot c is free
+          auto issue_tile = [&](int i) {
             const uint32_t G = gt + i;
+            int row[4];
             uint32_t nib = 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const bool ok = nxt[j] >= 0 && nxt[j] < p.s_kv;
-              if (nxt[j] >= p.s_kv || nxt[j] < -1) m0->bad_index = 1;
+              if (c == 0 && (nxt[j] >= p.s_kv || nxt[j] < -1)) m0->bad_index = 1;
               row[j] = ok ? nxt[j] : 0;
               nib |= ok ? (1u << j) : 0u;
             }
@@ -434,25 +441,48 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
               const int jn = (i + 1) * kNT + r0 + j;
               nxt[j] = (glane && i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
             }
-            // 16 validity bits of this warp's rows: half-word w of the tile's 128 bits
-            uint32_t v = glane ? (nib << (lane * 4)) : 0u;
-            v |= __shfl_xor_sync(0xffffffffu, v, 1);
-            v |= __shfl_xor_sync(0xffffffffu, v, 2);
-            if (lane == 0) reinterpret_cast<volatile unsigned short*>(&m0->valid_mask[G & 3][0])[w] = static_cast<unsigned short>(v);
-          };
-          auto gather_block = [&](int c) {
+            if (c == 0) {
+              // 64 validity bits of this half of the tile: word 2 hf + w = rows 64 hf + 32w .. + 31 = lanes 8w .. 8w + 7
+              uint32_t v = glane ? (nib << ((lane & 7) * 4)) : 0u;
+              v |= __shfl_xor_sync(0xffffffffu, v, 1);
+              v |= __shfl_xor_sync(0xffffffffu, v, 2);
+              v |= __shfl_xor_sync(0xffffffffu, v, 4);
+              if (glane && (lane & 7) == 0) m0->valid_mask[G & 3][2 * hf + (lane >> 3)] = v;
+            }
+            // tile 0 follows the Q block that passed through the slot (the caller has seen q_copied[c])
+            if (i > 0) mbar_wait(smem_u32(&m0->k_free[c]), (G - 1) & 1u, abort_flag);
             const uint32_t full = smem_u32(&m0->k_full[c]);
-            if (lane == 0) mbar_arrive_expect_tx(full, 16 * 128);
             __syncwarp();
-            if (glane) tma_gather4(k_dst + c * kKSlot, &tm_kv, full, c * 64, row[0], row[1], row[2], row[3]);
+            if (lane == 0) mbar_arrive_expect_tx(full, kKSlot / 2);
+            __syncwarp();
+            if (glane) tma_gather4(k_dst, &tm_kv, full, c * 64, row[0], row[1], row[2], row[3]);
           };
-          // ---- first tile: slot c is free once the Q block that passed through it is in TMEM
-          resolve(0);
-          if (mover) {
+          // Q block c of this token: slot c and the Q columns of block c are free once block c of the previous
+          // token's last tile has been multiplied; the same block of the next token is asked into L2 right away
+          if (hf == 0) {
+            if (lane == 0) {
+              if (gt >= 1) mbar_wait(smem_u32(&m0->k_free[c]), (gt - 1) & 1u, abort_flag);
+              const uint32_t qf = smem_u32(&m0->q_full[c]);
+              mbar_arrive_expect_tx(qf, static_cast<uint32_t>(p.h * 128));
+              tma_load_3d(base + c * kKSlot, &tm_q, qf, c * 64, 0, tok);
+              if (tok + n_pairs < p.s_q)
+                asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+                             ::"l"(&tm_q), "r"(c * 64), "r"(0), "r"(tok + n_pairs) : "memory");
+            }
+            __syncwarp();
+          }
+          if (!copier) {
+            mbar_wait(smem_u32(&m0->q_copied[c]), ti & 1u, abort_flag);
+            issue_tile(0);
+          } else {
             // shared memory -> TMEM: thread = head row (TMEM lane quarter = warp % 4); a 32-bit TMEM column
-            // holds two consecutive bf16 of the row; head rows >= h are zero.  Between two blocks the warp
-            // sends the gathers of the blocks that all four movers are through with.
-            int pend = 0;
+            // holds two consecutive bf16 of the row; head rows >= h are zero.  The blocks are moved in the
+            // order in which they arrive (every block has been asked for above: a load takes a thousand cycles
+            // or more, so the loads must not wait for one another), and this warp's own first gather goes
+            // out as soon as all four copiers are through with block c.
+            const int qrow = (warp & 3) * 32 + lane;
+            const uint32_t tq = tmem_addr(tmem, (warp & 3) * 32, kColQ);
+            bool tile0_out = false;
 #pragma unroll 1
             for (int cc = 0; cc < kNChunk; ++cc) {
               mbar_wait(smem_u32(&m0->q_full[cc]), ti & 1u, abort_flag);
@@ -460,11 +490,11 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
               uint32_t v[32];
 #pragma unroll
               for (int q = 0; q < 8; ++q) {
-                const uint32_t src = base + cc * kKSlot + q_row * 128 + ((q ^ (q_row & 7)) << 4);
+                const uint32_t src = base + cc * kKSlot + qrow * 128 + ((q ^ (qrow & 7)) << 4);
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                              : "=r"(v[4 * q]), "=r"(v[4 * q + 1]), "=r"(v[4 * q + 2]), "=r"(v[4 * q + 3]) : "r"(src));
               }
-              if (q_row >= p.h) {
+              if (qrow >= p.h) {
 #pragma unroll
                 for (int q = 0; q < 32; ++q) v[q] = 0u;
               }
@@ -474,61 +504,20 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
               fence_proxy_async_smem();   // the slot read above is next written by TMA (async proxy)
               __syncwarp();
               if (lane == 0) mbar_arrive(smem_u32(&m0->q_copied[cc]));
-              while (pend <= cc) {
+              if (!tile0_out && cc > c) {
                 uint32_t ok = 0;
-                if (lane == 0) ok = mbar_try_wait(smem_u32(&m0->q_copied[pend]), ti & 1u) ? 1u : 0u;
+                if (lane == 0) ok = mbar_try_wait(smem_u32(&m0->q_copied[c]), ti & 1u) ? 1u : 0u;
                 ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
-                gather_block(pend);
-                ++pend;
+                if (ok) { issue_tile(0); tile0_out = true; }
               }
             }
-            for (; pend < kNChunk; ++pend) {
-              mbar_wait(smem_u32(&m0->q_copied[pend]), ti & 1u, abort_flag);
-              gather_block(pend);
-            }
-          } else {
-#pragma unroll 1
-            for (int c = 0; c < kNChunk; ++c) {
+            if (!tile0_out) {
               mbar_wait(smem_u32(&m0->q_copied[c]), ti & 1u, abort_flag);
-              gather_block(c);
+              issue_tile(0);
             }
           }
-          // ---- the other tiles: slot c is free once block c of the tile before has been multiplied
-          for (int i = 1; i < n_tiles; ++i) {
-            resolve(i);
-            const uint32_t ph = (gt + i - 1) & 1u;
-#pragma unroll 1
-            for (int c = 0; c < kNChunk; ++c) {
-              mbar_wait(smem_u32(&m0->k_free[c]), ph, abort_flag);
-              gather_block(c);
-            }
-          }
+          for (int i = 1; i < n_tiles; ++i) issue_tile(i);
           gt += n_tiles;
-        }
-      } else {
-        // -------------------------------------------------------------- Q loads (warp 17)
-        // Block c of this token's Q goes into ring slot c as soon as block c of the previous token's last
-        // tile has been multiplied (k_free[c]); the next token's Q is asked into L2 a whole token ahead, so
-        // that the loads at the hand-over do not wait for device memory.
-        if (lane == 0) {
-          for (int t = 0; t < nb; ++t) {
-            const int ti = batch0 + t;
-            const int tok = pair + ti * n_pairs;
-            const int n_tiles = nt[t];
-            for (int c = 0; c < kNChunk; ++c) {
-              if (gt >= 1) mbar_wait(smem_u32(&m0->k_free[c]), (gt - 1) & 1u, abort_flag);
-              const uint32_t qf = smem_u32(&m0->q_full[c]);
-              mbar_arrive_expect_tx(qf, static_cast<uint32_t>(p.h * 128));
-              tma_load_3d(base + c * kKSlot, &tm_q, qf, c * 64, 0, tok);
-            }
-            if (tok + n_pairs < p.s_q) {
-              for (int c = 0; c < kNChunk; ++c)
-                asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
-                             ::"l"(&tm_q), "r"(c * 64), "r"(0), "r"(tok + n_pairs) : "memory");
-            }
-            gt += n_tiles;
-          }
         }
       }
     } else {
@@ -594,7 +583,7 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
           mbar_arrive(smem_u32(&m1->epi_cnt));
         }
       };
-      if (warp < 8) {
+      if constexpr (GRP == 0) {
         const uint32_t p_free_r[2] = {mapa_shared(smem_u32(&m0->p_free[0]), 0), mapa_shared(smem_u32(&m0->p_free[1]), 0)};
         for (int t = 0; t < nb; ++t) {
           const int ti = batch0 + t;
@@ -646,7 +635,7 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
             mbar_arrive_cluster(epi_done_r[ti & 1]);
           }
         }
-      } else if (warp == 8) {
+      } else if (GRP == 1 && warp == 8) {
         // -------------------------------------------------------------- P.V issuer (whole warp, an elected lane issues)
         {
           constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
@@ -697,12 +686,16 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
             gt += n_tiles;
           }
         }
-      } else if (warp >= 9 && warp < 17) {
-        // -------------------------------------------------------------- V producers (warps 9-16)
-        // warp 9+w fetches 64-column block w of the 512 value columns; lane l owns tile rows 4l..4l+3, which
-        // are rows 4(l%8).. of slab l/8 (a slab is 32 rows: two K = 16 steps of P.V).
-        const int w = warp - 9;
-        const int sl = lane >> 3;
+      } else if (warp >= 9 && warp < 25) {
+        // -------------------------------------------------------------- V gathers (warps 9-24)
+        // warp 9 + w + 8 hf fetches 64-column block w of the 512 value columns for slabs 2 hf and 2 hf + 1 of every
+        // tile (a slab is 32 rows: two K = 16 steps of P.V): lane l < 16 owns tile rows 64 hf + 4l .. + 3, which
+        // are rows 4 (l % 8) .. of slab 2 hf + l / 8.  The warp waits for its first slab, eight lanes send their
+        // gathers, then the same for the second: the slabs fill in the order in which P.V reads them.
+        const int pi = warp - 9;
+        const int w = pi & 7, hf = pi >> 3;
+        const bool glane = lane < 16;
+        const int r0 = 64 * hf + 4 * (lane & 15);
         for (int t = 0; t < nb; ++t) {
           const int ti = batch0 + t;
           const int tok = pair + ti * n_pairs;
@@ -710,7 +703,7 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
           const int32_t* idx_row = p.indices + static_cast<long long>(tok) * p.idx_st;
           int nxt[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) nxt[j] = (4 * lane + j < p.topk) ? idx_row[4 * lane + j] : -1;
+          for (int j = 0; j < 4; ++j) nxt[j] = (glane && r0 + j < p.topk) ? idx_row[r0 + j] : -1;
           auto issue_tile = [&](int i) {
             const uint32_t G = gt + i;
             int row[4];
@@ -718,20 +711,19 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
             for (int j = 0; j < 4; ++j) row[j] = (nxt[j] >= 0 && nxt[j] < p.s_kv) ? nxt[j] : 0;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const int jn = (i + 1) * kNT + 4 * lane + j;
-              nxt[j] = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+              const int jn = (i + 1) * kNT + r0 + j;
+              nxt[j] = (glane && i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
             }
-            // slab after slab, in the order in which P.V reads them: the whole warp waits for the slab, the
-            // eight lanes that own its rows send their gathers.  One arrival per slab announces all 64 gathers
-            // of the eight warps (the byte count may run ahead of the announcement: the phase cannot
-            // complete before this arrival).
-#pragma unroll 1
-            for (int s4 = 0; s4 < kNV; ++s4) {
-              if (G >= 1) mbar_wait(smem_u32(&m1->v_free[s4]), (G - 1) & 1u, abort_flag);
-              if (sl == s4) {
-                const uint32_t full = smem_u32(&m1->v_full[s4]);
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2) {
+              const int sl = 2 * hf + s2;
+              if (G >= 1) mbar_wait(smem_u32(&m1->v_free[sl]), (G - 1) & 1u, abort_flag);
+              if (glane && (lane >> 3) == s2) {
+                const uint32_t full = smem_u32(&m1->v_full[sl]);
+                // one arrival per slab announces all 64 gathers of its eight warps (the byte count may run
+                // ahead of the announcement: the phase cannot complete before this arrival)
                 if (w == 0 && (lane & 7) == 0) mbar_arrive_expect_tx(full, kVSlab);
-                tma_gather4(v_s + s4 * kVSlab + w * kVBlock + (lane & 7) * 512, &tm_kv, full, w * 64, row[0], row[1], row[2], row[3]);
+                tma_gather4(v_s + sl * kVSlab + w * kVBlock + (lane & 7) * 512, &tm_kv, full, w * 64, row[0], row[1], row[2], row[3]);
               }
               __syncwarp();
             }
@@ -740,16 +732,28 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
           // gathers run underneath it
           issue_tile(0);
           __syncwarp();
-          if (t > 0) epilogue_duty(ti - 1, gt - 1, tok - n_pairs);
+          if (GRP == 1 && hf == 0 && t > 0) epilogue_duty(ti - 1, gt - 1, tok - n_pairs);
           for (int i = 1; i < n_tiles; ++i) issue_tile(i);
           gt += n_tiles;
         }
         // the last token of the batch: nothing of the next batch is known yet
         __syncwarp();
-        epilogue_duty(batch0 + nb - 1, gt - 1, pair + (batch0 + nb - 1) * n_pairs);
+        if (GRP == 1 && hf == 0) epilogue_duty(batch0 + nb - 1, gt - 1, pair + (batch0 + nb - 1) * n_pairs);
       }
     }
     __syncthreads();   // nt[] is rewritten by the next batch
+  }
+  };
+  // Registers follow the work: the gather warps of the last two warpgroups need few, the softmax and correction /
+  // epilogue warps of the first two many (64 scores per thread live at once).
+  if (warp < 8) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+    run(std::integral_constant<int, 0>{});
+  } else if (warp < 20) {
+    run(std::integral_constant<int, 1>{});
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    run(std::integral_constant<int, 2>{});
   }
 
   tc_fence_before();
@@ -765,17 +769,17 @@ sparse_mla_fifo_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
   }
 }
 
-}  // namespace mla8
+}  // namespace mla9
 
-int launch_sparse_mla_fifo(const ftb_sparse_mla_args* a, cudaStream_t st) {
-  cudaError_t e = cudaFuncSetAttribute(mla8::sparse_mla_fifo_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla8::kSmemBytes);
-  if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla_fifo)");
+int launch_sparse_mla_wide(const ftb_sparse_mla_args* a, cudaStream_t st) {
+  cudaError_t e = cudaFuncSetAttribute(mla9::sparse_mla_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla9::kSmemBytes);
+  if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla_wide)");
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(mla8::kThreads);
-  cfg.dynamicSmemBytes = mla8::kSmemBytes;
+  cfg.blockDim = dim3(mla9::kThreads);
+  cfg.dynamicSmemBytes = mla9::kSmemBytes;
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
@@ -787,7 +791,7 @@ int launch_sparse_mla_fifo(const ftb_sparse_mla_args* a, cudaStream_t st) {
   if (pairs_dev == 0) {
     cfg.gridDim = dim3(2);
     int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, mla8::sparse_mla_fifo_kernel, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&n, mla9::sparse_mla_wide_kernel, &cfg);
     if (e != cudaSuccess || n <= 0) {
       (void)cudaGetLastError();
       int sms = 0;
@@ -800,20 +804,20 @@ int launch_sparse_mla_fifo(const ftb_sparse_mla_args* a, cudaStream_t st) {
   // One launch takes at most kBatch tokens per pair, so that every pair finds its tile counts once and runs
   // through its tokens without a stop; a longer batch of query tokens is a sequence of such launches on the
   // stream (a launch boundary every pairs x kBatch tokens costs next to nothing).
-  const long long cap = static_cast<long long>(pairs_dev) * mla8::kBatch;
+  const long long cap = static_cast<long long>(pairs_dev) * mla9::kBatch;
   // KV: box = 64 columns x 1 row (tile::gather4 fetches four such rows per instruction);
   // Q: boxes of [h rows x 64 columns] of one token; O: boxes of [32 rows x 64 columns] (a store that
   // reaches past row h is clipped)
   const uint32_t box_h = static_cast<uint32_t>(a->h < 128 ? a->h : 128);
   CUtensorMap tm_kv;
-  if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla8::kDqk,
+  if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla9::kDqk,
                     static_cast<uint64_t>(a->kv_stride_row), 1, 64)) {
-    set_last_error("sparse_mla_fifo: cuTensorMapEncodeTiled failed");
+    set_last_error("sparse_mla_wide: cuTensorMapEncodeTiled failed");
     return FTB_ERR_CUDA;
   }
   for (long long t0 = 0; t0 < a->s_q; t0 += cap) {
     const int n_tok = static_cast<int>(a->s_q - t0 < cap ? a->s_q - t0 : cap);
-    mla8::Params p;
+    mla9::Params p;
     p.indices = a->indices + t0 * a->idx_stride_token;
     p.lse = a->lse + t0 * a->lse_stride_token;
     p.s_q = n_tok; p.h = a->h; p.s_kv = a->s_kv; p.topk = a->topk;
@@ -825,19 +829,19 @@ int launch_sparse_mla_fifo(const ftb_sparse_mla_args* a, cudaStream_t st) {
     const void* q0 = static_cast<const __nv_bfloat16*>(a->q) + t0 * a->q_stride_token;
     void* o0 = static_cast<__nv_bfloat16*>(a->out) + t0 * a->out_stride_token;
     CUtensorMap tm_q, tm_o;
-    if (!make_tmap_3d(&tm_q, q0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mla8::kDqk, static_cast<uint64_t>(a->h),
+    if (!make_tmap_3d(&tm_q, q0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mla9::kDqk, static_cast<uint64_t>(a->h),
                       static_cast<uint64_t>(n_tok), static_cast<uint64_t>(a->q_stride_head),
                       static_cast<uint64_t>(a->q_stride_token), 64, box_h) ||
         !make_tmap_3d(&tm_o, o0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 512, static_cast<uint64_t>(a->h),
                       static_cast<uint64_t>(n_tok), static_cast<uint64_t>(a->out_stride_head),
                       static_cast<uint64_t>(a->out_stride_token), 64, box_h < 32 ? box_h : 32)) {
-      set_last_error("sparse_mla_fifo: cuTensorMapEncodeTiled failed");
+      set_last_error("sparse_mla_wide: cuTensorMapEncodeTiled failed");
       return FTB_ERR_CUDA;
     }
     const int pairs = pairs_dev < n_tok ? pairs_dev : n_tok;
     cfg.gridDim = dim3(static_cast<unsigned>(pairs) * 2u);
-    e = cudaLaunchKernelEx(&cfg, mla8::sparse_mla_fifo_kernel, tm_kv, tm_q, tm_o, p);
-    if (e != cudaSuccess) return check_cuda(e, "sparse_mla_fifo launch");
+    e = cudaLaunchKernelEx(&cfg, mla9::sparse_mla_wide_kernel, tm_kv, tm_q, tm_o, p);
+    if (e != cudaSuccess) return check_cuda(e, "sparse_mla_wide launch");
   }
   return FTB_OK;
 }

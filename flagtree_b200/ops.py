@@ -477,9 +477,14 @@ class GemmRsContext:
         # per-rank shape the staged form is the slowest (0.44 ms at tp = 2, 0.48 ms at tp = 8), so "auto"
         # keeps the fused kernel; the FP8 form always runs staged.
         self.staged = protocol == "staged"
+        # "copy" = one GEMM launch into a local partial, the shards sent by device-to-device copies on a second
+        # stream as they complete (copy engines), one reduce kernel
+        if protocol == "copy":
+            _lib.check(lib.ftb_gemm_rs_ctx_set_copy_engine(ctx, 1), "gemm_rs set_copy_engine")
+            self.protocol = "copy"
         have_mc_any = torch.tensor([1 if self.recv.mc_ptr else 0], device=self.device)
         dist.all_reduce(have_mc_any, op=dist.ReduceOp.MIN, group=group)
-        if self.protocol == "pull" or (self.staged and int(have_mc_any.item()) == 1):
+        if protocol != "copy" and (self.protocol == "pull" or (self.staged and int(have_mc_any.item()) == 1)):
             _lib.check(lib.ftb_gemm_rs_ctx_set_multicast(ctx, C.c_void_p(self.recv.mc_ptr)), "gemm_rs set_multicast")
         if self.staged:
             _lib.check(lib.ftb_gemm_rs_ctx_set_staged(ctx, 1), "gemm_rs set_staged")

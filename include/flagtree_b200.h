@@ -69,8 +69,8 @@ typedef struct ftb_sparse_mla_args {
                                role-split CTA pairs that walk through the tokens (scores in one
                                CTA, values in the other); 6 = paged FP8 form only: dequantise the
                                selected rows, then the persistent kernel; 7 = as 5 with tiles of 64
-                               rows in rings two tiles deep; 8 = as 5 with every ring slot refilled
-                               by all gather warps together, in the order of use (2-4: retired)  */
+                               rows in rings two tiles deep; 9 = as 5 with two gather warps per ring
+                               slot and 28 warps per CTA (2-4 and 8: retired)                    */
   int32_t* status;          /* optional device int32: kernels OR-in a non-zero FTB_ERR_* code */
   /* Paged FP8 form (kv_is_fp8 != 0): physical row = block_table[seq, p / page] * page + p % page,
    * the rule of test_accuracy_musa_vllm_mla.py:278-283.  Query token t belongs to sequence
@@ -239,6 +239,12 @@ FTB_API int ftb_gemm_rs_ctx_set_multicast(ftb_gemm_rs_ctx* ctx, void* mc_recv_pt
  * of their rows is complete, and one reduce kernel (in-switch reduction or peer loads) finishes the rank's
  * shard.  0 = the fused kernel (default).  The FP8 form always works this way. */
 FTB_API int ftb_gemm_rs_ctx_set_staged(ftb_gemm_rs_ctx* ctx, int staged);
+/* Copy-engine exchange for the bf16 calls of a context (before its first call; allocates a local partial of
+ * 2 * m * n bytes and a second stream): one GEMM launch stores the partial locally, shard by shard in rotated
+ * order; as each shard completes, a second stream copies it into its owner's receive slot with a device-to-device
+ * copy (carried out by the copy engines, no SM involved) and raises the owner's flag; a reduce kernel sums the
+ * tp partials of the own shard.  The call returns on `stream` as usual; the second stream is joined to it. */
+FTB_API int ftb_gemm_rs_ctx_set_copy_engine(ftb_gemm_rs_ctx* ctx, int on);
 /* Longest time, in SM clock cycles, that a kernel of this context waits for another rank before it gives up,
  * sets FTB_ERR_TIMEOUT in the status word and returns (default about one second).  After a timeout the
  * context is dead: later calls return at once with the status word unchanged; destroy it and create a new one

@@ -21,7 +21,7 @@ def _run(world, provider, protocol):
 
 @pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs >= 2 GPUs")
 @pytest.mark.parametrize("provider,protocol", [("auto", "auto"), ("auto", "pull"), ("auto", "staged"), ("auto", "push"),
-                                               ("cuda_ipc", "push"), ("cuda_ipc", "staged")])
+                                               ("cuda_ipc", "push"), ("cuda_ipc", "staged"), ("auto", "copy"), ("cuda_ipc", "copy")])
 def test_gemm_rs_matches_oracle(provider, protocol):
     """auto/auto = the fused kernel, with the pull protocol (in-switch reduction) from four ranks on when the box
     offers NVSwitch multicast, else push; cuda_ipc/staged = the staged protocol with plain peer loads.  The worker also runs

@@ -59,7 +59,8 @@ def test_sequence_sharded_context_merges_to_the_unsharded_result(n_ranks):
     kv = torch.randn(s_kv, 576, generator=g).bfloat16()
     idx = torch.stack([torch.randperm(s_kv, generator=g)[:topk] for _ in range(s_q)]).int()
     idx[1, 200:] = -1
-    idx[2] = torch.randperm(s_kv // n_ranks, generator=g)[:topk].int()    # every selected row lives on rank 0
+    idx[2] = -1
+    idx[2, :s_kv // n_ranks] = torch.randperm(s_kv // n_ranks, generator=g)[:topk].int()    # every selected row lives on rank 0
     ref_out, ref_lse = sparse_mla_fwd_ref(q, kv, idx, 0.06)
     parts_o, parts_l = [], []
     per = s_kv // n_ranks
