@@ -32,8 +32,8 @@ if ROOT not in sys.path:
 
 METRIC = "sparse_mla_fwd_tflops"
 UNIT = "TFLOP/s"
-KERNEL_OF_ALGO = {0: "sparse_mla_stream_kernel", 5: "sparse_mla_stream_kernel", 7: "sparse_mla_stream64_kernel",
-                  9: "sparse_mla_wide_kernel", 1: "sparse_mla_fwd_kernel"}
+KERNEL_OF_ALGO = {0: "sparse_mla_ring_kernel", 5: "sparse_mla_stream_kernel", 7: "sparse_mla_stream64_kernel",
+                  9: "sparse_mla_wide_kernel", 10: "sparse_mla_ring_kernel", 1: "sparse_mla_fwd_kernel"}
 SM_SCALE = 192 ** -0.5
 FLOPS_CFG2 = 2 * (576 + 512) * 128 * 6292480          # sum over tokens of min(t + 1, 2048) valid entries
 

@@ -583,6 +583,7 @@ int check_cuda(cudaError_t e, const char* what);
 int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_stream64(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_wide(const ftb_sparse_mla_args* a, cudaStream_t st);
+int launch_sparse_mla_ring(const ftb_sparse_mla_args* a, cudaStream_t st);
 }  // namespace ftb
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -618,12 +619,13 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     set_last_error("ftb_sparse_mla_fwd: kv row stride must be a multiple of 8 elements");
     return FTB_ERR_INVALID;
   }
-  if (a->algo_id < 0 || a->algo_id > 9) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
+  if (a->algo_id < 0 || a->algo_id > 10) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
   if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
   // algo 0 = default; algo 1 = one CTA per (token, output half), which is also the kernel of the FP8 paged
   // form, of the split form and of the diagnostic score tap; algo 5 = persistent role-split CTA pairs (scores
   // in one CTA, values in the other, Q in tensor memory, TMA row gathers); algo 7 = algo 5 with tiles of 64
-  // rows in rings two tiles deep; algo 9 = algo 5 with two gather warps per ring slot (28 warps per CTA, registers rebalanced between the roles).
+  // rows in rings two tiles deep; algo 9 = algo 5 with two gather warps per ring slot (28 warps per CTA, registers rebalanced between the
+  // roles); algo 10 = one ring of eleven slots for K and Q, Q moved to tensor memory by tcgen05.cp (the default).
   if (a->algo_id == 2 || a->algo_id == 3 || a->algo_id == 4 || a->algo_id == 8) {
     set_last_error("ftb_sparse_mla_fwd: algo_id %d (an earlier kernel) is no longer part of the library", a->algo_id);
     return FTB_ERR_UNSUPPORTED;
@@ -632,7 +634,8 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     if (a->algo_id == 5) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 7) return launch_sparse_mla_stream64(a, reinterpret_cast<cudaStream_t>(stream));
     if (a->algo_id == 9) return launch_sparse_mla_wide(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 0) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));   // fastest so far
+    if (a->algo_id == 10) return launch_sparse_mla_ring(a, reinterpret_cast<cudaStream_t>(stream));
+    if (a->algo_id == 0) return launch_sparse_mla_ring(a, reinterpret_cast<cudaStream_t>(stream));   // fastest so far
   }
   MlaParams p;
   memset(&p, 0, sizeof(p));
@@ -685,9 +688,9 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
       b.kv_stride_row = kDqk;
       b.indices = idx2;
       b.idx_stride_token = a->topk;
-      b.algo_id = 5;
+      b.algo_id = 10;
       b.workspace = nullptr; b.workspace_bytes = 0; b.n_splits = 0;
-      return launch_sparse_mla_stream(&b, st);
+      return launch_sparse_mla_ring(&b, st);
     }
   }
   if (n_splits > 1) {

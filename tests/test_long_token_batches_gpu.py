@@ -23,7 +23,7 @@ DEV = "cuda:0"
 S_Q = 74 * 64 + 200
 
 
-@pytest.mark.parametrize("algo", [0, 7, 9], ids=["default", "persistent_64row", "persistent_wide_gathers"])
+@pytest.mark.parametrize("algo", [0, 7, 9, 10], ids=["default", "persistent_64row", "persistent_wide_gathers", "persistent_ring"])
 def test_more_tokens_than_one_launch_takes(algo):
     c = W.mla_cfg2(device=DEV, s_q=S_Q, s_kv=2048, h=64, topk=128)
     out, lse = sparse_mla_fwd(c.q, c.kv, c.indices, c.sm_scale, check=True, algo=algo)
