@@ -287,14 +287,18 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
 
         t_nccl = _timed_collective(nccl_path, iters, flush, dist, sync_word, dev)
         # numeric check of the fused result, not timed
+        # the CPU oracle on a few rows of rank 0's shard (global rows [0, m / world)), from the very operands the ranks hold
+        rows = torch.tensor([0, 1, 127, 128, 511, m // world - 1], device=dev)
+        a_rows = [torch.empty(len(rows), k_loc, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        b_all = [torch.empty(k_loc, n, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        dist.all_gather(a_rows, case.a[rows].contiguous())
+        dist.all_gather(b_all, case.b)
         oracle_rows = None
         if rank == 0:
             from oracle.gemm_rs_ref import gemm_rs_rows_ref
-            rows = torch.tensor([0, 1, 127, 128, 511, m // world - 1])      # rank 0 owns global rows [0, m / world)
-            all_r = [W.gemm_cfg4(device="cpu", tp=world, rank=r, m=m, n=n, k_total=k_loc * world) for r in range(world)]
-            want = gemm_rs_rows_ref([c.a for c in all_r], [c.b for c in all_r], rows)
-            del all_r
-            oracle_rows = (rows, want)
+            want = gemm_rs_rows_ref([t.cpu() for t in a_rows], [t.cpu() for t in b_all], torch.arange(len(rows)))
+            oracle_rows = (rows.cpu(), want)
+        del a_rows, b_all
         ctx(case.a, case.b, out)
         torch.cuda.synchronize()
         parity = _parity_vs_fp32_reduce_scatter(out, case.a.float() @ case.b.float(), world, dist, dev, oracle_rows)

@@ -302,7 +302,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   __syncthreads();
   // The status word is read before any CTA of this launch can have written it only if an EARLIER
   // launch failed, so both CTAs of a pair take the same branch here.
-  if (bars->abort_flag) return;
+  if (bars->abort_flag) {
+    // copy-engine exchange: the second stream waits for the ready words whatever became of this launch
+    if (p.ce_ready != nullptr && blockIdx.x == 0 && tid < p.tp) st_release_sys(p.ce_ready + tid, p.epoch);
+    return;
+  }
   if (warp == 1) {
     if constexpr (NCTA == 1) {
       tmem_alloc(smem_u32(&bars->tmem_base), 512);
@@ -415,6 +419,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const uint32_t stg = staging + lg * 8192;        // this warp's two 4 KB staging boxes
     uint32_t local = 0, box_it = 0;
     unsigned int* pending_flag = nullptr;            // lane 0: counter of the last remote tile, not yet released
+    int ce_pending = -1;                             // lane 0, copy-engine exchange: row shard of the tile stored last, not yet counted
     // the accumulator-free barrier the MMA issuer waits on lives in the even CTA
     const uint32_t acc_empty_addr[2] = {
         NCTA == 1 ? smem_u32(&bars->acc_empty[0]) : mapa_shared(smem_u32(&bars->acc_empty[0]), 0),
@@ -594,6 +599,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       } else if (!PULL) {
         mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
         tc_fence_after();
+        if (ce && lane == 0 && ce_pending >= 0) {
+          // Copy-engine exchange: count the tile stored BEFORE this one for its row shard.  Its stores left a
+          // whole tile ago, so the fence that orders them before the count returns at once (a fence right behind
+          // the stores of a tile cost the GEMM a quarter of its time); the copy engine and the stream wait read
+          // through L2, so device scope is enough.  The last count of a shard publishes "shard complete".
+          __threadfence();
+          const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, 1u) + 1u;
+          if (cnt == p.ce_target) st_release_sys(p.ce_ready + ce_pending, p.epoch);
+          ce_pending = -1;
+        }
+        __syncwarp();                  // the tensor-memory loads below are warp-collective
         __nv_bfloat16* orow = p.c + static_cast<long long>(row) * p.ldc + n_blk * BN;
         const bool row_ok = row < p.m;
 #pragma unroll 1
@@ -617,17 +633,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           }
         }
         tc_fence_before();
-        __syncwarp();                  // orders the 32 lanes' stores before lane 0's fence below
+        __syncwarp();                  // orders the 32 lanes' stores before lane 0's fence one tile later
         if (lane == 0) {
           release_acc(acc);
-          if (ce) {
-            // count the tile for its row shard; the last warp of the shard on this rank publishes "shard complete"
-            __threadfence_system();
-            const unsigned int cnt = atomicAdd(p.ce_cnt + dst, 1u) + 1u;
-            if (cnt == p.ce_target) st_release_sys(p.ce_ready + dst, p.epoch);
-          }
+          if (ce) ce_pending = dst;    // counted one tile late, see above
         }
       }
+    }
+    if (lane == 0 && ce_pending >= 0) {
+      __threadfence();
+      const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, 1u) + 1u;
+      if (cnt == p.ce_target) st_release_sys(p.ce_ready + ce_pending, p.epoch);
     }
     if (lane == 0) {
       bulk_wait_all();
@@ -694,14 +710,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     else tmem_dealloc_pair(tmem, 512);
   }
   if (tid == 0 && p.status != nullptr && bars->abort_flag) atomicCAS(p.status, 0, FTB_ERR_TIMEOUT);
-  if (tid == 0 && p.tp > 1 && p.ce_ready == nullptr) {
-    // The last CTA to finish tells every peer that this rank's receive slots may be overwritten.
+  if (tid == 0 && p.tp > 1) {
+    // The last CTA to finish tells every peer that this rank's receive slots may be overwritten; with the
+    // copy-engine exchange it raises this rank's own "partial complete" word for the reduce kernel instead.
     __threadfence();
     const unsigned int prev = atomicAdd(p.counter, 1u);
     if (prev == gridDim.x - 1) {   // every CTA of the launch has arrived
       *p.counter = 0;
-      for (int peer = 0; peer < p.tp; ++peer)
-        st_release_sys(p.flags[peer] + p.tp * p.blocks_per_shard + p.rank, p.epoch);
+      if (p.ce_ready != nullptr) {
+        st_release_sys(p.flags[p.rank] + p.rank, p.epoch);
+      } else {
+        for (int peer = 0; peer < p.tp; ++peer)
+          st_release_sys(p.flags[peer] + p.tp * p.blocks_per_shard + p.rank, p.epoch);
+      }
     }
   }
 }
@@ -821,6 +842,8 @@ struct ftb_gemm_rs_ctx {
   void* part;                    // this rank's partial product [m, n] bf16 (local memory)
   unsigned int* d_ready;         // [tp] "shard d of the partial is complete" (call number)
   unsigned int* d_shard_cnt;     // [tp]
+  unsigned int* d_ce_counter;    // CTA completion counter of the GEMM launches (the reduce kernel has d_counter)
+  unsigned int* d_epoch_word;    // the current call number in device memory: source of the four-byte flag copies
   cudaStream_t comm;             // stream of the copies
   cudaEvent_t ev_fork, ev_join;
 };
@@ -852,7 +875,7 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_create(ftb_gemm_rs_ctx** out, int rank, i
   c->staged = 0;
   c->wait_limit = kWaitLimitCycles;
   c->copy_engine = 0;
-  c->part = nullptr; c->d_ready = nullptr; c->d_shard_cnt = nullptr; c->comm = nullptr; c->ev_fork = nullptr; c->ev_join = nullptr;
+  c->part = nullptr; c->d_ready = nullptr; c->d_shard_cnt = nullptr; c->d_ce_counter = nullptr; c->d_epoch_word = nullptr; c->comm = nullptr; c->ev_fork = nullptr; c->ev_join = nullptr;
   for (int i = 0; i < tp; ++i) {
     if (!recv_ptrs[i] || !flag_ptrs[i]) { delete c; set_last_error("ftb_gemm_rs_ctx_create: null peer pointer"); return FTB_ERR_INVALID; }
     c->recv[i] = recv_ptrs[i];
@@ -896,6 +919,8 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_destroy(ftb_gemm_rs_ctx* c) {
   cudaFree(c->part);
   cudaFree(c->d_ready);
   cudaFree(c->d_shard_cnt);
+  cudaFree(c->d_ce_counter);
+  cudaFree(c->d_epoch_word);
   if (c->comm) cudaStreamDestroy(c->comm);
   if (c->ev_fork) cudaEventDestroy(c->ev_fork);
   if (c->ev_join) cudaEventDestroy(c->ev_join);
@@ -947,7 +972,7 @@ __global__ void rs_fp8_publish_kernel(RsFp8Ptrs q, int d0, int nd, int word, uns
   st_release_sys(q.flags[d] + word, value);
 }
 
-__global__ void __launch_bounds__(256) rs_fp8_reduce_kernel(RsFp8Ptrs q, const __nv_bfloat16* mc_part, __nv_bfloat16* out,
+__global__ void __launch_bounds__(256, 3) rs_fp8_reduce_kernel(RsFp8Ptrs q, const __nv_bfloat16* mc_part, __nv_bfloat16* out,
                                                            long long ldo, int shard_rows, int n, int rank, int tp,
                                                            unsigned int epoch, unsigned int* counter, int* status, long long wait_limit) {
   __shared__ int s_abort;
@@ -970,7 +995,7 @@ __global__ void __launch_bounds__(256) rs_fp8_reduce_kernel(RsFp8Ptrs q, const _
     const long long total = static_cast<long long>(shard_rows) * vec_per_row;
     const long long row0 = static_cast<long long>(rank) * shard_rows;
     const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    constexpr int kU = 8;   // loads in flight per thread: one at a time moved 250 GB/s
+    constexpr int kU = 4;   // loads in flight per thread (one at a time moved 250 GB/s); three CTAs per SM
     for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * kU) {
       uint4 o[kU];
       long long off[kU], dst[kU];
@@ -1030,6 +1055,85 @@ __global__ void __launch_bounds__(256) rs_fp8_reduce_kernel(RsFp8Ptrs q, const _
   }
 }
 
+
+// Reduce kernel of the copy-engine exchange: every source lies in THIS rank's memory (the peers' partials of the
+// own shard in the receive slots, the own partial in the local partial buffer), so this is one pass over
+// TP x shard bytes at device-memory speed.  Waits (bounded) until every peer's flag shows this call, then each
+// thread sums V 16-byte vectors with all TP x V loads in flight before the first add (fixed source order, fp32).
+// The last CTA tells every peer that their partials of this call have been read.
+template <int TP, int V>
+__global__ void __launch_bounds__(256) rs_local_reduce_kernel(RsFp8Ptrs q, __nv_bfloat16* out, long long ldo, int shard_rows, int n,
+                                                             int rank, unsigned int epoch, unsigned int* counter, int* status,
+                                                             long long wait_limit) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
+  __syncthreads();
+  if (threadIdx.x < TP && !s_abort) {
+    const long long t0 = clock64();
+    while (ld_acquire_sys(q.flags[rank] + threadIdx.x) < epoch) {
+      if (clock64() - t0 > wait_limit) {
+        s_abort = 1;
+        if (status != nullptr) atomicCAS(status, 0, FTB_ERR_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  if (!s_abort) {
+    const int vec_per_row = n / 8;
+    const long long total = static_cast<long long>(shard_rows) * vec_per_row;
+    const long long row0 = static_cast<long long>(rank) * shard_rows;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * V) {
+      uint4 v[TP][V];
+      long long dst[V];
+      bool ok[V];
+#pragma unroll
+      for (int u = 0; u < V; ++u) {
+        const long long i = i0 + u * stride;
+        ok[u] = i < total;
+        const long long r = ok[u] ? i / vec_per_row : 0;
+        const int c8 = ok[u] ? static_cast<int>(i - r * vec_per_row) : 0;
+        const long long off = (row0 + r) * n + c8 * 8;
+        dst[u] = r * ldo + c8 * 8;
+#pragma unroll
+        for (int src = 0; src < TP; ++src)
+          v[src][u] = ok[u] ? __ldcs(reinterpret_cast<const uint4*>(q.recv[src] + off)) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < V; ++u) {
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+        for (int src = 0; src < TP; ++src) {
+          const uint32_t w[4] = {v[src][u].x, v[src][u].y, v[src][u].z, v[src][u].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            acc[2 * k] += __uint_as_float(w[k] << 16);
+            acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+          }
+        }
+        if (ok[u]) {
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          __stcs(reinterpret_cast<uint4*>(out + dst[u]), o);
+        }
+      }
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  __shared__ unsigned int s_last;
+  if (threadIdx.x == 0) s_last = (atomicAdd(counter, 1u) == gridDim.x - 1u) ? 1u : 0u;
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x == 0) *counter = 0u;
+    if (threadIdx.x < TP) st_release_sys(q.flags[threadIdx.x] + TP + rank, epoch);
+  }
+}
+
 }  // namespace gemm
 }  // namespace ftb
 
@@ -1073,7 +1177,7 @@ static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  gemm::rs_fp8_reduce_kernel<<<sms * 2, 256, 0, st>>>(q, reinterpret_cast<const __nv_bfloat16*>(c->mc_recv),
+  gemm::rs_fp8_reduce_kernel<<<sms * 3, 256, 0, st>>>(q, reinterpret_cast<const __nv_bfloat16*>(c->mc_recv),
                                                       reinterpret_cast<__nv_bfloat16*>(out), ldo, c->shard_rows, c->n, c->rank,
                                                       c->tp, c->epoch, c->d_counter, status, c->wait_limit);
   return check_cuda(cudaGetLastError(), "rs reduce launch");
@@ -1082,12 +1186,14 @@ static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int
 // Copy-engine exchange.  One persistent GEMM launch in the push protocol's tile order (the other ranks' row shards
 // first, rotated by rank, the own shard last) stores every tile into this rank's local partial [m, n] and, when
 // the last tile of a shard is stored, publishes the call number in ready[shard].  A second stream waits for that
-// word with a stream memory operation, makes sure the owner has finished reading the previous call's partial (a
-// bounded one-thread kernel: that wait is on another GPU), copies the 2 * n * m / tp bytes of the shard into the
-// owner's receive slot with an ordinary device-to-device copy, which the copy engines carry out, and raises the
-// owner's flag.  No SM moves exchange data, so the GEMM keeps its operand loads to itself.  After the GEMM the
-// main stream sets every ready word itself (the waits of the second stream end whatever became of the GEMM),
-// and the reduce kernel waits for the peers' flags and sums the tp partials of the own shard from local memory.
+// word with a stream memory operation, waits the same way until the owner has finished reading the previous call's
+// partial, copies the 2 * n * m / tp bytes of the shard into the owner's receive slot with an ordinary
+// device-to-device copy, which the copy engines carry out, and raises the owner's flag with a four-byte copy of
+// the call number.  No SM moves exchange data, so the GEMM keeps its operand loads to itself, and the second
+// stream needs no SM at all (stream waits have no time limit: a rank that never arrives stalls it).  After the GEMM the
+// kernel's last CTA raises this rank's own flag (a launch that finds the status word set raises every ready word
+// and leaves, so the waits of the second stream end whatever became of the GEMM), and the reduce kernel waits for
+// the peers' flags and sums the tp partials of the own shard from local memory.
 static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b, void* out, int k_local, int64_t lda,
                                int64_t ldb, int64_t ldo, int32_t* status, cudaStream_t st) {
   using namespace ftb;
@@ -1114,6 +1220,8 @@ static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b,
   p.wait_limit = c->wait_limit;
   p.ce_ready = c->d_ready;
   p.ce_cnt = c->d_shard_cnt;
+  p.counter = c->d_ce_counter;
+  for (int i = 0; i < tp; ++i) p.flags[i] = c->flags[i];
   const int n_blocks = (c->n + gemm::BN - 1) / gemm::BN;
   p.ce_target = epoch * static_cast<unsigned int>(c->blocks_per_shard) * static_cast<unsigned int>(n_blocks) * 4u;
   int rc = launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
@@ -1128,30 +1236,37 @@ static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b,
     const __nv_bfloat16* base = (i == rank) ? part : reinterpret_cast<const __nv_bfloat16*>(c->recv[rank]) + (i - rank) * slot;
     q.recv[i] = base;
   }
+  // The second stream runs no kernel: while the reduce kernels of all ranks sit on their SMs waiting for each
+  // other's flags, a kernel here might never be scheduled.  Waits are stream memory operations, the flag is a
+  // four-byte copy of the call number behind the shard's copy.
+  CUresult r = write32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_epoch_word), epoch, CU_STREAM_WRITE_VALUE_DEFAULT);
+  if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWriteValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
   for (int s = 1; s < tp; ++s) {
     const int d = (rank + s) % tp;
-    CUresult r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_ready + d), epoch, CU_STREAM_WAIT_VALUE_GEQ);
-    if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWaitValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
+    r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_ready + d), epoch, CU_STREAM_WAIT_VALUE_GEQ);
     // rank d has read the partial of the call before (its word [tp + d] in this rank's flags)
-    gemm::rs_fp8_wait_kernel<<<1, 32, 0, c->comm>>>(c->flags[rank], tp + d, 1, epoch - 1u, status, c->wait_limit);
+    if (r == CUDA_SUCCESS && epoch > 1u)
+      r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->flags[rank] + tp + d), epoch - 1u, CU_STREAM_WAIT_VALUE_GEQ);
+    if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWaitValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
     e = cudaMemcpyAsync(reinterpret_cast<__nv_bfloat16*>(c->recv[d]) + rank * slot, part + d * slot,
                         static_cast<size_t>(slot) * 2, cudaMemcpyDeviceToDevice, c->comm);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(c->flags[d] + rank, c->d_epoch_word, sizeof(unsigned int), cudaMemcpyDeviceToDevice, c->comm);
     if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine copy");
-    gemm::rs_fp8_publish_kernel<<<1, 32, 0, c->comm>>>(q, d, 1, rank, epoch, status);
   }
   e = cudaEventRecord(c->ev_join, c->comm);
   if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine join");
-  // ---- after the GEMM: every ready word has its final value whatever happened, the own flag is up
-  for (int d = 0; d < tp; ++d) {
-    CUresult r = write32(reinterpret_cast<CUstream>(st), reinterpret_cast<CUdeviceptr>(c->d_ready + d), epoch, CU_STREAM_WRITE_VALUE_DEFAULT);
-    if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWriteValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
-  }
-  gemm::rs_fp8_publish_kernel<<<1, 32, 0, st>>>(q, rank, 1, rank, epoch, status);
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  gemm::rs_fp8_reduce_kernel<<<sms * 2, 256, 0, st>>>(q, nullptr, reinterpret_cast<__nv_bfloat16*>(out), ldo, c->shard_rows, c->n, rank,
-                                                      tp, epoch, c->d_counter, status, c->wait_limit);
+  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+  const unsigned grid = static_cast<unsigned>(sms) * 4u;
+  switch (tp) {
+    case 2: gemm::rs_local_reduce_kernel<2, 4><<<grid, 256, 0, st>>>(q, o, ldo, c->shard_rows, c->n, rank, epoch, c->d_counter, status, c->wait_limit); break;
+    case 4: gemm::rs_local_reduce_kernel<4, 4><<<grid, 256, 0, st>>>(q, o, ldo, c->shard_rows, c->n, rank, epoch, c->d_counter, status, c->wait_limit); break;
+    case 8: gemm::rs_local_reduce_kernel<8, 2><<<grid, 256, 0, st>>>(q, o, ldo, c->shard_rows, c->n, rank, epoch, c->d_counter, status, c->wait_limit); break;
+    default:
+      gemm::rs_fp8_reduce_kernel<<<sms * 3, 256, 0, st>>>(q, nullptr, o, ldo, c->shard_rows, c->n, rank, tp, epoch, c->d_counter, status, c->wait_limit);
+  }
   rc = check_cuda(cudaGetLastError(), "rs reduce launch");
   if (rc != FTB_OK) return rc;
   // the next call's GEMM overwrites the partial: not before this call's copies have read it
@@ -1248,6 +1363,9 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_set_copy_engine(ftb_gemm_rs_ctx* c, int o
     if (e == cudaSuccess) e = cudaMemset(c->d_ready, 0, sizeof(unsigned int) * gemm::MAX_TP);
     if (e == cudaSuccess) e = cudaMalloc(&c->d_shard_cnt, sizeof(unsigned int) * gemm::MAX_TP);
     if (e == cudaSuccess) e = cudaMemset(c->d_shard_cnt, 0, sizeof(unsigned int) * gemm::MAX_TP);
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_epoch_word, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_ce_counter, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(c->d_ce_counter, 0, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->comm, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming);
@@ -1288,3 +1406,4 @@ extern "C" FTB_API int ftb_ipc_open(const uint8_t handle[64], void** ptr) {
 }
 extern "C" FTB_API int ftb_ipc_close(void* ptr) { return check_cuda(cudaIpcCloseMemHandle(ptr), "ftb_ipc_close"); }
 extern "C" FTB_API int ftb_ipc_free(void* ptr) { return check_cuda(cudaFree(ptr), "ftb_ipc_free"); }
+
