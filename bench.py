@@ -32,8 +32,7 @@ if ROOT not in sys.path:
 
 METRIC = "sparse_mla_fwd_tflops"
 UNIT = "TFLOP/s"
-KERNEL_OF_ALGO = {0: "sparse_mla_ring_kernel", 5: "sparse_mla_stream_kernel", 7: "sparse_mla_stream64_kernel",
-                  9: "sparse_mla_wide_kernel", 10: "sparse_mla_ring_kernel", 1: "sparse_mla_fwd_kernel"}
+KERNEL_OF_ALGO = {0: "sparse_mla_ring_kernel", 5: "sparse_mla_ring_kernel", 1: "sparse_mla_fwd_kernel"}
 SM_SCALE = 192 ** -0.5
 FLOPS_CFG2 = 2 * (576 + 512) * 128 * 6292480          # sum over tokens of min(t + 1, 2048) valid entries
 
@@ -147,7 +146,7 @@ def bench_mla_decode_fp8(args, dev, peaks):
     ridge: reported both as TFLOP/s and as GB/s of the bytes that must move."""
     from flagtree_b200 import sparse_mla_fwd_paged
     from flagtree_b200 import workloads as W
-    c = W.mla_cfg3(device=dev)
+    c = W.mla_cfg3(device=dev, batch=args.decode_batch)
     b, n_q, h, _ = c.q.shape
     n_valid = int((c.indices >= 0).sum())
     flops = 2 * (576 + 512) * h * n_valid
@@ -397,6 +396,7 @@ def main():
     ap.add_argument("--no-gemm", action="store_true", help="skip the GEMM + reduce-scatter sections (cfg4, cfg5)")
     ap.add_argument("--no-fp8-sweep", action="store_true", help="skip the cfg5 sweep")
     ap.add_argument("--no-decode", action="store_true", help="skip the paged FP8 decode and cache-write sections (cfg3)")
+    ap.add_argument("--decode-batch", type=int, default=64, help="sequences of the decode section (64 = cfg3; fewer for profiler captures)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))

@@ -580,9 +580,6 @@ __global__ void __launch_bounds__(256) sparse_mla_merge_parts_kernel(const T* __
 namespace ftb {
 void set_last_error(const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
-int launch_sparse_mla_stream(const ftb_sparse_mla_args* a, cudaStream_t st);
-int launch_sparse_mla_stream64(const ftb_sparse_mla_args* a, cudaStream_t st);
-int launch_sparse_mla_wide(const ftb_sparse_mla_args* a, cudaStream_t st);
 int launch_sparse_mla_ring(const ftb_sparse_mla_args* a, cudaStream_t st);
 }  // namespace ftb
 
@@ -619,24 +616,17 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
     set_last_error("ftb_sparse_mla_fwd: kv row stride must be a multiple of 8 elements");
     return FTB_ERR_INVALID;
   }
-  if (a->algo_id < 0 || a->algo_id > 10) { set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d", a->algo_id); return FTB_ERR_INVALID; }
+  // algo 0 = default = 5: persistent role-split CTA pairs (scores in one CTA, values in the other, Q in tensor
+  // memory, one ring for K and Q filled by TMA row gathers); algo 1 = one CTA per (token, output half), which is
+  // also the kernel of the FP8 paged form without a workspace, of the split form and of the diagnostic score tap;
+  // algo 6 = paged FP8 form: dequantise the selected rows, then the persistent kernel.
+  if (a->algo_id != 0 && a->algo_id != 1 && a->algo_id != 5 && a->algo_id != 6) {
+    set_last_error("ftb_sparse_mla_fwd: unknown algo_id %d (0 = default, 1, 5, 6)", a->algo_id);
+    return FTB_ERR_INVALID;
+  }
   if (a->sm_scale <= 0.0f) { set_last_error("ftb_sparse_mla_fwd: sm_scale must be positive"); return FTB_ERR_INVALID; }
-  // algo 0 = default; algo 1 = one CTA per (token, output half), which is also the kernel of the FP8 paged
-  // form, of the split form and of the diagnostic score tap; algo 5 = persistent role-split CTA pairs (scores
-  // in one CTA, values in the other, Q in tensor memory, TMA row gathers); algo 7 = algo 5 with tiles of 64
-  // rows in rings two tiles deep; algo 9 = algo 5 with two gather warps per ring slot (28 warps per CTA, registers rebalanced between the
-  // roles); algo 10 = one ring of eleven slots for K and Q, Q moved to tensor memory by tcgen05.cp (the default).
-  if (a->algo_id == 2 || a->algo_id == 3 || a->algo_id == 4 || a->algo_id == 8) {
-    set_last_error("ftb_sparse_mla_fwd: algo_id %d (an earlier kernel) is no longer part of the library", a->algo_id);
-    return FTB_ERR_UNSUPPORTED;
-  }
-  if (!a->kv_is_fp8 && a->dbg_scores == nullptr && a->n_splits <= 1) {
-    if (a->algo_id == 5) return launch_sparse_mla_stream(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 7) return launch_sparse_mla_stream64(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 9) return launch_sparse_mla_wide(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 10) return launch_sparse_mla_ring(a, reinterpret_cast<cudaStream_t>(stream));
-    if (a->algo_id == 0) return launch_sparse_mla_ring(a, reinterpret_cast<cudaStream_t>(stream));   // fastest so far
-  }
+  if (!a->kv_is_fp8 && a->dbg_scores == nullptr && a->n_splits <= 1 && (a->algo_id == 0 || a->algo_id == 5))
+    return launch_sparse_mla_ring(a, reinterpret_cast<cudaStream_t>(stream));
   MlaParams p;
   memset(&p, 0, sizeof(p));
   p.q = reinterpret_cast<const __nv_bfloat16*>(a->q);
@@ -688,7 +678,7 @@ extern "C" FTB_API int ftb_sparse_mla_fwd(const ftb_sparse_mla_args* a, void* st
       b.kv_stride_row = kDqk;
       b.indices = idx2;
       b.idx_stride_token = a->topk;
-      b.algo_id = 10;
+      b.algo_id = 5;
       b.workspace = nullptr; b.workspace_bytes = 0; b.n_splits = 0;
       return launch_sparse_mla_ring(&b, st);
     }

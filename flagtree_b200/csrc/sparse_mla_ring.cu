@@ -18,6 +18,16 @@
 // the last tile is still being multiplied (and the token after it is asked into L2), and no warp has to
 // carry Q from shared to tensor memory.
 //
+// Gather warps.  A warp hands the TMA unit one gather4 every 65 to 70 cycles, lane after lane (a 32-lane
+// instruction keeps it busy for 2240 cycles, 16 lanes for 1260), and warps that share a scheduler share its
+// dispatch of such operations (about one per 20 cycles per scheduler).  So every K entry belongs to two warps, 16
+// lanes and 64 rows each, eighteen gather warps in all, and they sit on the three schedulers that the MMA
+// issuer is not on (warp ids 9-31 except those that are 0 modulo 4): with four gather warps beside it the
+// issuer needed 420 instead of 265 cycles per block.
+// The kernel runs 32 warps per CTA; registers move from the gather warps to the softmax / correction warps
+// (setmaxnreg), and every group of warps runs its own copy of the batch loop so that its budget applies to its
+// own code only.
+//
 // Softmax: two threads per head row; the running maximum moves only when it grows by more than 2^8, so that
 // the accumulator in CTA 1 is rarely rescaled.  P (bf16) and the rescale factors go to a staging area and
 // from there to CTA 1 with bulk copies that complete on CTA 1's barrier; the arrival that announces them
@@ -26,10 +36,13 @@
 // The number of tiles of a token (last non-negative index, rounded up to 128 rows, at least one) is
 // found for 64 tokens at a time by all warps of a CTA, with a CTA barrier on either side.
 //
-// Warps (576 threads per CTA): CTA 0: 0-7 softmax, 8 MMA issuer, 9-17 ring producers (warp 9 + c: block c of Q
-// and of every tile).  CTA 1: 0-3 correction, 4 relay, 8 MMA issuer, 9-16 V producers, 0-7 and 9-16 epilogue.
+// Warps (1024 threads per CTA): CTA 0: 0-7 softmax, 8 MMA issuer, eighteen ring producers (producer 2c + hf: rows
+// 64 hf .. 64 hf + 63 of block c of every tile; hf = 0 also loads block c of Q).  CTA 1: 0-3 correction, 4 relay,
+// 8 MMA issuer, 9-16 V producers, 0-7 and 9-16 epilogue.
 // Every wait is bounded; a wait that runs out sets the abort flag, after which every later wait returns at
 // once and the status word reports a timeout.
+#include <type_traits>
+
 #include "sm100.cuh"
 #include "tmap.cuh"
 
@@ -38,7 +51,7 @@ namespace ftb {
 void set_last_error(const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 
-namespace mla10 {
+namespace mla_ring {
 
 constexpr int kDqk = 576;
 constexpr int kNChunk = 9;
@@ -60,7 +73,7 @@ constexpr int kOff0Misc = kOff0P + kPBuf;                  // 212992
 constexpr int kOff1P = kNV * kVSlab;                       // 131072
 constexpr int kOff1Misc = kOff1P + 2 * kPBuf;              // 196608
 constexpr int kSmemBytes = kOff0Misc + 4096 + 1024;        // the larger of the two + misc + alignment slack
-constexpr int kThreads = 576;
+constexpr int kThreads = 1024;
 constexpr int kWarps = kThreads / 32;
 constexpr uint32_t kColQ = 0;                  // TMEM columns of CTA 0: Q (288), then S
 constexpr uint32_t kColS = 320;
@@ -76,7 +89,7 @@ struct Params {
 };
 
 struct Misc0 {   // CTA 0
-  unsigned long long k_full[kNK];   // one arrival announcing the bytes of the entry (a gather of 16 KB or a tile load of Q)
+  unsigned long long k_full[kNK];   // two arrivals, one per gather warp of the entry, each announcing its bytes (8 KB of gathers; the tile load of a Q entry counts on the first)
   unsigned long long k_free[kNK];   // tcgen05.commit behind the entry's MMAs or its copy to tensor memory
   unsigned long long s_full;        // tcgen05.commit
   unsigned long long s_free;        // 8 softmax warps
@@ -189,7 +202,7 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
     *abort_flag = (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) ? 1 : 0;
     if (cta == 0) {
       m0->bad_index = 0;
-      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), 1); mbar_init(smem_u32(&m0->k_free[i]), 1); }
+      for (int i = 0; i < kNK; ++i) { mbar_init(smem_u32(&m0->k_full[i]), 2); mbar_init(smem_u32(&m0->k_free[i]), 1); }
       mbar_init(smem_u32(&m0->s_full), 1);
       mbar_init(smem_u32(&m0->s_free), 8);
       for (int i = 0; i < 2; ++i) { mbar_init(smem_u32(&m0->p_free[i]), 1); mbar_init(smem_u32(&m0->epi_done[i]), 1); }
@@ -242,10 +255,18 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
   // tokens of this pair: pair, pair + n_pairs, ...  (the host launches no more pairs than tokens)
   const int my_tokens = (p.s_q - pair + n_pairs - 1) / n_pairs;
   uint32_t gt = 0;   // tiles processed before the current token: every role counts the same way
+  // CTA 0: index of this warp among the eighteen ring producers (-1 = not one): the warps 9-31 whose id is not 0
+  // modulo 4, in order (they share no scheduler with the MMA issuer, warp 8).
+  const int prod = (warp >= 9 && (warp & 3) != 0) ? (warp - 9) - ((warp - 8) >> 2) : -1;
   RingPos pos;       // CTA 0, issuer and producers: position in the stream of ring entries
-  pos.slot = (cta == 0 && warp >= 9) ? static_cast<uint32_t>(warp - 9) : 0u;
+  pos.slot = (cta == 0 && prod >= 0) ? static_cast<uint32_t>(prod >> 1) : 0u;
   pos.use = 0;
 
+  // The body of the kernel as a function of the warp group it is compiled for (0: warps 0-7, 1: warps 8-19,
+  // 2: warps 20-31): every group runs the same batch loop, but each copy only holds its own roles, so that the
+  // register budget set for the group applies to exactly the code that the group executes.
+  auto run = [&](auto group_tag) {
+  constexpr int GRP = decltype(group_tag)::value;
   for (int batch0 = 0; batch0 < my_tokens; batch0 += kBatch) {
     const int nb = min(kBatch, my_tokens - batch0);
     // ------------------------------------------------------------------ tiles per token of this batch
@@ -266,7 +287,7 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
     if (cta == 0) {
       // ===================================================================== CTA 0: scores
       const uint32_t k_s = base + kOff0K;
-      if (warp < 8) {
+      if constexpr (GRP == 0) {
         // -------------------------------------------------------------- softmax (two threads per head row)
         // thread tid: head row = tid % 128 (TMEM lane), columns 64*(tid/128) .. +63 of the tile
         const int rowi = tid & 127;
@@ -391,7 +412,7 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(fin_r[ti & 1]);
         }
-      } else if (warp == 8) {
+      } else if (GRP == 1 && warp == 8) {
         // -------------------------------------------------------------- ring consumer: Q copies and Q.K^T
         // The whole warp runs the loop and waits; an elected lane (always the same one, so that its commits
         // cover its MMAs and copies) issues.  The descriptors differ in their low word only.  Per token: nine Q
@@ -446,14 +467,17 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
             gt += n_tiles;
           }
         }
-      } else {
-        // -------------------------------------------------------------- ring producers (warps 9-17)
-        // warp 9 + c supplies block c of every token's Q (one TMA tile load) and of every tile (lane l owns tile
-        // rows 4l .. 4l + 3: one gather4), in the order of the ring: its entries are c, c + 9, c + 18, ...  A
-        // slot is free once the commit behind the entry that used it last has arrived (k_free); the parity wait
-        // is exact because the entry eleven places back is at most one phase away.  Block c of the token after
-        // this one is asked into L2 when this token's is loaded.
-        const int c = warp - 9;
+      } else if (prod >= 0) {
+        // -------------------------------------------------------------- ring producers
+        // producer 2c + hf supplies rows 64 hf .. 64 hf + 63 of block c of every tile (lane l < 16 owns tile rows
+        // 64 hf + 4l .. + 3: one gather4) and, if hf = 0, block c of every token's Q (one TMA tile load), in the
+        // order of the ring: its entries are c, c + 9, c + 18, ...  A slot is free once the commit behind the
+        // entry that used it last has arrived (k_free); the parity wait is exact because the entry eleven places
+        // back is at most one phase away.  Each of the two warps of an entry arrives on its barrier with its own
+        // byte count.  Block c of the token after this one is asked into L2 when this token's is loaded.
+        const int c = prod >> 1, hf = prod & 1;
+        const bool glane = lane < 16;
+        const int r0 = 64 * hf + 4 * (lane & 15);
         for (int t = 0; t < nb; ++t) {
           const int ti = batch0 + t;
           const int tok = pair + ti * n_pairs;
@@ -461,16 +485,20 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
           const int32_t* idx_row = p.indices + static_cast<long long>(tok) * p.idx_st;
           int nxt[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) nxt[j] = (4 * lane + j < p.topk) ? idx_row[4 * lane + j] : -1;
+          for (int j = 0; j < 4; ++j) nxt[j] = (glane && r0 + j < p.topk) ? idx_row[r0 + j] : -1;
           // ---- the Q entry
           if (pos.use >= 1) mbar_wait(smem_u32(&m0->k_free[pos.slot]), (pos.use - 1) & 1u, abort_flag);
           if (lane == 0) {
             const uint32_t full = smem_u32(&m0->k_full[pos.slot]);
-            mbar_arrive_expect_tx(full, static_cast<uint32_t>(p.h * 128));
-            tma_load_3d(k_s + pos.slot * kKSlot, &tm_q, full, c * 64, 0, tok);
-            if (tok + n_pairs < p.s_q)
-              asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
-                           ::"l"(&tm_q), "r"(c * 64), "r"(0), "r"(tok + n_pairs) : "memory");
+            if (hf == 0) {
+              mbar_arrive_expect_tx(full, static_cast<uint32_t>(p.h * 128));
+              tma_load_3d(k_s + pos.slot * kKSlot, &tm_q, full, c * 64, 0, tok);
+              if (tok + n_pairs < p.s_q)
+                asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+                             ::"l"(&tm_q), "r"(c * 64), "r"(0), "r"(tok + n_pairs) : "memory");
+            } else {
+              mbar_arrive(full);
+            }
           }
           __syncwarp();
           pos.advance(kNChunk);
@@ -488,23 +516,23 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const int jn = (i + 1) * kNT + 4 * lane + j;
-              nxt[j] = (i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
+              const int jn = (i + 1) * kNT + r0 + j;
+              nxt[j] = (glane && i + 1 < n_tiles && jn < p.topk) ? idx_row[jn] : -1;
             }
             if (c == 0) {
-              // 128 validity bits of the tile: word w = rows 32w..32w+31 = lanes 8w..8w+7, four bits each
-              uint32_t v = nib << ((lane & 7) * 4);
+              // 64 validity bits of this half of the tile: word 2 hf + w = rows 64 hf + 32w .. + 31 = lanes 8w .. 8w + 7
+              uint32_t v = glane ? (nib << ((lane & 7) * 4)) : 0u;
               v |= __shfl_xor_sync(0xffffffffu, v, 1);
               v |= __shfl_xor_sync(0xffffffffu, v, 2);
               v |= __shfl_xor_sync(0xffffffffu, v, 4);
-              if ((lane & 7) == 0) m0->valid_mask[G & 3][lane >> 3] = v;
+              if (glane && (lane & 7) == 0) m0->valid_mask[G & 3][2 * hf + (lane >> 3)] = v;
             }
             if (pos.use >= 1) mbar_wait(smem_u32(&m0->k_free[pos.slot]), (pos.use - 1) & 1u, abort_flag);
             const uint32_t full = smem_u32(&m0->k_full[pos.slot]);
             __syncwarp();
-            if (lane == 0) mbar_arrive_expect_tx(full, kKSlot);
+            if (lane == 0) mbar_arrive_expect_tx(full, kKSlot / 2);
             __syncwarp();
-            tma_gather4(k_s + pos.slot * kKSlot + lane * 512, &tm_kv, full, c * 64, row[0], row[1], row[2], row[3]);
+            if (glane) tma_gather4(k_s + pos.slot * kKSlot + r0 * 128, &tm_kv, full, c * 64, row[0], row[1], row[2], row[3]);
             pos.advance(kNChunk);
           }
           gt += n_tiles;
@@ -573,7 +601,7 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
           mbar_arrive(smem_u32(&m1->epi_cnt));
         }
       };
-      if (warp < 8) {
+      if constexpr (GRP == 0) {
         const uint32_t p_free_r[2] = {mapa_shared(smem_u32(&m0->p_free[0]), 0), mapa_shared(smem_u32(&m0->p_free[1]), 0)};
         const uint32_t stage_free_r = mapa_shared(smem_u32(&m0->stage_free), 0);
         for (int t = 0; t < nb; ++t) {
@@ -627,7 +655,7 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
             mbar_arrive_cluster_relaxed(epi_done_r[ti & 1]);
           }
         }
-      } else if (warp == 8) {
+      } else if (GRP == 1 && warp == 8) {
         // -------------------------------------------------------------- P.V issuer (whole warp, an elected lane issues)
         {
           constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, 128, 256, 0, 1);
@@ -724,6 +752,18 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
     }
     __syncthreads();   // nt[] is rewritten by the next batch
   }
+  };
+  // Registers follow the work: the gather warps need few, the softmax and correction / epilogue warps many
+  // (64 scores per thread live at once).
+  if (warp < 8) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 96;");
+    run(std::integral_constant<int, 0>{});
+  } else if (warp < 20) {
+    run(std::integral_constant<int, 1>{});
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    run(std::integral_constant<int, 2>{});
+  }
 
   tc_fence_before();
   __syncthreads();
@@ -738,17 +778,17 @@ sparse_mla_ring_kernel(const __grid_constant__ CUtensorMap tm_kv, const __grid_c
   }
 }
 
-}  // namespace mla10
+}  // namespace mla_ring
 
 int launch_sparse_mla_ring(const ftb_sparse_mla_args* a, cudaStream_t st) {
-  cudaError_t e = cudaFuncSetAttribute(mla10::sparse_mla_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla10::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(mla_ring::sparse_mla_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, mla_ring::kSmemBytes);
   if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(sparse_mla_ring)");
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(mla10::kThreads);
-  cfg.dynamicSmemBytes = mla10::kSmemBytes;
+  cfg.blockDim = dim3(mla_ring::kThreads);
+  cfg.dynamicSmemBytes = mla_ring::kSmemBytes;
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
@@ -760,7 +800,7 @@ int launch_sparse_mla_ring(const ftb_sparse_mla_args* a, cudaStream_t st) {
   if (pairs_dev == 0) {
     cfg.gridDim = dim3(2);
     int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, mla10::sparse_mla_ring_kernel, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&n, mla_ring::sparse_mla_ring_kernel, &cfg);
     if (e != cudaSuccess || n <= 0) {
       (void)cudaGetLastError();
       int sms = 0;
@@ -773,20 +813,20 @@ int launch_sparse_mla_ring(const ftb_sparse_mla_args* a, cudaStream_t st) {
   // One launch takes at most kBatch tokens per pair, so that every pair finds its tile counts once and runs
   // through its tokens without a stop; a longer batch of query tokens is a sequence of such launches on the
   // stream (a launch boundary every pairs x kBatch tokens costs next to nothing).
-  const long long cap = static_cast<long long>(pairs_dev) * mla10::kBatch;
+  const long long cap = static_cast<long long>(pairs_dev) * mla_ring::kBatch;
   // KV: box = 64 columns x 1 row (tile::gather4 fetches four such rows per instruction);
   // Q: boxes of [h rows x 64 columns] of one token; O: boxes of [32 rows x 64 columns] (a store that
   // reaches past row h is clipped)
   const uint32_t box_h = static_cast<uint32_t>(a->h < 128 ? a->h : 128);
   CUtensorMap tm_kv;
-  if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla10::kDqk,
+  if (!make_tmap_2d(&tm_kv, a->kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, static_cast<uint64_t>(a->s_kv), mla_ring::kDqk,
                     static_cast<uint64_t>(a->kv_stride_row), 1, 64)) {
     set_last_error("sparse_mla_ring: cuTensorMapEncodeTiled failed");
     return FTB_ERR_CUDA;
   }
   for (long long t0 = 0; t0 < a->s_q; t0 += cap) {
     const int n_tok = static_cast<int>(a->s_q - t0 < cap ? a->s_q - t0 : cap);
-    mla10::Params p;
+    mla_ring::Params p;
     p.indices = a->indices + t0 * a->idx_stride_token;
     p.lse = a->lse + t0 * a->lse_stride_token;
     p.s_q = n_tok; p.h = a->h; p.s_kv = a->s_kv; p.topk = a->topk;
@@ -798,7 +838,7 @@ int launch_sparse_mla_ring(const ftb_sparse_mla_args* a, cudaStream_t st) {
     const void* q0 = static_cast<const __nv_bfloat16*>(a->q) + t0 * a->q_stride_token;
     void* o0 = static_cast<__nv_bfloat16*>(a->out) + t0 * a->out_stride_token;
     CUtensorMap tm_q, tm_o;
-    if (!make_tmap_3d(&tm_q, q0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mla10::kDqk, static_cast<uint64_t>(a->h),
+    if (!make_tmap_3d(&tm_q, q0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, mla_ring::kDqk, static_cast<uint64_t>(a->h),
                       static_cast<uint64_t>(n_tok), static_cast<uint64_t>(a->q_stride_head),
                       static_cast<uint64_t>(a->q_stride_token), 64, box_h) ||
         !make_tmap_3d(&tm_o, o0, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, 512, static_cast<uint64_t>(a->h),
@@ -809,7 +849,7 @@ int launch_sparse_mla_ring(const ftb_sparse_mla_args* a, cudaStream_t st) {
     }
     const int pairs = pairs_dev < n_tok ? pairs_dev : n_tok;
     cfg.gridDim = dim3(static_cast<unsigned>(pairs) * 2u);
-    e = cudaLaunchKernelEx(&cfg, mla10::sparse_mla_ring_kernel, tm_kv, tm_q, tm_o, p);
+    e = cudaLaunchKernelEx(&cfg, mla_ring::sparse_mla_ring_kernel, tm_kv, tm_q, tm_o, p);
     if (e != cudaSuccess) return check_cuda(e, "sparse_mla_ring launch");
   }
   return FTB_OK;

@@ -1,6 +1,6 @@
 """Query batches longer than one launch of the persistent sparse-MLA kernels walks through.
 
-The persistent kernels give every CTA pair at most 64 tokens per launch (74 pairs on a B200: 4736 tokens);
+The persistent kernel gives every CTA pair at most 64 tokens per launch (74 pairs on a B200: 4736 tokens);
 a longer batch becomes several launches over consecutive token ranges, each with its own offsets into q,
 indices, out and lse.  Long prefill is the normal case for sparse attention, so the range arithmetic gets a
 test of its own: 4936 tokens (two launches), compared token by token with the one-CTA-per-token kernel (a
@@ -23,8 +23,8 @@ DEV = "cuda:0"
 S_Q = 74 * 64 + 200
 
 
-@pytest.mark.parametrize("algo", [0, 7, 9, 10], ids=["default", "persistent_64row", "persistent_wide_gathers", "persistent_ring"])
-def test_more_tokens_than_one_launch_takes(algo):
+def test_more_tokens_than_one_launch_takes():
+    algo = 0
     c = W.mla_cfg2(device=DEV, s_q=S_Q, s_kv=2048, h=64, topk=128)
     out, lse = sparse_mla_fwd(c.q, c.kv, c.indices, c.sm_scale, check=True, algo=algo)
     ref_out, ref_lse = sparse_mla_fwd(c.q, c.kv, c.indices, c.sm_scale, check=True, algo=1)

@@ -32,9 +32,9 @@ def _errors(out, lse, ref_out, ref_lse):
     return e_out, e_lse
 
 
-# every bf16 kernel behind algo_id: 5 is what algo_id 0 selects
-ALGOS = [1, 5, 7, 9, 10]
-ALGO_IDS = ["single_cta", "persistent", "persistent_64row", "persistent_wide_gathers", "persistent_ring"]
+# both bf16 kernels behind algo_id: 5 is what algo_id 0 selects
+ALGOS = [1, 5]
+ALGO_IDS = ["single_cta", "persistent"]
 
 
 def _check(q, kv, idx, sm_scale, name="", algo=0):
@@ -153,7 +153,7 @@ def _stepped_scores_case(order, n_tiles=5, h=128, s_q=3, seed=3):
     return q, kv, idx
 
 
-@pytest.mark.parametrize("algo", [0, 5, 7, 9, 10, 1], ids=["default", "persistent", "persistent_64row", "persistent_wide_gathers", "persistent_ring", "single_cta"])
+@pytest.mark.parametrize("algo", [0, 1], ids=["default", "single_cta"])
 @pytest.mark.parametrize("order", ["up", "down", "mixed"])
 def test_running_maximum_steps_across_tiles(order, algo):
     """The online softmax (test_accuracy_musa_vllm_mla.py:313-320) rescales its accumulator whenever the row
@@ -177,11 +177,11 @@ def test_large_random_scores_are_stable():
     q = (torch.randn(3, 128, 576, generator=g) * 8).bfloat16()
     kv = torch.randn(700, 576, generator=g).bfloat16()
     idx = torch.stack([torch.randperm(700, generator=g)[:640] for _ in range(3)]).int()
-    for algo in (0, 7, 9, 10, 1):
+    for algo in (0, 1):
         _check(q, kv, idx, 0.5, f"large_scores_algo{algo}", algo)
 
 
-@pytest.mark.parametrize("algo", [0, 7, 9, 10, 1], ids=["default", "persistent_64row", "persistent_wide_gathers", "persistent_ring", "single_cta"])
+@pytest.mark.parametrize("algo", [0, 1], ids=["default", "single_cta"])
 def test_base2_lse_convention(algo):
     """lse_base2: the log-sum-exp in base-2 units of score * log2(e), the convention of the reference's dense
     attention (python/triton/ops/flash_attention.py:103) = natural-log LSE / ln 2; the output does not change."""
@@ -299,7 +299,7 @@ def test_negative_index_other_than_padding_is_reported():
     q = torch.randn(2, 16, 576, generator=g).bfloat16().to(DEV)
     kv = torch.randn(32, 576, generator=g).bfloat16().to(DEV)
     idx = torch.tensor([[0, 1, -2, 3], [4, -1, 5, 6]], dtype=torch.int32, device=DEV)
-    for algo in (0, 7, 9, 10, 1):
+    for algo in (0, 1):
         with pytest.raises(RuntimeError, match="BAD_INDEX"):
             sparse_mla_fwd(q, kv, idx, 0.1, check=True, algo=algo)
 
