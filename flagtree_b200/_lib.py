@@ -126,6 +126,13 @@ def load() -> C.CDLL:
             lib.ftb_gemm_rs_fp8.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
                                             C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
             lib.ftb_gemm_rs_fp8.restype = C.c_int
+            lib.ftb_ag_gemm_workspace_bytes.argtypes = [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
+            lib.ftb_ag_gemm_ctx_create.argtypes = [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int, C.c_int,
+                                                   C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
+            lib.ftb_ag_gemm_ctx_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
+            lib.ftb_ag_gemm_ctx_destroy.argtypes = [C.c_void_p]
+            lib.ftb_ag_gemm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64,
+                                        C.c_int64, C.c_void_p, C.c_void_p]
             lib.ftb_ipc_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.POINTER(C.c_uint8)]
             lib.ftb_ipc_open.argtypes = [C.POINTER(C.c_uint8), C.POINTER(C.c_void_p)]
             lib.ftb_ipc_close.argtypes = [C.c_void_p]

@@ -73,6 +73,9 @@ struct Params {
   unsigned int* ce_ready;            // [tp] (NULL = another protocol)
   unsigned int* ce_cnt;              // [tp] epilogue-warp arrivals per row shard, monotonic over calls
   unsigned int ce_target;            // value ce_cnt[d] reaches in this call
+  // all-gather + GEMM: the rows of A arrive shard by shard (copy engines of the peers); ag_flags[src] takes the
+  // call number once rank src's shard is in place.  NULL = A is complete at launch.
+  const unsigned int* ag_flags;
 };
 
 
@@ -127,8 +130,10 @@ __device__ __forceinline__ void tile_coords(const Params& p, int t, int cta, int
   }
   const int groups_per_shard = p.blocks_per_shard / NCTA;
   const int per_shard = groups_per_shard * p.n_blocks;
-  const int ord = t / per_shard;                     // remote shards first, own shard last
-  dst = (p.rank + 1 + ord) % p.tp;
+  const int ord = t / per_shard;
+  // reduce-scatter: remote shards first, own shard last.  All-gather: own rows first, then the shard of rank - 1
+  // (every rank sends to rank + 1 first), rank - 2, ...
+  dst = p.ag_flags != nullptr ? (p.rank - ord + p.tp) % p.tp : (p.rank + 1 + ord) % p.tp;
   const int r = t - ord * per_shard;
   const int mg = r / p.n_blocks;
   n_blk = r - mg * p.n_blocks;
@@ -305,7 +310,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (bars->abort_flag) {
     // copy-engine exchange: the second stream waits for the ready words whatever became of this launch
     if (p.ce_ready != nullptr && blockIdx.x == 0 && tid < p.tp) st_release_sys(p.ce_ready + tid, p.epoch);
-    return;
+    return;   // (an all-gather launch that leaves here does not release the peers: the context is dead)
   }
   if (warp == 1) {
     if constexpr (NCTA == 1) {
@@ -329,6 +334,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       for (int t = group; t < p.n_tiles; t += n_groups) {
         int m_blk, n_blk, dst;
         tile_coords<NCTA, PULL>(p, t, cta, m_blk, n_blk, dst);
+        if (p.ag_flags != nullptr && ld_acquire_sys(p.ag_flags + dst) < p.epoch && !*abort_flag) {
+          // all-gather: the rows of this tile come from rank dst; wait (bounded) until its copy has landed
+          const long long t0 = clock64();
+          while (ld_acquire_sys(p.ag_flags + dst) < p.epoch) {
+            if (*abort_flag) break;
+            if (clock64() - t0 > p.wait_limit) { *abort_flag = 1; break; }
+            __nanosleep(200);
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");   // the copy was seen through the generic proxy, the loads below use the async one
+        }
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
@@ -433,7 +448,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       tile_coords<NCTA, PULL>(p, t, cta, m_blk, n_blk, dst);
       const uint32_t acc = local & 1u;
       const int row = m_blk * BM + lg * 32 + lane;
-      const bool ce = !PULL && p.ce_ready != nullptr;
+      const bool ag = !PULL && p.ag_flags != nullptr;
+      const bool ce = !PULL && (p.ce_ready != nullptr || ag);      // both store every tile plainly into c
       const bool remote = !PULL && !ce && p.tp > 1 && dst != p.rank;
       if constexpr (PULL) {
         // Before overwriting a row block of the partial buffer make sure its owner has fetched the
@@ -636,7 +652,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();                  // orders the 32 lanes' stores before lane 0's fence one tile later
         if (lane == 0) {
           release_acc(acc);
-          if (ce) ce_pending = dst;    // counted one tile late, see above
+          if (ce && !ag) ce_pending = dst;    // counted one tile late, see above
         }
       }
     }
@@ -717,7 +733,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const unsigned int prev = atomicAdd(p.counter, 1u);
     if (prev == gridDim.x - 1) {   // every CTA of the launch has arrived
       *p.counter = 0;
-      if (p.ce_ready != nullptr) {
+      if (p.ag_flags != nullptr) {
+        // all-gather: every peer may overwrite its shard in this rank's gather buffer
+        for (int peer = 0; peer < p.tp; ++peer) st_release_sys(p.flags[peer] + p.tp + p.rank, p.epoch);
+      } else if (p.ce_ready != nullptr) {
         st_release_sys(p.flags[p.rank] + p.rank, p.epoch);
       } else {
         for (int peer = 0; peer < p.tp; ++peer)
@@ -1407,3 +1426,138 @@ extern "C" FTB_API int ftb_ipc_open(const uint8_t handle[64], void** ptr) {
 extern "C" FTB_API int ftb_ipc_close(void* ptr) { return check_cuda(cudaIpcCloseMemHandle(ptr), "ftb_ipc_close"); }
 extern "C" FTB_API int ftb_ipc_free(void* ptr) { return check_cuda(cudaFree(ptr), "ftb_ipc_free"); }
 
+
+
+// ---------------------------------------------------------------------------------------------
+// All-gather + GEMM (the column-parallel sibling that feeds the row-parallel GEMM + reduce-scatter).
+//
+// Rank r holds the row shard A_r [m / tp, k] and its weight columns B_r [k, n_local]; every rank computes
+// C_r = A . B_r with A [m, k] the shards of all ranks stacked in rank order.  The shards travel on the copy
+// engines: a second stream copies this rank's shard into every peer's gather buffer (rank + 1 first) and raises
+// the peer's flag with a four-byte copy of the call number; it runs no kernel.  One persistent GEMM launch reads
+// A from the rank's gather buffer, own rows first, then the shards in the order in which they are sent to it; its
+// TMA producer waits (bounded) for a shard's flag before it loads the shard's first tile.  The kernel's last CTA
+// tells the peers that the gather buffer has been read, which is what their next call's copies wait for.
+// Flag words of rank d: [src] = last call whose shard from rank src has landed, [tp + src] = last call in which
+// rank src finished reading rank d's shard out of src's own gather buffer.
+struct ftb_ag_gemm_ctx {
+  int rank, tp, m, k, shard_rows;
+  void* ag[gemm::MAX_TP];              // gather buffers [m, k] bf16 (peer-mapped)
+  unsigned int* flags[gemm::MAX_TP];
+  unsigned int* d_counter;
+  unsigned int* d_epoch_word;
+  cudaStream_t comm;
+  cudaEvent_t ev_fork, ev_join;
+  unsigned int epoch;
+  long long wait_limit;
+};
+
+extern "C" FTB_API int ftb_ag_gemm_workspace_bytes(int m, int k, int tp, int64_t* ag_bytes, int64_t* flag_bytes) {
+  if (m <= 0 || k <= 0 || tp <= 0 || tp > gemm::MAX_TP || (m % (tp * gemm::BM)) || (k % 8) || !ag_bytes || !flag_bytes) {
+    set_last_error("ftb_ag_gemm_workspace_bytes: need 1 <= tp <= 8, m a multiple of tp*128, k a multiple of 8");
+    return FTB_ERR_INVALID;
+  }
+  *ag_bytes = static_cast<int64_t>(m) * k * 2;
+  *flag_bytes = 256;
+  return FTB_OK;
+}
+
+extern "C" FTB_API int ftb_ag_gemm_ctx_create(ftb_ag_gemm_ctx** out, int rank, int tp, int m, int k, void* const* ag_ptrs,
+                                              void* const* flag_ptrs) {
+  int64_t ab, fb;
+  if (!out || !ag_ptrs || !flag_ptrs || rank < 0 || rank >= tp) { set_last_error("ftb_ag_gemm_ctx_create: bad argument"); return FTB_ERR_INVALID; }
+  int rc = ftb_ag_gemm_workspace_bytes(m, k, tp, &ab, &fb);
+  if (rc != FTB_OK) return rc;
+  ftb_ag_gemm_ctx* c = new ftb_ag_gemm_ctx();
+  memset(c, 0, sizeof(*c));
+  c->rank = rank; c->tp = tp; c->m = m; c->k = k; c->shard_rows = m / tp;
+  c->wait_limit = kWaitLimitCycles;
+  for (int i = 0; i < tp; ++i) {
+    if (!ag_ptrs[i] || !flag_ptrs[i]) { delete c; set_last_error("ftb_ag_gemm_ctx_create: null peer pointer"); return FTB_ERR_INVALID; }
+    c->ag[i] = ag_ptrs[i];
+    c->flags[i] = reinterpret_cast<unsigned int*>(flag_ptrs[i]);
+  }
+  cudaError_t e = cudaMalloc(&c->d_counter, sizeof(unsigned int));
+  if (e == cudaSuccess) e = cudaMemset(c->d_counter, 0, sizeof(unsigned int));
+  if (e == cudaSuccess) e = cudaMalloc(&c->d_epoch_word, sizeof(unsigned int));
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->comm, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming);
+  if (e != cudaSuccess) { ftb_ag_gemm_ctx_destroy(c); return check_cuda(e, "ftb_ag_gemm_ctx_create"); }
+  *out = c;
+  return FTB_OK;
+}
+
+extern "C" FTB_API int ftb_ag_gemm_ctx_set_wait_limit(ftb_ag_gemm_ctx* c, int64_t cycles) {
+  if (!c || cycles <= 0) { set_last_error("ftb_ag_gemm_ctx_set_wait_limit: need a context and a positive cycle count"); return FTB_ERR_INVALID; }
+  c->wait_limit = cycles;
+  return FTB_OK;
+}
+
+extern "C" FTB_API int ftb_ag_gemm_ctx_destroy(ftb_ag_gemm_ctx* c) {
+  if (!c) return FTB_OK;
+  cudaFree(c->d_counter);
+  cudaFree(c->d_epoch_word);
+  if (c->comm) cudaStreamDestroy(c->comm);
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
+  delete c;
+  return FTB_OK;
+}
+
+extern "C" FTB_API int ftb_ag_gemm(ftb_ag_gemm_ctx* c, const void* a_shard, const void* b, void* out, int n_local, int64_t lda,
+                                   int64_t ldb, int64_t ldc, int32_t* status, void* stream) {
+  if (!c || !a_shard || !b || !out) { set_last_error("ftb_ag_gemm: null pointer"); return FTB_ERR_INVALID; }
+  if ((ldc % 8) || (reinterpret_cast<uintptr_t>(out) & 15) || (lda % 8) || (reinterpret_cast<uintptr_t>(a_shard) & 15)) {
+    set_last_error("ftb_ag_gemm: a_shard and out must be 16-byte aligned with leading dimensions that are multiples of 8");
+    return FTB_ERR_INVALID;
+  }
+  const int ok = gemm_operands_ok(c->ag[c->rank], b, c->m, n_local, c->k, c->k, ldb);
+  if (ok != FTB_OK) return ok;
+  static StreamValue32Fn wait32 = get_stream_memop("cuStreamWaitValue32");
+  static StreamValue32Fn write32 = get_stream_memop("cuStreamWriteValue32");
+  if (!wait32 || !write32) { set_last_error("ftb_ag_gemm: stream memory operations are not available"); return FTB_ERR_UNSUPPORTED; }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  c->epoch += 1;
+  const unsigned int epoch = c->epoch;
+  const int tp = c->tp, rank = c->rank;
+  const size_t shard_bytes = static_cast<size_t>(c->shard_rows) * c->k * 2;
+  cudaError_t e = cudaEventRecord(c->ev_fork, st);      // the shard is ready on the caller's stream
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm, c->ev_fork, 0);
+  if (e != cudaSuccess) return check_cuda(e, "ag_gemm fork");
+  // ---- second stream: own shard into the own gather buffer, then to the peers, rank + 1 first
+  CUresult r = write32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_epoch_word), epoch, CU_STREAM_WRITE_VALUE_DEFAULT);
+  if (r != CUDA_SUCCESS) { set_last_error("ftb_ag_gemm: cuStreamWriteValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
+  for (int s = 0; s < tp; ++s) {
+    const int d = (rank + s) % tp;
+    // rank d has read the gather buffer of the call before (its word [tp + d] in this rank's flags; for d = rank the
+    // word is written by this rank's own GEMM of that call, which the fork event already covers)
+    if (d != rank && epoch > 1u) {
+      r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->flags[rank] + tp + d), epoch - 1u, CU_STREAM_WAIT_VALUE_GEQ);
+      if (r != CUDA_SUCCESS) { set_last_error("ftb_ag_gemm: cuStreamWaitValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
+    }
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c->ag[d]) + static_cast<size_t>(rank) * c->shard_rows * c->k;
+    e = cudaMemcpy2DAsync(dst, static_cast<size_t>(c->k) * 2, a_shard, static_cast<size_t>(lda) * 2, static_cast<size_t>(c->k) * 2,
+                          static_cast<size_t>(c->shard_rows), cudaMemcpyDeviceToDevice, c->comm);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(c->flags[d] + rank, c->d_epoch_word, sizeof(unsigned int), cudaMemcpyDeviceToDevice, c->comm);
+    if (e != cudaSuccess) return check_cuda(e, "ag_gemm copy");
+  }
+  (void)shard_bytes;
+  e = cudaEventRecord(c->ev_join, c->comm);
+  if (e != cudaSuccess) return check_cuda(e, "ag_gemm join");
+  // ---- the GEMM over the gather buffer
+  gemm::Params p;
+  memset(&p, 0, sizeof(p));
+  p.tp = tp; p.rank = rank; p.shard_rows = c->shard_rows; p.blocks_per_shard = c->shard_rows / gemm::BM;
+  p.epoch = epoch;
+  p.c = reinterpret_cast<__nv_bfloat16*>(out); p.ldc = ldc;
+  p.status = status;
+  p.wait_limit = c->wait_limit;
+  p.ag_flags = c->flags[rank];
+  p.counter = c->d_counter;
+  for (int i = 0; i < tp; ++i) p.flags[i] = c->flags[i];
+  int rc = launch_gemm(c->ag[rank], b, c->m, n_local, c->k, c->k, ldb, p, st);
+  if (rc != FTB_OK) return rc;
+  // the caller may overwrite its shard once the copies have read it
+  return check_cuda(cudaStreamWaitEvent(st, c->ev_join, 0), "ag_gemm join wait");
+}

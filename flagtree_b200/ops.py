@@ -557,6 +557,87 @@ class GemmRsContext:
             self.flags.close()
 
 
+class AgGemmContext:
+    """Workspace of one (M, K, group) all-gather + GEMM shape: peer-mapped gather buffers [M, K] and flags.
+    Creation and `close` are collective over `group`.  One call may be in flight per context."""
+
+    def __init__(self, m: int, k: int, group=None, device: Optional[torch.device] = None, provider: str = "auto"):
+        import torch.distributed as dist
+        from .symm import SymmetricBuffer
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.tp = dist.get_world_size(group)
+        self.m, self.k = m, k
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        lib = _lib.load()
+        ab, fb = C.c_int64(), C.c_int64()
+        _lib.check(lib.ftb_ag_gemm_workspace_bytes(m, k, self.tp, C.byref(ab), C.byref(fb)), "ag_gemm workspace")
+        with torch.cuda.device(self.device):
+            self.ag = SymmetricBuffer(ab.value, group, self.device, provider)
+            self.flags = SymmetricBuffer(fb.value, group, self.device, provider)
+            ag_ptrs = (C.c_void_p * self.tp)(*self.ag.ptrs)
+            flag_ptrs = (C.c_void_p * self.tp)(*self.flags.ptrs)
+            ctx = C.c_void_p()
+            _lib.check(lib.ftb_ag_gemm_ctx_create(C.byref(ctx), self.rank, self.tp, m, k, ag_ptrs, flag_ptrs), "ag_gemm ctx_create")
+        self._ctx = ctx
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def __call__(self, a_shard: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        _require_cuda(a_shard, b)
+        assert a_shard.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+        assert a_shard.shape == (self.m // self.tp, self.k) and b.shape[0] == self.k, "incompatible dimensions"
+        assert a_shard.stride(1) == 1 and b.stride(1) == 1
+        n_local = b.shape[1]
+        if out is None:
+            out = torch.empty(self.m, n_local, dtype=torch.bfloat16, device=a_shard.device)
+        assert out.shape == (self.m, n_local) and out.stride(1) == 1
+        with torch.cuda.device(a_shard.device):
+            rc = _lib.load().ftb_ag_gemm(self._ctx, a_shard.data_ptr(), b.data_ptr(), out.data_ptr(), n_local, a_shard.stride(0),
+                                         b.stride(0), out.stride(0), self.status.data_ptr(), C.c_void_p(_stream_ptr(a_shard.device)))
+        _lib.check(rc, "ag_gemm")
+        return out
+
+    def set_wait_limit(self, cycles: int):
+        _lib.check(_lib.load().ftb_ag_gemm_ctx_set_wait_limit(self._ctx, int(cycles)), "ag_gemm set_wait_limit")
+
+    def check(self):
+        _check_status(self.status, "ag_gemm")
+
+    def close(self):
+        if self._ctx is not None:
+            import torch.distributed as dist
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+            _lib.load().ftb_ag_gemm_ctx_destroy(self._ctx)
+            self._ctx = None
+            self.ag.close_peers()
+            self.flags.close_peers()
+            dist.barrier(self.group)
+            self.ag.close()
+            self.flags.close()
+
+
+_AG_CONTEXTS = {}
+
+
+def ag_gemm(a_shard: torch.Tensor, b: torch.Tensor, group=None, *, out: Optional[torch.Tensor] = None,
+            check: bool = False) -> torch.Tensor:
+    """All-gather + GEMM: rank r passes its row shard A_r [M/tp, K] and its weight columns B_r [K, N_local] and gets
+    C_r [M, N_local] = cat_r(A_r) @ B_r as bf16 (the column-parallel step that precedes `gemm_rs`).  Collective over
+    `group`; the workspace of each (M, K, group) is created on first use and cached."""
+    import torch.distributed as dist
+    tp = dist.get_world_size(group)
+    m, k = a_shard.shape[0] * tp, a_shard.shape[1]
+    key = (m, k, a_shard.device.index, id(group))
+    hit = _AG_CONTEXTS.get(key)
+    if hit is None or hit[0] is not group:
+        hit = _AG_CONTEXTS[key] = (group, AgGemmContext(m, k, group, a_shard.device))
+    res = hit[1](a_shard, b, out)
+    if check:
+        hit[1].check()
+    return res
+
+
 _RS_CONTEXTS = {}     # (form, M, N, device, group key) -> (group, context); holding the group keeps its id unique
 
 
@@ -569,10 +650,13 @@ def _rs_context(form: str, m: int, n: int, group, device) -> "GemmRsContext":
 
 
 def gemm_rs_close_all():
-    """Closes every workspace that `gemm_rs` / `gemm_rs_fp8` created (collective over their groups)."""
+    """Closes every workspace that `gemm_rs` / `gemm_rs_fp8` / `ag_gemm` created (collective over their groups)."""
     for key in sorted(_RS_CONTEXTS, key=lambda k: (k[0], k[1], k[2], k[3])):
         _RS_CONTEXTS[key][1].close()
     _RS_CONTEXTS.clear()
+    for key in sorted(_AG_CONTEXTS, key=lambda k: (k[0], k[1], k[2])):
+        _AG_CONTEXTS[key][1].close()
+    _AG_CONTEXTS.clear()
 
 
 def gemm_rs(a: torch.Tensor, b: torch.Tensor, group=None, *, out: Optional[torch.Tensor] = None,

@@ -264,6 +264,27 @@ FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* ctx, const void* a, const void* b, 
                             const float* b_scale, void* out, int k_local, int64_t lda, int64_t ldb,
                             int64_t a_scale_ld, int64_t b_scale_ld, int64_t ldo, int32_t* status, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * All-gather + GEMM, the column-parallel sibling that feeds ftb_gemm_rs in a tensor-parallel block: rank r
+ * holds the row shard A_r [m / tp, k] bf16 and its weight columns B_r [k, n_local]; every rank gets
+ * C_r [m, n_local] = A . B_r with A the shards of all ranks stacked in rank order.  The reference has no
+ * collective; the GEMM core replaces python/triton/ops/matmul.py:92-151 as above.  The shards travel on the copy
+ * engines while the GEMM already multiplies the rows that have arrived (own rows first).
+ * Workspace: every rank provides a gather buffer (ag_bytes) and a flag buffer (flag_bytes), zero-initialised and
+ * mapped into every peer; `ag_ptrs[i]` / `flag_ptrs[i]` are this process's pointers to rank i's.  One call in
+ * flight per context, same order on every rank; device-side waits are bounded (FTB_ERR_TIMEOUT), the stream
+ * waits of the second stream are not.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ftb_ag_gemm_ctx ftb_ag_gemm_ctx;
+FTB_API int ftb_ag_gemm_workspace_bytes(int m, int k, int tp, int64_t* ag_bytes, int64_t* flag_bytes);
+FTB_API int ftb_ag_gemm_ctx_create(ftb_ag_gemm_ctx** ctx, int rank, int tp, int m, int k, void* const* ag_ptrs,
+                                   void* const* flag_ptrs);
+FTB_API int ftb_ag_gemm_ctx_set_wait_limit(ftb_ag_gemm_ctx* ctx, int64_t cycles);
+FTB_API int ftb_ag_gemm_ctx_destroy(ftb_ag_gemm_ctx* ctx);
+/* a_shard [m / tp, k] bf16 (lda), b [k, n_local] bf16 (ldb), out [m, n_local] bf16 (ldc). */
+FTB_API int ftb_ag_gemm(ftb_ag_gemm_ctx* ctx, const void* a_shard, const void* b, void* out, int n_local, int64_t lda,
+                        int64_t ldb, int64_t ldc, int32_t* status, void* stream);
+
 FTB_API int ftb_ipc_alloc(int64_t bytes, void** ptr, uint8_t handle[64]);
 FTB_API int ftb_ipc_open(const uint8_t handle[64], void** ptr);
 FTB_API int ftb_ipc_close(void* ptr);

@@ -51,6 +51,13 @@ def gemm_rs_rows_ref(a_ranks: Sequence[torch.Tensor], b_ranks: Sequence[torch.Te
     return total
 
 
+def ag_gemm_ref(a_shards: Sequence[torch.Tensor], b_rank: torch.Tensor) -> torch.Tensor:
+    """All-gather + GEMM: a_shards[r] [M/tp, K] stacked in rank order, times this rank's B [K, N_local], fp32.
+    The dense product follows python/test/unit/operators/test_matmul.py:187-199 (golden = torch.matmul); the
+    reference has no collective, so the gather is defined here: rows of rank r are rows [r*M/tp, (r+1)*M/tp)."""
+    return torch.matmul(torch.cat([_f32(a) for a in a_shards], dim=0), _f32(b_rank))
+
+
 def dequant_block_scaled(x_u8: torch.Tensor, scale: torch.Tensor, block_r: int, block_c: int) -> torch.Tensor:
     """e4m3 bytes [R, C] with one fp32 scale per (block_r x block_c) block -> fp32 [R, C]."""
     if x_u8.dtype != torch.uint8:

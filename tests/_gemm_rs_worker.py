@@ -66,6 +66,25 @@ def main():
               f"repeat-identical {same}", flush=True)
         ok = ok and err <= (world + 1) * 2 ** -8 * scale and same
         ctx.close()
+    # all-gather + GEMM: every rank's row shard of A against this rank's weight columns
+    from flagtree_b200 import AgGemmContext
+    from oracle.gemm_rs_ref import ag_gemm_ref
+    for (m, k, n_local) in [(world * 128, 64, 256), (world * 256, 320, 1000), (world * 1024, 2304, 1792)]:
+        g = torch.Generator().manual_seed(4242)
+        shards = [(torch.randn(m // world, k, generator=g) * k ** -0.5).bfloat16() for _ in range(world)]
+        bs = [(torch.randn(k, n_local, generator=g)).bfloat16() for _ in range(world)]
+        ref = ag_gemm_ref(shards, bs[rank])
+        ctx = AgGemmContext(m, k, None, dev, provider)
+        a, b = shards[rank].to(dev), bs[rank].to(dev)
+        outs = [ctx(a, b).clone() for _ in range(3)]
+        torch.cuda.synchronize()
+        ctx.check()
+        err = (outs[0].float().cpu() - ref).abs().max().item()
+        scale = ref.abs().max().item()
+        same = all(torch.equal(outs[0], o) for o in outs[1:])
+        print(f"[rank {rank}] ag_gemm m={m} k={k} n_local={n_local}: err {err:.3e} scale {scale:.3e} repeat-identical {same}", flush=True)
+        ok = ok and err <= 2 ** -8 * scale and same
+        ctx.close()
     t = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()

@@ -92,6 +92,21 @@ def _case_reduce_scatter_fp8_convention(rank, world):
     assert torch.allclose(out, ref, rtol=1e-5, atol=1e-5)
 
 
+def _case_all_gather_gemm_convention(rank, world):
+    """All-gather + GEMM: the oracle's result of rank r equals gloo's all_gather of the row shards times the rank's
+    weight columns; rows of rank s sit at [s * M / tp, (s + 1) * M / tp)."""
+    from oracle.gemm_rs_ref import ag_gemm_ref
+    g = torch.Generator().manual_seed(5)
+    shards = [torch.randn(8, 24, generator=g).bfloat16() for _ in range(world)]
+    bs = [torch.randn(24, 16, generator=g).bfloat16() for _ in range(world)]
+    gathered = [torch.empty(8, 24, dtype=torch.bfloat16) for _ in range(world)]
+    dist.all_gather(gathered, shards[rank])
+    out = torch.cat(gathered).float() @ bs[rank].float()
+    ref = ag_gemm_ref(shards, bs[rank])
+    assert torch.equal(out, ref)
+    assert torch.equal(ref[rank * 8:(rank + 1) * 8], shards[rank].float() @ bs[rank].float())
+
+
 def _case_mla_sequence_sharded_kv(rank, world):
     """A context whose latent rows are sharded over the ranks: each rank runs the forward over its own rows with
     `shard_indices` (entries outside its range become padding), the (out, lse) parts are all-gathered, and the
@@ -120,7 +135,8 @@ def _case_mla_sequence_sharded_kv(rank, world):
 @pytest.mark.parametrize("fn,port", [("_case_symmetric_exchange", 29611), ("_case_mla_token_sharding", 29612),
                                      ("_case_reduce_scatter_convention", 29613),
                                      ("_case_reduce_scatter_fp8_convention", 29614),
-                                     ("_case_mla_sequence_sharded_kv", 29615)])
+                                     ("_case_mla_sequence_sharded_kv", 29615),
+                                     ("_case_all_gather_gemm_convention", 29616)])
 def test_two_ranks_gloo(fn, port):
     _spawn(fn, 2, port)
 
