@@ -189,6 +189,24 @@ def bench_kv_cache_write(args, dev, peaks):
             "l2": "new rows (302 MB) larger than L2"}
 
 
+def bench_topk_indices(args, dev, peaks):
+    """The index producer of the headline workload: 4096 tokens, 32768 scores each, the 2048 largest.  Bound by
+    device memory: 4 * s_kv bytes of scores read and 4 * topk bytes of indices written per token; the scores
+    (537 MB) exceed L2."""
+    from flagtree_b200 import topk_indices
+    g = torch.Generator(device=dev)
+    g.manual_seed(3200)
+    s_q, s_kv, topk = 4096, 32768, 2048
+    scores = torch.randn(s_q, s_kv, generator=g, device=dev)
+    out = torch.empty(s_q, topk, dtype=torch.int32, device=dev)
+    iters = max(5, min(args.steps, 20))
+    ms = _time_events(lambda: topk_indices(scores, topk, out=out), iters)
+    nbytes = s_q * (4 * s_kv + 4 * topk)
+    return {"workload": f"topk_indices_sq{s_q}_skv{s_kv}_topk{topk}", "ms": ms, "iters": iters, "bytes": nbytes,
+            "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+            "bound": "hbm", "kernel": "topk_select_kernel", "l2": "scores (537 MB) larger than L2"}
+
+
 def bench_fp8_dense_peak(dev):
     """A plain library FP8 GEMM (cuBLASLt through torch._scaled_mm, e4m3 x e4m3 -> bf16, 8192^3) timed once as the
     dense FP8 figure to hold the block-scaled FP8 kernels against; None when this torch has no such op."""
@@ -310,6 +328,51 @@ def bench_gemm_rs(args, dev, rank, world, dist, peaks):
         ctx.close()
     else:
         res.update({"tflops_per_gpu": flops / t_gemm / 1e9, "frac_of_peak": flops / t_gemm / 1e9 / peaks["bf16_tflops"]})
+    return res
+
+
+def bench_ag_gemm(args, dev, rank, world, dist, peaks):
+    """The column-parallel sibling of cfg4: all-gather of the row shards of A [8192, 7168] fused with the GEMM against
+    this rank's weight columns [7168, 2304] (the same flops and the same bytes over NVLink per rank as cfg4).
+    Timed against the plain GEMM on an A that is already complete; checked against an fp32 product of NCCL's
+    all-gather of the shards."""
+    from flagtree_b200 import AgGemmContext, matmul
+    m, k, n_loc = 8192, 7168, 2304
+    g = torch.Generator(device=dev)
+    g.manual_seed(4100 + rank)
+    a_shard = (torch.randn(m // world, k, generator=g, device=dev) * k ** -0.5).bfloat16()
+    b = torch.randn(k, n_loc, generator=g, device=dev).bfloat16()
+    a_all = [torch.empty_like(a_shard) for _ in range(world)]
+    dist.all_gather(a_all, a_shard)
+    a_full = torch.cat(a_all)
+    flops = 2 * m * k * n_loc
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    sync_word = torch.zeros(1, device=dev)
+    iters = max(5, min(args.steps, 20))
+    c = torch.empty(m, n_loc, dtype=torch.bfloat16, device=dev)
+    t_gemm = _timed_collective(lambda: matmul(a_full, b, out=c), iters, flush, dist, sync_word, dev)
+    ctx = AgGemmContext(m, k, None, dev)
+    out = torch.empty(m, n_loc, dtype=torch.bfloat16, device=dev)
+    t_fused = _timed_collective(lambda: ctx(a_shard, b, out), iters, flush, dist, sync_word, dev)
+    ctx.check()
+
+    def nccl_path():
+        dist.all_gather(a_all, a_shard)
+        matmul(torch.cat(a_all), b, out=c)
+
+    t_nccl = _timed_collective(nccl_path, iters, flush, dist, sync_word, dev)
+    ctx(a_shard, b, out)
+    torch.cuda.synchronize()
+    ref = a_full.float() @ b.float()
+    err, scale = float((out.float() - ref).abs().max()), float(ref.abs().max())
+    okt = torch.tensor([1 if err <= 2 ** -8 * scale else 0], device=dev)
+    dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+    res = {"workload": f"ag_gemm_m{m}_k{k}_nlocal{n_loc}_tp{world}", "tp": world, "dtype": "bf16", "flops_per_gpu": flops,
+           "gemm_only_ms": t_gemm, "fused_ms": t_fused, "tflops_per_gpu": flops / t_fused / 1e9,
+           "frac_of_peak": flops / t_fused / 1e9 / peaks["bf16_tflops"], "exposed_comm": t_fused / t_gemm - 1.0,
+           "nccl_all_gather_plus_gemm_ms": t_nccl, "gathered_bytes_per_gpu": (world - 1) / world * m * k * 2,
+           "parity": {"max_abs_err": err, "tol": 2 ** -8 * scale, "ok": bool(int(okt.item()) == 1)}, "iters": iters}
+    ctx.close()
     return res
 
 
@@ -546,15 +609,18 @@ def main():
                "note": "the step is bound by the host link: the floor is the same bytes copied both ways at once with no kernel"}
         del hq, hkv, hidx, hout, hlse
 
-    decode_fp8 = kv_write = None
+    decode_fp8 = kv_write = topk_b = None
     if world == 1 and not args.no_decode:
         decode_fp8 = bench_mla_decode_fp8(args, dev, peaks)
         kv_write = bench_kv_cache_write(args, dev, peaks)
+        topk_b = bench_topk_indices(args, dev, peaks)
     del case, out, lse
     torch.cuda.empty_cache()
-    gemm_rs = gemm_rs_fp8 = fp8_peak = None
+    gemm_rs = gemm_rs_fp8 = fp8_peak = ag = None
     if not args.no_gemm:
         gemm_rs = bench_gemm_rs(args, dev, rank, world, dist, peaks)
+        if world > 1:
+            ag = bench_ag_gemm(args, dev, rank, world, dist, peaks)
         if not args.no_fp8_sweep:
             if world == 1:
                 fp8_peak = bench_fp8_dense_peak(dev)
@@ -589,8 +655,8 @@ def main():
             "config": make_config(args.s_q),
             "roofline": roofline, "cpu_baseline": cpu_b, "e2e": e2e, "gpu_launches": args.steps,
             "strong_scaling": strong,
-            "gemm_rs": gemm_rs, "gemm_rs_fp8": gemm_rs_fp8,
-            "mla_decode_fp8": decode_fp8, "kv_cache_write": kv_write,
+            "gemm_rs": gemm_rs, "gemm_rs_fp8": gemm_rs_fp8, "ag_gemm": ag,
+            "mla_decode_fp8": decode_fp8, "kv_cache_write": kv_write, "topk_indices": topk_b,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

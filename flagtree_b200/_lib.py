@@ -67,6 +67,13 @@ class KvCacheWriteArgs(C.Structure):
                 ("status", C.c_void_p)]
 
 
+class TopkArgs(C.Structure):
+    """Mirror of `ftb_topk_args`."""
+    _fields_ = [("scores", C.c_void_p), ("lengths", C.c_void_p), ("out", C.c_void_p),
+                ("s_q", C.c_int32), ("s_kv", C.c_int32), ("topk", C.c_int32),
+                ("scores_stride_token", C.c_int64), ("out_stride_token", C.c_int64)]
+
+
 _lib = None
 _lock = threading.Lock()
 
@@ -109,6 +116,9 @@ def load() -> C.CDLL:
             lib.ftb_kv_cache_write_fp8.argtypes = [C.POINTER(KvCacheWriteArgs), C.c_void_p]
             lib.ftb_kv_cache_write_workspace_bytes.argtypes = [C.c_int32]
             lib.ftb_kv_cache_write_workspace_bytes.restype = C.c_int64
+            if lib.ftb_sizeof_topk_args() != C.sizeof(TopkArgs):
+                raise RuntimeError("ftb_topk_args layout differs between the header and the Python mirror")
+            lib.ftb_topk_indices.argtypes = [C.POINTER(TopkArgs), C.c_void_p]
             lib.ftb_gemm_bf16.argtypes = [C.POINTER(GemmArgs), C.c_void_p]
             if lib.ftb_sizeof_gemm_fp8_args() != C.sizeof(GemmFp8Args):
                 raise RuntimeError("ftb_gemm_fp8_args layout differs between the header and the Python mirror")

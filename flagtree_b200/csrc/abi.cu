@@ -33,3 +33,4 @@ extern "C" FTB_API int ftb_sizeof_gemm_args(void) { return static_cast<int>(size
 extern "C" FTB_API int ftb_sizeof_gemm_fp8_args(void) { return static_cast<int>(sizeof(ftb_gemm_fp8_args)); }
 extern "C" FTB_API int ftb_sizeof_sparse_mla_merge_args(void) { return static_cast<int>(sizeof(ftb_sparse_mla_merge_args)); }
 extern "C" FTB_API int ftb_sizeof_kv_cache_write_args(void) { return static_cast<int>(sizeof(ftb_kv_cache_write_args)); }
+extern "C" FTB_API int ftb_sizeof_topk_args(void) { return static_cast<int>(sizeof(ftb_topk_args)); }

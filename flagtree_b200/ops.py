@@ -335,6 +335,32 @@ def shard_indices(indices: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
     return torch.where(inside, indices - lo, torch.full_like(indices, -1))
 
 
+def topk_indices(scores: torch.Tensor, topk: int, lengths: Optional[torch.Tensor] = None, *,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The index producer in front of `sparse_mla_fwd`: scores [S_q, S_kv] fp32 -> indices [S_q, topk] int32, per
+    token the positions of the `topk` largest scores among its first `lengths[t]` positions (all of them when
+    `lengths` is None), ascending, padded with -1.  Exact: floats ordered by value with -0 below +0 and NaN above
+    +inf, ties to the lower position.  The reference builds index lists for its block-sparse ops on the device
+    in the same spirit (python/triton/ops/blocksparse/matmul.py:117-127)."""
+    _require_cuda(scores, lengths)
+    assert scores.dim() == 2 and scores.dtype == torch.float32 and scores.stride(1) == 1
+    s_q, s_kv = scores.shape
+    if lengths is not None:
+        assert lengths.dtype == torch.int32 and lengths.shape == (s_q,) and lengths.is_contiguous()
+    if out is None:
+        out = torch.empty(s_q, topk, dtype=torch.int32, device=scores.device)
+    assert out.shape == (s_q, topk) and out.dtype == torch.int32 and out.stride(1) == 1
+    a = _lib.TopkArgs()
+    a.scores, a.out = scores.data_ptr(), out.data_ptr()
+    a.lengths = lengths.data_ptr() if lengths is not None else None
+    a.s_q, a.s_kv, a.topk = s_q, s_kv, int(topk)
+    a.scores_stride_token, a.out_stride_token = scores.stride(0), out.stride(0)
+    with torch.cuda.device(scores.device):
+        rc = _lib.load().ftb_topk_indices(C.byref(a), C.c_void_p(_stream_ptr(scores.device)))
+    _lib.check(rc, "topk_indices")
+    return out
+
+
 def kv_cache_write_fp8(rows: torch.Tensor, slot_mapping: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Tensor,
                        page_size: int = 64, *, check: bool = False) -> None:
     """Quantise new latent rows to e4m3 with one fp32 scale per page and scatter them into the paged cache, in

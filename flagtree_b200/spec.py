@@ -25,5 +25,5 @@ def matmul_kernel(grid, a, b, c, M, N, K, acc_dtype, input_precision, fp8_fast_a
 
 
 def ops_modify_all(all_array):
-    all_array += ["sparse_mla_fwd", "sparse_mla_fwd_paged", "sparse_mla_merge", "kv_cache_write_fp8", "gemm_rs", "gemm_rs_fp8", "ag_gemm"]
+    all_array += ["sparse_mla_fwd", "sparse_mla_fwd_paged", "sparse_mla_merge", "kv_cache_write_fp8", "gemm_rs", "gemm_rs_fp8", "ag_gemm", "topk_indices"]
     return all_array

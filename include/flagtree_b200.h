@@ -139,6 +139,24 @@ FTB_API int ftb_sparse_mla_merge(const ftb_sparse_mla_merge_args* args, void* st
 FTB_API int ftb_sizeof_sparse_mla_merge_args(void);
 
 /* ------------------------------------------------------------------------------------------
+ * Top-k index producer, the step in front of the sparse MLA forward: for every query token the positions of the
+ * `topk` largest scores among its first lengths[t] key positions (all s_kv when lengths is NULL), in ascending
+ * position order, padded with -1: the `indices` argument of ftb_sparse_mla_fwd.  Exact and deterministic: floats
+ * are ordered by value (-0 below +0, NaN patterns above +inf), ties go to the lower position.  The reference has no
+ * such kernel; its nearest relatives are the look-up-table builders of the block-sparse ops,
+ *   python/triton/ops/blocksparse/matmul.py:117-127, which also turn a selection into index lists on the device.
+ * ------------------------------------------------------------------------------------------ */
+typedef struct ftb_topk_args {
+  const float* scores;        /* fp32 [s_q, s_kv], scores_stride_token elements between tokens */
+  const int32_t* lengths;     /* int32 [s_q] or NULL                                            */
+  int32_t* out;               /* int32 [s_q, topk], out_stride_token elements between tokens   */
+  int32_t s_q, s_kv, topk;
+  int64_t scores_stride_token, out_stride_token;
+} ftb_topk_args;
+FTB_API int ftb_topk_indices(const ftb_topk_args* args, void* stream);
+FTB_API int ftb_sizeof_topk_args(void);
+
+/* ------------------------------------------------------------------------------------------
  * Write path of the paged FP8 latent cache (the producer of the format the paged forward reads):
  * new latent rows are quantised to e4m3 with one fp32 scale per page and scattered into their slots.
  * Analogue of the reference's quantising cache writer

@@ -213,3 +213,25 @@ def kv_cache_write_fp8_ref(rows: torch.Tensor, slot_mapping: torch.Tensor, kv_ca
     qv = (x[keep] / scale[pages][:, None]).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8)
     flat[slots[keep]] = qv
     return cache, scale
+
+
+def topk_indices_ref(scores: torch.Tensor, topk: int, lengths: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """CPU restatement of the index producer: per token the positions of the `topk` largest scores among the first
+    lengths[t] positions, ascending, padded with -1.  Floats are ordered through the usual order-preserving map to
+    unsigned 32-bit keys (sign bit flipped for non-negative values, all bits for negative ones), so -0 < +0 and NaN
+    patterns sort by their bits; ties go to the lower position (stable sort)."""
+    import numpy as np
+    sc = scores.detach().to("cpu").to(torch.float32).contiguous().numpy()
+    s_q, s_kv = sc.shape
+    u = sc.view(np.uint32)
+    keys = np.where(u & np.uint32(0x80000000), ~u, u | np.uint32(0x80000000))
+    out = np.full((s_q, topk), -1, dtype=np.int32)
+    for t in range(s_q):
+        n = s_kv if lengths is None else max(0, min(int(lengths[t]), s_kv))
+        k = min(topk, n)
+        if k == 0:
+            continue
+        # stable descending order: negate the key order by sorting (max - key) ascending with a stable sort
+        order = np.argsort(np.uint32(0xFFFFFFFF) - keys[t, :n], kind="stable")[:k]
+        out[t, :k] = np.sort(order).astype(np.int32)
+    return torch.from_numpy(out)

@@ -10,7 +10,7 @@ def test_ops_modify_all_appends_this_package_ops():
     names = ["matmul", "attention"]
     res = spec.ops_modify_all(names)
     assert res is names
-    for op in ("sparse_mla_fwd", "sparse_mla_fwd_paged", "sparse_mla_merge", "kv_cache_write_fp8", "gemm_rs", "gemm_rs_fp8", "ag_gemm"):
+    for op in ("sparse_mla_fwd", "sparse_mla_fwd_paged", "sparse_mla_merge", "kv_cache_write_fp8", "gemm_rs", "gemm_rs_fp8", "ag_gemm", "topk_indices"):
         assert op in res
     assert res[:2] == ["matmul", "attention"]
     import flagtree_b200
