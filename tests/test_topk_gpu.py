@@ -13,7 +13,8 @@ from oracle.sparse_mla_ref import sparse_mla_fwd_ref, topk_indices_ref
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("s_kv,topk", [(1, 1), (37, 5), (512, 512), (513, 64), (4096, 2048), (70000, 2048)])
+@pytest.mark.parametrize("s_kv,topk", [(1, 1), (37, 5), (512, 512), (513, 64), (1024, 1000), (4096, 2048), (32768, 2048),
+                                       (70000, 2048)])
 def test_random_scores_match_exactly(s_kv, topk):
     g = torch.Generator().manual_seed(s_kv + topk)
     sc = torch.randn(9, s_kv, generator=g)
@@ -36,6 +37,19 @@ def test_ties_zeros_infinities_and_lengths():
     assert torch.equal(got[2], torch.arange(topk, dtype=torch.int32))
     assert (got[3] == -1).all() and got[4, 0] == 0 and (got[4, 1:] == -1).all()
     assert (got[5, :299] == torch.arange(299)).all() and got[5, 299] == -1
+
+
+def test_many_rows_with_causal_lengths_and_a_strided_view():
+    """More rows than SMs (the persistent kernel takes several rows per CTA), ragged lengths, ties from rounding the
+    scores to bf16, and a view whose rows are not contiguous."""
+    g = torch.Generator().manual_seed(11)
+    s_q, s_kv, topk = 700, 8192, 512
+    wide = torch.randn(s_q, s_kv + 64, generator=g).bfloat16().float()
+    sc = wide[:, :s_kv]
+    lengths = torch.randint(0, s_kv + 1, (s_q,), generator=g).int()
+    lengths[:4] = torch.tensor([0, 1, s_kv, 512])
+    got = topk_indices(wide.to(DEV)[:, :s_kv], topk, lengths.to(DEV)).cpu()
+    assert torch.equal(got, topk_indices_ref(sc, topk, lengths))
 
 
 def test_causal_lengths_feed_the_forward():
