@@ -204,7 +204,7 @@ def bench_topk_indices(args, dev, peaks):
     nbytes = s_q * (4 * s_kv + 4 * topk)
     return {"workload": f"topk_indices_sq{s_q}_skv{s_kv}_topk{topk}", "ms": ms, "iters": iters, "bytes": nbytes,
             "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_hbm_peak": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-            "bound": "hbm", "kernel": "topk_select_kernel", "l2": "scores (537 MB) larger than L2"}
+            "bound": "hbm", "kernel": "topk_select_rows_kernel", "l2": "scores (537 MB) larger than L2"}
 
 
 def bench_fp8_dense_peak(dev):

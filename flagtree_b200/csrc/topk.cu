@@ -171,7 +171,8 @@ constexpr int kPerThread = kRowMax / kBigThreads;          // 32 keys per thread
 constexpr int kSample = 256;
 constexpr int kSampleMinLen = 4096;                        // shorter rows are selected without a bracket
 constexpr int kListMax = 256;                              // a bin of at most this many keys is ranked by counting
-constexpr size_t kBigSmem = static_cast<size_t>(kRowMax) * 4 + 256 * 32 * 4 + 256 * 4 + kSample * 4 + kBigWarps * 4 + 16 * 4;
+constexpr size_t kBigSmem = static_cast<size_t>(kRowMax) * 4 + 256 * 32 * 4 + 256 * 4 + kSample * 4 + kBigWarps * 4 + 16 * 4 +
+                            2 * kBigThreads * 4 + 2 * kListMax * 4;
 
 enum { kCtlBin = 0, kCtlRemaining, kCtlBinCount, kCtlInside, kCtlAbove, kCtlLo, kCtlHi, kCtlListCount, kCtlThresh, kCtlNeedEq };
 
@@ -204,11 +205,14 @@ __global__ void __launch_bounds__(kBigThreads, 1) topk_select_rows_kernel(const 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* buf = reinterpret_cast<float*>(smem_raw);                                   // the row in flight
   int* hist = reinterpret_cast<int*>(smem_raw + static_cast<size_t>(kRowMax) * 4);   // [256 bins][32 lanes]
-  uint32_t* list = reinterpret_cast<uint32_t*>(hist);                                // [kListMax], after the passes
   int* bin_total = hist + 256 * 32;                                                  // [256]
   uint32_t* samp = reinterpret_cast<uint32_t*>(bin_total + 256);                     // [256]
   uint32_t* warp_sum = samp + kSample;                                               // [32]
   int* ctl = reinterpret_cast<int*>(warp_sum + kBigWarps);                           // [16]
+  uint32_t* gt_extra = reinterpret_cast<uint32_t*>(ctl + 16);                        // [1024] per owner thread: keys of
+  uint32_t* eq_extra = gt_extra + kBigThreads;                                       // [1024] the last bin above / equal
+  uint32_t* list = eq_extra + kBigThreads;                                           // [kListMax] keys of the last bin
+  int* list_pos = reinterpret_cast<int*>(list + kListMax);                           // [kListMax] and their positions
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int twist = tid & 7;
   const int pos0 = tid * kPerThread;
@@ -244,8 +248,8 @@ __global__ void __launch_bounds__(kBigThreads, 1) topk_select_rows_kernel(const 
     __syncthreads();
     if (row + static_cast<int>(gridDim.x) < p.s_q) fetch_row(p, row + gridDim.x, buf);   // overlaps the selection
 
-    uint32_t thresh = 0;
-    int need_eq = 0x7fffffff;                              // k == len: every position of the row is taken
+    uint32_t above_bits = 0, tie_bits = 0;                 // register order: keys above the last bin, ties of a one-key bin
+    int need_eq = 0;
     if (k < len) {
       if (sampled) {
         // rank of sample s among the 256: four threads count a quarter each
@@ -253,8 +257,8 @@ __global__ void __launch_bounds__(kBigThreads, 1) topk_select_rows_kernel(const 
         const uint32_t mine = samp[s_no];
         int rank = 0;
 #pragma unroll
-        for (int i = 0; i < kSample / 4; i += 4) {
-          const uint4 v = *reinterpret_cast<const uint4*>(samp + quarter * (kSample / 4) + i);
+        for (int m = 0; m < kSample / 16; ++m) {           // the four threads of a sample read different banks
+          const uint4 v = *reinterpret_cast<const uint4*>(samp + 16 * m + 4 * quarter);
           rank += (v.x > mine) + (v.y > mine) + (v.z > mine) + (v.w > mine);
         }
         rank += __shfl_xor_sync(0xffffffffu, rank, 1);
@@ -415,24 +419,31 @@ __global__ void __launch_bounds__(kBigThreads, 1) topk_select_rows_kernel(const 
         bin_count = ctl[kCtlBinCount];
         low_bits = shift;
       }
-      if (low_bits == 0) {
-        thresh = lo + prefix;
-        need_eq = remaining;
-        __syncthreads();                                   // ctl is rewritten by the next row
-      } else {
-        // the few keys of the bin, ranked by counting: the threshold is the key v with
-        // #{keys > v} < remaining <= #{keys >= v}
-        if (tid == 0) ctl[kCtlListCount] = 0;
-        __syncthreads();                                   // also: every thread is done reading the histogram
-        if (cand != 0) {
+      // the last bin [base, top]: keys above it are taken, its own few keys go to a list with their positions and
+      // are ranked by counting: the threshold is the key v with #{keys > v} < remaining <= #{keys >= v}
+      const uint32_t base = lo + prefix;
+      const uint32_t span = min(low_bits == 0 ? 0u : ((1u << low_bits) - 1u), hi - base);   // keys above H were counted apart
+      const uint32_t top = base + span;
+      gt_extra[tid] = 0u;
+      eq_extra[tid] = 0u;
+      if (tid == 0) ctl[kCtlListCount] = 0;
+      __syncthreads();
+      const uint32_t valid_reg = swap_nibbles(valid_pos, twist);
 #pragma unroll
-          for (int r = 0; r < kPerThread; ++r) {
-            if ((cand >> r) & 1u) {
-              const uint32_t rel = key[r] - lo;
-              if ((rel & mask) == prefix) list[atomicAdd(&ctl[kCtlListCount], 1)] = rel;
-            }
+      for (int r = 0; r < kPerThread; ++r) {
+        above_bits |= key[r] > top ? (1u << r) : 0u;
+        if (key[r] - base <= span && ((valid_reg >> r) & 1u)) {
+          if (low_bits == 0) {
+            tie_bits |= 1u << r;                           // the bin is one key wide: these are the ties
+          } else {
+            const int at = atomicAdd(&ctl[kCtlListCount], 1);
+            list[at] = key[r];
+            list_pos[at] = pos0 + 4 * ((r >> 2) ^ twist) + (r & 3);
           }
         }
+      }
+      need_eq = remaining;
+      if (low_bits != 0) {
         __syncthreads();
         const int n = ctl[kCtlListCount];
         if (tid < n) {
@@ -443,24 +454,27 @@ __global__ void __launch_bounds__(kBigThreads, 1) topk_select_rows_kernel(const 
             gt += o > v ? 1 : 0;
             ge += o >= v ? 1 : 0;
           }
-          if (gt < remaining && remaining <= ge) { ctl[kCtlThresh] = static_cast<int>(v); ctl[kCtlNeedEq] = remaining - gt; }
+          const int at = list_pos[tid];
+          if (gt < remaining) {
+            if (remaining <= ge) { atomicOr(&eq_extra[at >> 5], 1u << (at & 31)); ctl[kCtlNeedEq] = remaining - gt; }
+            else atomicOr(&gt_extra[at >> 5], 1u << (at & 31));
+          }
         }
         __syncthreads();
-        thresh = lo + static_cast<uint32_t>(ctl[kCtlThresh]);
         need_eq = ctl[kCtlNeedEq];
       }
+    } else {
+      // k == len: every position of the row is taken
+      above_bits = swap_nibbles(valid_pos, twist);
+      gt_extra[tid] = 0u;
+      eq_extra[tid] = 0u;
+      need_eq = 0;
     }
 
-    // per thread the keys above and equal to the threshold as bit masks in position order, one scan over the
-    // packed counts (equal << 16 | above; neither exceeds 32768), then each thread writes its few positions
-    uint32_t gt_bits = 0, eq_bits = 0;
-#pragma unroll
-    for (int r = 0; r < kPerThread; ++r) {
-      gt_bits |= key[r] > thresh ? (1u << r) : 0u;
-      eq_bits |= key[r] == thresh ? (1u << r) : 0u;
-    }
-    gt_bits = swap_nibbles(gt_bits, twist);
-    eq_bits = swap_nibbles(eq_bits, twist) & valid_pos;
+    // per thread the taken keys and the ties as bit masks in position order, one scan over the packed counts
+    // (ties << 16 | taken; neither exceeds 32768), then each thread writes its few positions
+    uint32_t gt_bits = swap_nibbles(above_bits, twist) | gt_extra[tid];
+    uint32_t eq_bits = (swap_nibbles(tie_bits, twist) | eq_extra[tid]) & valid_pos;
     const uint32_t packed = (static_cast<uint32_t>(__popc(eq_bits)) << 16) | static_cast<uint32_t>(__popc(gt_bits));
     uint32_t incl = packed;
 #pragma unroll

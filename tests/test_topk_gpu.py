@@ -52,6 +52,32 @@ def test_many_rows_with_causal_lengths_and_a_strided_view():
     assert torch.equal(got, topk_indices_ref(sc, topk, lengths))
 
 
+def test_long_rows_with_few_distinct_values_and_a_misleading_sample():
+    """Rows long enough for the sampled bracket: few distinct values (crowded bins, ties across many threads), a
+    constant row, a sorted row, and a row whose sampled positions hold values unlike the rest (the bracket is
+    rejected and the whole key range is searched)."""
+    g = torch.Generator().manual_seed(21)
+    s_kv, topk = 32768, 2048
+    rows = [torch.randint(-3, 4, (s_kv,), generator=g).float(),
+            torch.full((s_kv,), 2.5),
+            torch.arange(s_kv).float(),
+            -torch.arange(s_kv).float(),
+            torch.randn(s_kv, generator=g).mul(1e-30),                  # denormal-range keys
+            torch.randn(s_kv, generator=g)]
+    odd = torch.randn(s_kv, generator=g)
+    sample_at = (torch.arange(256) * s_kv >> 8) + (torch.arange(256) & 15)
+    odd[sample_at] = 1e6
+    rows.append(odd)
+    low = torch.randn(s_kv, generator=g)
+    low[sample_at] = -1e6
+    rows.append(low)
+    sc = torch.stack(rows)
+    lengths = torch.tensor([s_kv, s_kv, s_kv, s_kv, s_kv, 4096, s_kv, s_kv], dtype=torch.int32)
+    for k in (topk, 1, 32767):
+        got = topk_indices(sc.to(DEV), k, lengths.to(DEV)).cpu()
+        assert torch.equal(got, topk_indices_ref(sc, k, lengths)), k
+
+
 def test_causal_lengths_feed_the_forward():
     """The producer's output as the `indices` of the forward: causal lengths, scores = q.k of head 0."""
     g = torch.Generator().manual_seed(8)
