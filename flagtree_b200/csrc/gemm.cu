@@ -51,6 +51,9 @@ constexpr int MAX_TP = 8;
 struct Params {
   int m, n, k;
   int n_blocks, m_blocks, n_tiles;
+  // The tiles of the last, partial wave are cut into two halves of 128 columns each so that twice as many CTA
+  // groups share them: loop positions below n_full are whole tiles, the rest are halves (n_steps positions in all).
+  int n_full, n_steps;
   // plain GEMM output
   __nv_bfloat16* c;
   long long ldc;
@@ -140,6 +143,14 @@ __device__ __forceinline__ void tile_coords(const Params& p, int t, int cta, int
   m_blk = dst * p.blocks_per_shard + mg * NCTA + cta;
 }
 
+// Loop position -> tile number, first column of the tile that this step computes, and its width.
+struct Step { int tile, col_off, width; };
+__device__ __forceinline__ Step step_of(const Params& p, int pos) {
+  if (pos < p.n_full) return Step{pos, 0, BN};
+  const int r = pos - p.n_full;
+  return Step{p.n_full + (r >> 1), (r & 1) * (BN / 2), BN / 2};
+}
+
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
   unsigned int v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -168,7 +179,9 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 template <int NSRC>
 __device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long long slot,
                                                   __nv_bfloat16* orow, int n_blk, uint32_t full_bar, uint32_t parity,
-                                                  uint32_t tacc, volatile int* abort_flag, bool skip_reads) {
+                                                  uint32_t tacc, volatile int* abort_flag, bool skip_reads,
+                                                  int col_off, int width) {
+  const int col_base = n_blk * BN + col_off;          // first column of this step; `orow` points at it
   constexpr int NS = NSRC > 0 ? NSRC : 1;
   // Receive slots are stored as contiguous 4 KB boxes of [32 rows x 64 columns] in the staging
   // (128B-swizzled) order; `rrow` points at this thread's row inside box column 0 of its row group.
@@ -185,11 +198,11 @@ __device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long 
   uint4 bufA[NS][2], bufB[NS][2];
   auto fetch = [&](uint4 (&buf)[NS][2], int col) {
     if constexpr (NSRC > 0) {
-      if (!skip_reads && n_blk * BN + col < p.n) {
+      if (!skip_reads && col_base + col < p.n) {
 #pragma unroll
         for (int i = 0; i < NSRC; ++i) {
-          buf[i][0] = *reinterpret_cast<const uint4*>(src_ptr[i] + box_off(n_blk * BN + col));
-          buf[i][1] = *reinterpret_cast<const uint4*>(src_ptr[i] + box_off(n_blk * BN + col + 8));
+          buf[i][0] = *reinterpret_cast<const uint4*>(src_ptr[i] + box_off(col_base + col));
+          buf[i][1] = *reinterpret_cast<const uint4*>(src_ptr[i] + box_off(col_base + col + 8));
         }
       } else {
 #pragma unroll
@@ -215,12 +228,12 @@ __device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long 
           }
         }
       }
-    } else if (!skip_reads && n_blk * BN + col < p.n) {
+    } else if (!skip_reads && col_base + col < p.n) {
       for (int src = 0; src < p.tp; ++src) {
         if (src == p.rank) continue;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint4 w = *reinterpret_cast<const uint4*>(rrow + src * slot + box_off(n_blk * BN + col + h * 8));
+          const uint4 w = *reinterpret_cast<const uint4*>(rrow + src * slot + box_off(col_base + col + h * 8));
           const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
@@ -231,10 +244,10 @@ __device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long 
         }
       }
     }
-    if (n_blk * BN + col < p.n) {   // n is a multiple of 8 (and row blocks are full in this mode)
+    if (col_base + col < p.n) {   // n is a multiple of 8 (and row blocks are full in this mode)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        if (n_blk * BN + col + h * 8 < p.n) {
+        if (col_base + col + h * 8 < p.n) {
           uint4 o;
           o.x = pack_bf16x2(f[h * 8], f[h * 8 + 1]);
           o.y = pack_bf16x2(f[h * 8 + 2], f[h * 8 + 3]);
@@ -249,13 +262,13 @@ __device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long 
   mbar_wait(full_bar, parity, abort_flag);
   tc_fence_after();
 #pragma unroll 1
-  for (int c0 = 0; c0 < BN; c0 += 32) {
+  for (int c0 = 0; c0 < width; c0 += 32) {
     fetch(bufB, c0 + 16);
     uint32_t v[32];
     tmem_ld32(tacc + c0, v);
     tmem_wait_ld();
     finish(v, bufA, c0);
-    if (c0 + 32 < BN) fetch(bufA, c0 + 32);
+    if (c0 + 32 < width) fetch(bufA, c0 + 32);
     finish(v + 16, bufB, c0 + 16);
   }
 }
@@ -331,9 +344,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // ------------------------------------------------------------------ TMA producer (every CTA)
     if (lane == 0) {
       uint32_t it = 0;
-      for (int t = group; t < p.n_tiles; t += n_groups) {
+      for (int pos = group; pos < p.n_steps; pos += n_groups) {
+        const Step stp = step_of(p, pos);
         int m_blk, n_blk, dst;
-        tile_coords<NCTA, PULL>(p, t, cta, m_blk, n_blk, dst);
+        tile_coords<NCTA, PULL>(p, stp.tile, cta, m_blk, n_blk, dst);
+        const int b_blocks = stp.width / 64 / NCTA;          // 64-column blocks of B this CTA loads per stage
+        const int b_col0 = n_blk * BN + stp.col_off + cta * b_blocks * 64;
+        const uint32_t stage_tx = A_BYTES + b_blocks * B_BLOCK_BYTES;
         if (p.ag_flags != nullptr && ld_acquire_sys(p.ag_flags + dst) < p.epoch && !*abort_flag) {
           // all-gather: the rows of this tile come from rank dst; wait (bounded) until its copy has landed
           const long long t0 = clock64();
@@ -351,20 +368,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           const uint32_t a_dst = base + s * STAGE_BYTES;
           if constexpr (NCTA == 1) {
             const uint32_t full = smem_u32(&bars->full[s]);
-            mbar_arrive_expect_tx(full, STAGE_BYTES);
+            mbar_arrive_expect_tx(full, stage_tx);
             tma_load_2d(a_dst, &tm_a, full, kb * BK, m_blk * BM);
 #pragma unroll
             for (int j = 0; j < C::B_BLOCKS; ++j)
-              tma_load_2d(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full, n_blk * BN + j * 64, kb * BK);
+              if (j < b_blocks) tma_load_2d(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full, b_col0 + j * 64, kb * BK);
           } else {
             // Both CTAs' loads are counted on the even CTA's barrier; that CTA announces the total.
             const uint32_t full0 = mapa_shared(smem_u32(&bars->full[s]), 0);
-            if (cta == 0) mbar_arrive_expect_tx(smem_u32(&bars->full[s]), 2 * STAGE_BYTES);
+            if (cta == 0) mbar_arrive_expect_tx(smem_u32(&bars->full[s]), 2 * stage_tx);
             tma_load_2d_pair(a_dst, &tm_a, full0, kb * BK, m_blk * BM);
 #pragma unroll
             for (int j = 0; j < C::B_BLOCKS; ++j)
-              tma_load_2d_pair(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full0,
-                               n_blk * BN + (cta * C::B_BLOCKS + j) * 64, kb * BK);
+              if (j < b_blocks) tma_load_2d_pair(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full0, b_col0 + j * 64, kb * BK);
           }
         }
       }
@@ -374,7 +390,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     // The whole warp runs the loop and waits; an elected lane (always the same one, so that its commits cover
     // its MMAs) issues.  Descriptors: only the low word (address) changes, by constants per k step.
     if (cta == 0) {
-      constexpr uint32_t kIdesc = umma_idesc(kFmtBF16, BM * NCTA, BN, 0, 1);
+      constexpr uint32_t kIdescFull = umma_idesc(kFmtBF16, BM * NCTA, BN, 0, 1);
+      constexpr uint32_t kIdescHalf = umma_idesc(kFmtBF16, BM * NCTA, BN / 2, 0, 1);
       const uint64_t ad0 = smem_desc_sw128(base, 16, 1024);
       const uint64_t bd0 = smem_desc_sw128(base + A_BYTES, B_BLOCK_BYTES, 1024);
       const uint32_t ad_lo0 = static_cast<uint32_t>(ad0), ad_hi = static_cast<uint32_t>(ad0 >> 32);
@@ -385,7 +402,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const uint32_t accf_own = NCTA == 1 ? smem_u32(&bars->acc_full[0]) : mapa_shared(smem_u32(&bars->acc_full[0]), 0);
       const uint32_t accf_peer = NCTA == 1 ? 0u : mapa_shared(smem_u32(&bars->acc_full[0]), 1);
       uint32_t s = 0, ph = 0, local = 0;     // stage and its phase bit, tiles done by this group
-      for (int t = group; t < p.n_tiles; t += n_groups, ++local) {
+      for (int pos = group; pos < p.n_steps; pos += n_groups, ++local) {
+        const uint32_t kIdesc = pos < p.n_full ? kIdescFull : kIdescHalf;
         const uint32_t acc = local & 1u;
         mbar_wait(smem_u32(&bars->acc_empty[acc]), ((local >> 1) & 1u) ^ 1u, abort_flag);
         tc_fence_after();
@@ -435,6 +453,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     uint32_t local = 0, box_it = 0;
     unsigned int* pending_flag = nullptr;            // lane 0: counter of the last remote tile, not yet released
     int ce_pending = -1;                             // lane 0, copy-engine exchange: row shard of the tile stored last, not yet counted
+    unsigned int ce_weight = 0;                      // what that tile counts: 2 for a whole tile, 1 for a half
     // the accumulator-free barrier the MMA issuer waits on lives in the even CTA
     const uint32_t acc_empty_addr[2] = {
         NCTA == 1 ? smem_u32(&bars->acc_empty[0]) : mapa_shared(smem_u32(&bars->acc_empty[0]), 0),
@@ -443,9 +462,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       if constexpr (NCTA == 1) mbar_arrive(acc_empty_addr[a]);
       else mbar_arrive_cluster(acc_empty_addr[a]);
     };
-    for (int t = group; t < p.n_tiles; t += n_groups, ++local) {
+    for (int pos = group; pos < p.n_steps; pos += n_groups, ++local) {
+      const Step stp = step_of(p, pos);
       int m_blk, n_blk, dst;
-      tile_coords<NCTA, PULL>(p, t, cta, m_blk, n_blk, dst);
+      tile_coords<NCTA, PULL>(p, stp.tile, cta, m_blk, n_blk, dst);
       const uint32_t acc = local & 1u;
       const int row = m_blk * BM + lg * 32 + lane;
       const bool ag = !PULL && p.ag_flags != nullptr;
@@ -597,17 +617,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();
       } else if (!PULL && !ce && p.tp > 1) {
         const int rl = row - dst * p.shard_rows;
-        __nv_bfloat16* orow = p.out + static_cast<long long>(rl) * p.ldo + n_blk * BN;
+        __nv_bfloat16* orow = p.out + static_cast<long long>(rl) * p.ldo + n_blk * BN + stp.col_off;
         const long long slot = static_cast<long long>(p.shard_rows) * p.n;
         const uint32_t full_bar = smem_u32(&bars->acc_full[acc]);
         const uint32_t par = (local >> 1) & 1u;
         const uint32_t tacc = tmem_addr(tmem, lg * 32, acc * BN);
         const bool skip = false;
         switch (p.tp) {
-          case 2: own_tile_epilogue<1>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
-          case 4: own_tile_epilogue<3>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
-          case 8: own_tile_epilogue<7>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
-          default: own_tile_epilogue<0>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip); break;
+          case 2: own_tile_epilogue<1>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width); break;
+          case 4: own_tile_epilogue<3>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width); break;
+          case 8: own_tile_epilogue<7>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width); break;
+          default: own_tile_epilogue<0>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width); break;
         }
         tc_fence_before();
         __syncwarp();
@@ -621,22 +641,22 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           // the stores of a tile cost the GEMM a quarter of its time); the copy engine and the stream wait read
           // through L2, so device scope is enough.  The last count of a shard publishes "shard complete".
           __threadfence();
-          const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, 1u) + 1u;
+          const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, ce_weight) + ce_weight;
           if (cnt == p.ce_target) st_release_sys(p.ce_ready + ce_pending, p.epoch);
           ce_pending = -1;
         }
         __syncwarp();                  // the tensor-memory loads below are warp-collective
-        __nv_bfloat16* orow = p.c + static_cast<long long>(row) * p.ldc + n_blk * BN;
+        __nv_bfloat16* orow = p.c + static_cast<long long>(row) * p.ldc + n_blk * BN + stp.col_off;
         const bool row_ok = row < p.m;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c0 = 0; c0 < stp.width; c0 += 32) {
           uint32_t v[32];
           tmem_ld32(tmem_addr(tmem, lg * 32, acc * BN + c0), v);
           tmem_wait_ld();
           if (row_ok) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
-              const int col = n_blk * BN + c0 + j;
+              const int col = n_blk * BN + stp.col_off + c0 + j;
               if (col < p.n) {   // n is a multiple of 8
                 uint4 o;
                 o.x = pack_bf16x2(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
@@ -652,13 +672,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();                  // orders the 32 lanes' stores before lane 0's fence one tile later
         if (lane == 0) {
           release_acc(acc);
-          if (ce && !ag) ce_pending = dst;    // counted one tile late, see above
+          if (ce && !ag) { ce_pending = dst; ce_weight = stp.width == BN ? 2u : 1u; }   // counted one tile late, see above
         }
       }
     }
     if (lane == 0 && ce_pending >= 0) {
       __threadfence();
-      const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, 1u) + 1u;
+      const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, ce_weight) + ce_weight;
       if (cnt == p.ce_target) st_release_sys(p.ce_ready + ce_pending, p.epoch);
     }
     if (lane == 0) {
@@ -790,7 +810,18 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b, cons
   // grid never exceeds one CTA per SM, which this kernel's shared-memory footprint already enforces.
   const int groups = p.n_tiles < max_groups ? p.n_tiles : max_groups;
   cfg.gridDim = dim3(NCTA * groups);
-  e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, p);
+  // Tiles left over after the whole waves: when at most half of the groups would have one, each is cut into two
+  // halves of 128 columns.  The push protocol sends whole tiles only, so there the leftover must lie in the
+  // rank's own row shard (the last tiles of the order); the pull protocol keeps whole tiles.
+  gemm::Params q = p;
+  const int left = p.n_tiles % groups;
+  const bool push = p.tp > 1 && p.ce_ready == nullptr && p.ag_flags == nullptr;
+  static const int no_split = getenv("FTB_GEMM_NO_SPLIT") ? atoi(getenv("FTB_GEMM_NO_SPLIT")) : 0;
+  const bool split = !PULL && !no_split && p.n_tiles > groups && left > 0 && 2 * left <= groups &&
+                     (!push || left <= p.n_tiles / p.tp);
+  q.n_full = split ? p.n_tiles - left : p.n_tiles;
+  q.n_steps = q.n_full + 2 * (p.n_tiles - q.n_full);
+  e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, q);
   return check_cuda(e, "gemm launch");
 }
 
@@ -1242,7 +1273,7 @@ static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b,
   p.counter = c->d_ce_counter;
   for (int i = 0; i < tp; ++i) p.flags[i] = c->flags[i];
   const int n_blocks = (c->n + gemm::BN - 1) / gemm::BN;
-  p.ce_target = epoch * static_cast<unsigned int>(c->blocks_per_shard) * static_cast<unsigned int>(n_blocks) * 4u;
+  p.ce_target = epoch * static_cast<unsigned int>(c->blocks_per_shard) * static_cast<unsigned int>(n_blocks) * 8u;   // 4 epilogue warps per tile and row block, a whole tile counts 2
   int rc = launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
   if (rc != FTB_OK) return rc;
   // ---- exchange on the second stream, destination after destination in the order in which the shards complete

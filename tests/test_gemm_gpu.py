@@ -33,6 +33,18 @@ def test_matmul_shapes(m, n, k):
     _check(a, b, f"{m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("m,n,k", [(4096, 4864, 256), (2048, 9992, 128), (3072, 2560, 192)])
+def test_leftover_tiles_run_as_half_width_steps(m, n, k):
+    """Shapes whose tile count leaves a few tiles after the whole waves of a 148-SM GPU: 304 = 4 x 74 + 8 pair
+    tiles; 320 = 4 x 74 + 24 with a last column block of 8 columns; 120 = 74 + 46 (too many left to halve).  The
+    leftover runs as 128-column halves where that helps, and every element must still be the product."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    b = torch.randn(k, n, generator=g).bfloat16()
+    c = _check(a, b, f"{m}x{n}x{k}")
+    assert torch.equal(c, matmul(a.to(DEV), b.to(DEV)))
+
+
 def test_matmul_powers_of_two_exact():
     """Inputs 2^randint(-3,0) as in test_matmul.py:164-176; K=64 keeps every fp32 partial sum exact,
     so the result must equal the fp32 product rounded to bf16 bit for bit."""
