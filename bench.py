@@ -443,6 +443,13 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def _progress(msg):
+    """A line on stderr per finished section when FTB_BENCH_PROGRESS is set (stdout carries the one JSON line)."""
+    if os.environ.get("FTB_BENCH_PROGRESS"):
+        torch.cuda.synchronize()
+        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -533,6 +540,7 @@ def main():
 
     # ---- strong scaling: ONE cfg2 batch (rank 0's) split over the ranks, tokens dealt round-robin so that the
     # short early tokens of the causal batch are spread evenly; same kernel, max over ranks
+    _progress("headline done")
     strong = None
     if world > 1 and args.s_q == 4096:
         c0 = W.mla_cfg2(device=dev, s_q=4096, s_kv=4096, h=128, topk=2048, rank=0)
@@ -552,6 +560,7 @@ def main():
         del sq, sidx, so, sl
 
     # ---- end-to-end through the public API with host buffers (pinned), copies inside the timed region
+    _progress("strong scaling done")
     e2e = None
     if not args.no_e2e:
         hq = case.q.cpu().pin_memory()
@@ -609,6 +618,7 @@ def main():
                "note": "the step is bound by the host link: the floor is the same bytes copied both ways at once with no kernel"}
         del hq, hkv, hidx, hout, hlse
 
+    _progress("e2e done")
     decode_fp8 = kv_write = topk_b = None
     if world == 1 and not args.no_decode:
         decode_fp8 = bench_mla_decode_fp8(args, dev, peaks)
@@ -619,12 +629,15 @@ def main():
     gemm_rs = gemm_rs_fp8 = fp8_peak = ag = None
     if not args.no_gemm:
         gemm_rs = bench_gemm_rs(args, dev, rank, world, dist, peaks)
+        _progress("gemm_rs done")
         if world > 1:
             ag = bench_ag_gemm(args, dev, rank, world, dist, peaks)
+            _progress("ag_gemm done")
         if not args.no_fp8_sweep:
             if world == 1:
                 fp8_peak = bench_fp8_dense_peak(dev)
             gemm_rs_fp8 = bench_gemm_rs_fp8(args, dev, rank, world, dist, peaks)
+            _progress("gemm_rs_fp8 done")
             if fp8_peak is not None:
                 gemm_rs_fp8["fp8_dense_peak"] = fp8_peak
 

@@ -73,11 +73,16 @@ struct Params {
   long long wait_limit;              // cycles after which a wait for another rank gives up (status = timeout)
   // copy-engine exchange: every tile is stored into the local partial (c / ldc); when the last tile of a row
   // shard has been stored its word in ce_ready takes the call number, which a stream memory operation waits for
-  unsigned int* ce_ready;            // [tp] (NULL = another protocol)
-  unsigned int* ce_cnt;              // [tp] epilogue-warp arrivals per row shard, monotonic over calls
-  unsigned int ce_target;            // value ce_cnt[d] reaches in this call
+  // Row shards leave in ce_chunks pieces of consecutive row blocks each (words [d * ce_chunks + piece]); the peers'
+  // pieces of this rank's own rows arrive in its receive slots (row-major [tp][shard_rows][n]) with a flag per
+  // (source, piece), and the epilogue of the own rows, which come last, adds them: no separate reduce pass.
+  unsigned int* ce_ready;            // [tp * ce_chunks] (NULL = another protocol)
+  unsigned int* ce_cnt;              // [tp * ce_chunks] epilogue-warp arrivals per piece, monotonic over calls
+  unsigned int ce_target;            // value ce_cnt[] reaches in this call
+  int ce_chunks;
   // all-gather + GEMM: the rows of A arrive shard by shard (copy engines of the peers); ag_flags[src] takes the
-  // call number once rank src's shard is in place.  NULL = A is complete at launch.
+  // call number once rank src's shard is in place.  NULL = A is complete at launch.  The rank's own rows are read
+  // from the caller's shard through a tensor map of their own (no copy, no wait).
   const unsigned int* ag_flags;
 };
 
@@ -180,15 +185,18 @@ template <int NSRC>
 __device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long long slot,
                                                   __nv_bfloat16* orow, int n_blk, uint32_t full_bar, uint32_t parity,
                                                   uint32_t tacc, volatile int* abort_flag, bool skip_reads,
-                                                  int col_off, int width) {
+                                                  int col_off, int width, bool row_major) {
   const int col_base = n_blk * BN + col_off;          // first column of this step; `orow` points at it
   constexpr int NS = NSRC > 0 ? NSRC : 1;
   // Receive slots are stored as contiguous 4 KB boxes of [32 rows x 64 columns] in the staging
   // (128B-swizzled) order; `rrow` points at this thread's row inside box column 0 of its row group.
-  const __nv_bfloat16* rrow = p.recv[p.rank] + static_cast<long long>(rl >> 5) * (p.n >> 6) * 2048 + (rl & 31) * 64;
+  // With the copy-engine exchange the slots are plain row-major [shard_rows][n].
+  const __nv_bfloat16* rrow = row_major ? p.recv[p.rank] + static_cast<long long>(rl) * p.n
+                                        : p.recv[p.rank] + static_cast<long long>(rl >> 5) * (p.n >> 6) * 2048 + (rl & 31) * 64;
   const int sw = rl & 7;
   auto box_off = [&](int col) -> long long {   // element offset of 8 columns starting at absolute column `col`
-    return static_cast<long long>(col >> 6) * 2048 + ((((col & 63) >> 3) ^ sw) << 3);
+    return row_major ? static_cast<long long>(col)
+                     : static_cast<long long>(col >> 6) * 2048 + ((((col & 63) >> 3) ^ sw) << 3);
   };
   const __nv_bfloat16* src_ptr[NS];
   if constexpr (NSRC > 0) {
@@ -259,7 +267,7 @@ __device__ __forceinline__ void own_tile_epilogue(const Params& p, int rl, long 
     }
   };
   fetch(bufA, 0);
-  mbar_wait(full_bar, parity, abort_flag);
+  if (!__all_sync(0xffffffffu, mbar_wait(full_bar, parity, abort_flag))) return;   // a wait ran out: the tile is not written
   tc_fence_after();
 #pragma unroll 1
   for (int c0 = 0; c0 < width; c0 += 32) {
@@ -283,7 +291,8 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) 
 
 template <int NCTA, bool PULL>
 __global__ void __launch_bounds__(PULL ? THREADS_PULL : THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const __grid_constant__ CUtensorMap tm_a_own, const Params p) {
   using C = Cfg<NCTA>;
   constexpr int STAGES = C::STAGES;
   constexpr int STAGE_BYTES = C::STAGE_BYTES;
@@ -315,6 +324,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     }
     fence_mbar_init();
     tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_a_own);
     tma_prefetch_desc(&tm_b);
   }
   __syncthreads();
@@ -322,7 +332,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   // launch failed, so both CTAs of a pair take the same branch here.
   if (bars->abort_flag) {
     // copy-engine exchange: the second stream waits for the ready words whatever became of this launch
-    if (p.ce_ready != nullptr && blockIdx.x == 0 && tid < p.tp) st_release_sys(p.ce_ready + tid, p.epoch);
+    if (p.ce_ready != nullptr && blockIdx.x == 0 && tid < p.tp * p.ce_chunks) st_release_sys(p.ce_ready + tid, p.epoch);
     return;   // (an all-gather launch that leaves here does not release the peers: the context is dead)
   }
   if (warp == 1) {
@@ -351,7 +361,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int b_blocks = stp.width / 64 / NCTA;          // 64-column blocks of B this CTA loads per stage
         const int b_col0 = n_blk * BN + stp.col_off + cta * b_blocks * 64;
         const uint32_t stage_tx = A_BYTES + b_blocks * B_BLOCK_BYTES;
-        if (p.ag_flags != nullptr && ld_acquire_sys(p.ag_flags + dst) < p.epoch && !*abort_flag) {
+        const bool own_rows = p.ag_flags != nullptr && dst == p.rank;
+        const CUtensorMap* ta = own_rows ? &tm_a_own : &tm_a;
+        const int a_row0 = own_rows ? m_blk * BM - p.rank * p.shard_rows : m_blk * BM;
+        if (p.ag_flags != nullptr && !own_rows && ld_acquire_sys(p.ag_flags + dst) < p.epoch && !*abort_flag) {
           // all-gather: the rows of this tile come from rank dst; wait (bounded) until its copy has landed
           const long long t0 = clock64();
           while (ld_acquire_sys(p.ag_flags + dst) < p.epoch) {
@@ -359,17 +372,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if (clock64() - t0 > p.wait_limit) { *abort_flag = 1; break; }
             __nanosleep(200);
           }
-          asm volatile("fence.proxy.async;" ::: "memory");   // the copy was seen through the generic proxy, the loads below use the async one
         }
+        // the copy was seen through the generic proxy, the loads below use the async one
+        if (p.ag_flags != nullptr) asm volatile("fence.proxy.async;" ::: "memory");
+        if (*abort_flag) break;                              // a wait ran out: nothing more is loaded
         for (int kb = 0; kb < kb_total; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag);
+          if (!mbar_wait(smem_u32(&bars->empty[s]), ph ^ 1u, abort_flag)) break;
           const uint32_t a_dst = base + s * STAGE_BYTES;
           if constexpr (NCTA == 1) {
             const uint32_t full = smem_u32(&bars->full[s]);
             mbar_arrive_expect_tx(full, stage_tx);
-            tma_load_2d(a_dst, &tm_a, full, kb * BK, m_blk * BM);
+            tma_load_2d(a_dst, ta, full, kb * BK, a_row0);
 #pragma unroll
             for (int j = 0; j < C::B_BLOCKS; ++j)
               if (j < b_blocks) tma_load_2d(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full, b_col0 + j * 64, kb * BK);
@@ -377,7 +392,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // Both CTAs' loads are counted on the even CTA's barrier; that CTA announces the total.
             const uint32_t full0 = mapa_shared(smem_u32(&bars->full[s]), 0);
             if (cta == 0) mbar_arrive_expect_tx(smem_u32(&bars->full[s]), 2 * stage_tx);
-            tma_load_2d_pair(a_dst, &tm_a, full0, kb * BK, m_blk * BM);
+            tma_load_2d_pair(a_dst, ta, full0, kb * BK, a_row0);
 #pragma unroll
             for (int j = 0; j < C::B_BLOCKS; ++j)
               if (j < b_blocks) tma_load_2d_pair(a_dst + A_BYTES + j * B_BLOCK_BYTES, &tm_b, full0, b_col0 + j * 64, kb * BK);
@@ -405,11 +420,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       for (int pos = group; pos < p.n_steps; pos += n_groups, ++local) {
         const uint32_t kIdesc = pos < p.n_full ? kIdescFull : kIdescHalf;
         const uint32_t acc = local & 1u;
-        mbar_wait(smem_u32(&bars->acc_empty[acc]), ((local >> 1) & 1u) ^ 1u, abort_flag);
+        // a wait that ran out ends the loop for the whole warp: no more MMAs
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_empty[acc]), ((local >> 1) & 1u) ^ 1u, abort_flag))) break;
         tc_fence_after();
         const uint32_t d = tmem + acc * BN;
+        bool live = true;
         for (int kb = 0; kb < kb_total; ++kb) {
-          mbar_wait(full0 + s * 8, ph, abort_flag);
+          if (!__all_sync(0xffffffffu, mbar_wait(full0 + s * 8, ph, abort_flag))) { live = false; break; }
           tc_fence_after();
           const uint32_t a_lo = ad_lo0 + ((s * STAGE_BYTES) >> 4);
           const uint32_t b_lo = bd_lo0 + ((s * STAGE_BYTES) >> 4);
@@ -435,6 +452,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           __syncwarp();
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
+        if (!live) break;
         if (elect_one()) {
           if constexpr (NCTA == 1) {
             umma_commit(accf_own + acc * 8);
@@ -469,8 +487,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const uint32_t acc = local & 1u;
       const int row = m_blk * BM + lg * 32 + lane;
       const bool ag = !PULL && p.ag_flags != nullptr;
-      const bool ce = !PULL && (p.ce_ready != nullptr || ag);      // both store every tile plainly into c
-      const bool remote = !PULL && !ce && p.tp > 1 && dst != p.rank;
+      const bool ce_own = !PULL && p.ce_ready != nullptr && dst == p.rank;   // copy-engine exchange, own rows: reduced here
+      const bool ce = !PULL && !ce_own && (p.ce_ready != nullptr || ag);    // tiles stored plainly into c
+      const bool remote = !PULL && !ce && !ce_own && p.tp > 1 && dst != p.rank;
+      const int blk_in_shard = m_blk - dst * p.blocks_per_shard;
+      const int piece = p.ce_ready != nullptr ? blk_in_shard * p.ce_chunks / p.blocks_per_shard : 0;
       if constexpr (PULL) {
         // Before overwriting a row block of the partial buffer make sure its owner has fetched the
         // previous call's sum (the owner's done[] word in this rank's flag buffer).
@@ -510,13 +531,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             red_release_sys_add(pending_flag, 1u);
             pending_flag = nullptr;
           }
+          if (ce_pending >= 0) {
+            __threadfence();
+            const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, ce_weight) + ce_weight;
+            if (cnt == p.ce_target) st_release_sys(p.ce_ready + ce_pending, p.epoch);
+            ce_pending = -1;
+          }
           const int blk = m_blk - dst * p.blocks_per_shard;
+          // push: a counter per (source, row block) that reaches flag_target; copy engines: a word per
+          // (source, piece) that takes the call number
+          const int words_per_src = ce_own ? p.ce_chunks : p.blocks_per_shard;
+          const int word = ce_own ? piece : blk;
+          const unsigned int want = ce_own ? p.epoch : p.flag_target;
           for (int src = 0; src < p.tp; ++src) {
             if (src == p.rank) continue;
-            const unsigned int* f = p.flags[p.rank] + src * p.blocks_per_shard + blk;
-            if (ld_acquire_sys(f) < p.flag_target && !*abort_flag) {
+            const unsigned int* f = p.flags[p.rank] + src * words_per_src + word;
+            if (ld_acquire_sys(f) < want && !*abort_flag) {
               const long long t0 = clock64();
-              while (ld_acquire_sys(f) < p.flag_target) {
+              while (ld_acquire_sys(f) < want) {
                 if (*abort_flag) break;
                 if (clock64() - t0 > p.wait_limit) { *abort_flag = 1; break; }
               }
@@ -527,7 +559,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       }
       if constexpr (PULL) {
         // partial tile -> this rank's own symmetric buffer (row-major [m, n] bf16), then count the row block
-        mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag))) break;   // a wait ran out
         tc_fence_after();
         __nv_bfloat16* orow = p.recv[p.rank] + static_cast<long long>(row) * p.n + n_blk * BN;
 #pragma unroll 1
@@ -562,7 +594,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         __syncwarp();
       } else if (remote) {
-        mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag))) break;   // a wait ran out
         tc_fence_after();
         // Drain the accumulator into registers as packed bf16 and hand the TMEM buffer back at once,
         // so that a slow link only delays this warp's stores, not the MMAs of the next tiles.
@@ -624,16 +656,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const uint32_t tacc = tmem_addr(tmem, lg * 32, acc * BN);
         const bool skip = false;
         switch (p.tp) {
-          case 2: own_tile_epilogue<1>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width); break;
-          case 4: own_tile_epilogue<3>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width); break;
-          case 8: own_tile_epilogue<7>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width); break;
-          default: own_tile_epilogue<0>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width); break;
+          case 2: own_tile_epilogue<1>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width, ce_own); break;
+          case 4: own_tile_epilogue<3>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width, ce_own); break;
+          case 8: own_tile_epilogue<7>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width, ce_own); break;
+          default: own_tile_epilogue<0>(p, rl, slot, orow, n_blk, full_bar, par, tacc, abort_flag, skip, stp.col_off, stp.width, ce_own); break;
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) release_acc(acc);
       } else if (!PULL) {
-        mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag);
+        if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag))) break;   // a wait ran out
         tc_fence_after();
         if (ce && lane == 0 && ce_pending >= 0) {
           // Copy-engine exchange: count the tile stored BEFORE this one for its row shard.  Its stores left a
@@ -672,7 +704,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         __syncwarp();                  // orders the 32 lanes' stores before lane 0's fence one tile later
         if (lane == 0) {
           release_acc(acc);
-          if (ce && !ag) { ce_pending = dst; ce_weight = stp.width == BN ? 2u : 1u; }   // counted one tile late, see above
+          if (ce && !ag) { ce_pending = dst * p.ce_chunks + piece; ce_weight = stp.width == BN ? 2u : 1u; }   // counted one tile late, see above
         }
       }
     }
@@ -739,6 +771,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 
   tc_fence_before();
   __syncthreads();
+  if (bars->abort_flag) {
+    // A wait ran out somewhere in this CTA.  Loads that were already issued still land in this CTA's shared memory
+    // and MMAs already issued still read it: give them time (bounded) before the CTA may leave.
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    // copy-engine exchange: the second stream waits for the ready words whatever became of this launch
+    if (p.ce_ready != nullptr && tid < p.tp * p.ce_chunks) st_release_sys(p.ce_ready + tid, p.epoch);
+  }
   if constexpr (NCTA == 2) cluster_sync_all();   // no CTA leaves while its peer may still signal or read it
   if (warp == 1) {
     tc_fence_after();
@@ -757,7 +796,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // all-gather: every peer may overwrite its shard in this rank's gather buffer
         for (int peer = 0; peer < p.tp; ++peer) st_release_sys(p.flags[peer] + p.tp + p.rank, p.epoch);
       } else if (p.ce_ready != nullptr) {
-        st_release_sys(p.flags[p.rank] + p.rank, p.epoch);
+        // copy-engine exchange: the peers' pieces in this rank's receive slots have been read
+        for (int peer = 0; peer < p.tp; ++peer) st_release_sys(p.flags[peer] + p.tp * p.ce_chunks + p.rank, p.epoch);
       } else {
         for (int peer = 0; peer < p.tp; ++peer)
           st_release_sys(p.flags[peer] + p.tp * p.blocks_per_shard + p.rank, p.epoch);
@@ -783,7 +823,8 @@ static StreamValue32Fn get_stream_memop(const char* name) {
 }
 
 template <int NCTA, bool PULL>
-static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const gemm::Params& p, int sms, cudaStream_t st) {
+static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const CUtensorMap& tm_a_own, const gemm::Params& p, int sms,
+                          cudaStream_t st) {
   auto kern = gemm::gemm_bf16_kernel<NCTA, PULL>;
   constexpr int smem = gemm::Cfg<NCTA>::SMEM_BYTES;
   constexpr int threads = PULL ? gemm::THREADS_PULL : gemm::THREADS;
@@ -821,7 +862,7 @@ static int launch_variant(const CUtensorMap& tm_a, const CUtensorMap& tm_b, cons
                      (!push || left <= p.n_tiles / p.tp);
   q.n_full = split ? p.n_tiles - left : p.n_tiles;
   q.n_steps = q.n_full + 2 * (p.n_tiles - q.n_full);
-  e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, q);
+  e = cudaLaunchKernelEx(&cfg, kern, tm_a, tm_b, tm_a_own, q);
   return check_cuda(e, "gemm launch");
 }
 
@@ -835,14 +876,21 @@ static int gemm_operands_ok(const void* a, const void* b, int m, int n, int k, l
   return FTB_OK;
 }
 
+// `a_own` (all-gather + GEMM only): the rank's own row shard [rows_own, k], read in place of its rows of `a`.
 static int launch_gemm(const void* a, const void* b, int m, int n, int k, long long lda, long long ldb,
-                       gemm::Params& p, cudaStream_t st) {
+                       gemm::Params& p, cudaStream_t st, const void* a_own = nullptr, int rows_own = 0, long long lda_own = 0) {
   const int ok = gemm_operands_ok(a, b, m, n, k, lda, ldb);
   if (ok != FTB_OK) return ok;
-  CUtensorMap tm_a, tm_b;
+  CUtensorMap tm_a, tm_b, tm_a_own;
   if (!make_tmap_2d(&tm_a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, m, k, lda, gemm::BM, gemm::BK) ||
       !make_tmap_2d(&tm_b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k, n, ldb, gemm::BK, 64)) {
     set_last_error("gemm: cuTensorMapEncodeTiled failed");
+    return FTB_ERR_CUDA;
+  }
+  if (a_own == nullptr) {
+    tm_a_own = tm_a;
+  } else if (!make_tmap_2d(&tm_a_own, a_own, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_own, k, lda_own, gemm::BM, gemm::BK)) {
+    set_last_error("gemm: cuTensorMapEncodeTiled failed (own shard)");
     return FTB_ERR_CUDA;
   }
   p.m = m; p.n = n; p.k = k;
@@ -857,8 +905,8 @@ static int launch_gemm(const void* a, const void* b, int m, int n, int k, long l
   if (force == 1 || force == 2) ncta = (force == 2 && p.tp > 1 && (p.blocks_per_shard % 2)) ? 1 : force;
   const bool pull = p.tp > 1 && p.mc_part != nullptr;
   p.n_tiles = ((p.m_blocks + ncta - 1) / ncta) * p.n_blocks;
-  if (ncta == 2) return pull ? launch_variant<2, true>(tm_a, tm_b, p, sms, st) : launch_variant<2, false>(tm_a, tm_b, p, sms, st);
-  return pull ? launch_variant<1, true>(tm_a, tm_b, p, sms, st) : launch_variant<1, false>(tm_a, tm_b, p, sms, st);
+  if (ncta == 2) return pull ? launch_variant<2, true>(tm_a, tm_b, tm_a_own, p, sms, st) : launch_variant<2, false>(tm_a, tm_b, tm_a_own, p, sms, st);
+  return pull ? launch_variant<1, true>(tm_a, tm_b, tm_a_own, p, sms, st) : launch_variant<1, false>(tm_a, tm_b, tm_a_own, p, sms, st);
 }
 
 extern "C" FTB_API int ftb_gemm_bf16(const ftb_gemm_args* g, void* stream) {
@@ -884,14 +932,15 @@ struct ftb_gemm_rs_ctx {
   unsigned int* d_blk_counter;   // pull mode: arrivals per 128-row block
   void* mc_recv;                 // multicast address of the receive/partial buffers (NULL = push mode)
   unsigned int epoch;
-  int form;                      // 0 = not used yet, 1 = fused bf16 calls, 2 = staged calls (bf16 or FP8): the flag words differ
+  int form;                      // 0 = not used yet, 1 = fused bf16 calls, 2 = staged calls (bf16 or FP8), 3 = copy-engine calls: the flag words differ
   int staged;                    // bf16 calls: 0 = fused kernel (push or pull), 1 = staged (GEMM per shard group + one reduce)
   long long wait_limit;          // cycles a device-side wait for another rank may last
   // copy-engine exchange
   int copy_engine;               // bf16 calls: the exchange runs on the copy engines beside the GEMM
+  int ce_chunks;                 // pieces a row shard leaves in
   void* part;                    // this rank's partial product [m, n] bf16 (local memory)
-  unsigned int* d_ready;         // [tp] "shard d of the partial is complete" (call number)
-  unsigned int* d_shard_cnt;     // [tp]
+  unsigned int* d_ready;         // [tp * ce_chunks] "piece of shard d of the partial is complete" (call number)
+  unsigned int* d_shard_cnt;     // [tp * ce_chunks]
   unsigned int* d_ce_counter;    // CTA completion counter of the GEMM launches (the reduce kernel has d_counter)
   unsigned int* d_epoch_word;    // the current call number in device memory: source of the four-byte flag copies
   cudaStream_t comm;             // stream of the copies
@@ -1234,91 +1283,76 @@ static int staged_gemm_rs(ftb_gemm_rs_ctx* c, GemmRows gemm_rows, void* out, int
 }
 
 // Copy-engine exchange.  One persistent GEMM launch in the push protocol's tile order (the other ranks' row shards
-// first, rotated by rank, the own shard last) stores every tile into this rank's local partial [m, n] and, when
-// the last tile of a shard is stored, publishes the call number in ready[shard].  A second stream waits for that
-// word with a stream memory operation, waits the same way until the owner has finished reading the previous call's
-// partial, copies the 2 * n * m / tp bytes of the shard into the owner's receive slot with an ordinary
-// device-to-device copy, which the copy engines carry out, and raises the owner's flag with a four-byte copy of
-// the call number.  No SM moves exchange data, so the GEMM keeps its operand loads to itself, and the second
-// stream needs no SM at all (stream waits have no time limit: a rank that never arrives stalls it).  After the GEMM the
-// kernel's last CTA raises this rank's own flag (a launch that finds the status word set raises every ready word
-// and leaves, so the waits of the second stream end whatever became of the GEMM), and the reduce kernel waits for
-// the peers' flags and sums the tp partials of the own shard from local memory.
+// first, rotated by rank, the own shard last).  Tiles of other ranks' rows are stored into this rank's local partial
+// [m, n]; a shard leaves in `chunks` pieces of consecutive row blocks: when the last tile of a piece is stored its
+// word in ready[] takes the call number, a second stream waits for that word with a stream memory operation (and,
+// before the first piece, until the owner has read the previous call's pieces), copies the piece into the owner's
+// receive slot with an ordinary device-to-device copy, which the copy engines carry out, and raises the owner's
+// flag for (source, piece) with a four-byte copy of the call number.  The epilogue of the own rows waits (bounded)
+// for the peers' flags of the piece and adds their partials to the accumulator in fp32: the sum is written once,
+// there is no reduce pass, and no SM moves exchange data.  The second stream runs no kernel (a kernel there might
+// find every SM held by GEMM CTAs that wait for it) and its waits have no time limit: a rank that never arrives
+// stalls it.  A launch that finds the status word set, or whose waits ran out, raises every ready word so that the
+// waits of the second stream end whatever became of the GEMM.
 static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b, void* out, int k_local, int64_t lda,
                                int64_t ldb, int64_t ldo, int32_t* status, cudaStream_t st) {
   using namespace ftb;
-  if (c->form == 1) { set_last_error("ftb_gemm_rs: this context has served fused calls"); return FTB_ERR_INVALID; }
+  if (c->form == 1 || c->form == 2) { set_last_error("ftb_gemm_rs: this context has served calls of another protocol (the flag words differ)"); return FTB_ERR_INVALID; }
   static StreamValue32Fn wait32 = get_stream_memop("cuStreamWaitValue32");
   static StreamValue32Fn write32 = get_stream_memop("cuStreamWriteValue32");
   if (!wait32 || !write32) { set_last_error("ftb_gemm_rs: stream memory operations are not available"); return FTB_ERR_UNSUPPORTED; }
-  c->form = 2;
+  c->form = 3;
   c->epoch += 1;
   const unsigned int epoch = c->epoch;
   const int tp = c->tp, rank = c->rank;
+  const int chunks = c->ce_chunks;
   const long long slot = static_cast<long long>(c->shard_rows) * c->n;       // elements of one row shard
+  const long long piece = slot / chunks;                                      // elements of one piece
   __nv_bfloat16* part = reinterpret_cast<__nv_bfloat16*>(c->part);
   cudaError_t e = cudaEventRecord(c->ev_fork, st);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm, c->ev_fork, 0);
   if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine fork");
-  // ---- GEMM into the local partial
   gemm::Params p;
   memset(&p, 0, sizeof(p));
   p.tp = tp; p.rank = rank; p.shard_rows = c->shard_rows; p.blocks_per_shard = c->blocks_per_shard;
   p.epoch = epoch;
   p.c = part; p.ldc = c->n;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
   p.status = status;
   p.wait_limit = c->wait_limit;
   p.ce_ready = c->d_ready;
   p.ce_cnt = c->d_shard_cnt;
+  p.ce_chunks = chunks;
   p.counter = c->d_ce_counter;
-  for (int i = 0; i < tp; ++i) p.flags[i] = c->flags[i];
+  for (int i = 0; i < tp; ++i) {
+    p.flags[i] = c->flags[i];
+    p.recv[i] = reinterpret_cast<__nv_bfloat16*>(c->recv[i]);
+  }
   const int n_blocks = (c->n + gemm::BN - 1) / gemm::BN;
-  p.ce_target = epoch * static_cast<unsigned int>(c->blocks_per_shard) * static_cast<unsigned int>(n_blocks) * 8u;   // 4 epilogue warps per tile and row block, a whole tile counts 2
+  // 4 epilogue warps per tile and row block, a whole tile counts 2
+  p.ce_target = epoch * static_cast<unsigned int>(c->blocks_per_shard / chunks) * static_cast<unsigned int>(n_blocks) * 8u;
   int rc = launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
   if (rc != FTB_OK) return rc;
-  // ---- exchange on the second stream, destination after destination in the order in which the shards complete
-  gemm::RsFp8Ptrs q;
-  memset(&q, 0, sizeof(q));
-  for (int i = 0; i < tp; ++i) {
-    q.flags[i] = c->flags[i];
-    // the reduce kernel addresses source i as base + (rank * shard_rows + r) * n: the peers' shards sit in this
-    // rank's receive slots, its own in the local partial
-    const __nv_bfloat16* base = (i == rank) ? part : reinterpret_cast<const __nv_bfloat16*>(c->recv[rank]) + (i - rank) * slot;
-    q.recv[i] = base;
-  }
-  // The second stream runs no kernel: while the reduce kernels of all ranks sit on their SMs waiting for each
-  // other's flags, a kernel here might never be scheduled.  Waits are stream memory operations, the flag is a
-  // four-byte copy of the call number behind the shard's copy.
+  // ---- exchange on the second stream, piece after piece in the order in which they complete
   CUresult r = write32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_epoch_word), epoch, CU_STREAM_WRITE_VALUE_DEFAULT);
   if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWriteValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
   for (int s = 1; s < tp; ++s) {
     const int d = (rank + s) % tp;
-    r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_ready + d), epoch, CU_STREAM_WAIT_VALUE_GEQ);
-    // rank d has read the partial of the call before (its word [tp + d] in this rank's flags)
-    if (r == CUDA_SUCCESS && epoch > 1u)
-      r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->flags[rank] + tp + d), epoch - 1u, CU_STREAM_WAIT_VALUE_GEQ);
-    if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWaitValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
-    e = cudaMemcpyAsync(reinterpret_cast<__nv_bfloat16*>(c->recv[d]) + rank * slot, part + d * slot,
-                        static_cast<size_t>(slot) * 2, cudaMemcpyDeviceToDevice, c->comm);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(c->flags[d] + rank, c->d_epoch_word, sizeof(unsigned int), cudaMemcpyDeviceToDevice, c->comm);
-    if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine copy");
+    for (int ch = 0; ch < chunks; ++ch) {
+      r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_ready + d * chunks + ch), epoch, CU_STREAM_WAIT_VALUE_GEQ);
+      // rank d has read the pieces of the call before (its word [tp * chunks + d] in this rank's flags)
+      if (r == CUDA_SUCCESS && ch == 0 && epoch > 1u)
+        r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->flags[rank] + tp * chunks + d), epoch - 1u, CU_STREAM_WAIT_VALUE_GEQ);
+      if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWaitValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
+      e = cudaMemcpyAsync(reinterpret_cast<__nv_bfloat16*>(c->recv[d]) + rank * slot + ch * piece, part + d * slot + ch * piece,
+                          static_cast<size_t>(piece) * 2, cudaMemcpyDeviceToDevice, c->comm);
+      if (e == cudaSuccess)
+        e = cudaMemcpyAsync(c->flags[d] + rank * chunks + ch, c->d_epoch_word, sizeof(unsigned int), cudaMemcpyDeviceToDevice, c->comm);
+      if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine copy");
+    }
   }
   e = cudaEventRecord(c->ev_join, c->comm);
   if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine join");
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
-  const unsigned grid = static_cast<unsigned>(sms) * 4u;
-  switch (tp) {
-    case 2: gemm::rs_local_reduce_kernel<2, 4><<<grid, 256, 0, st>>>(q, o, ldo, c->shard_rows, c->n, rank, epoch, c->d_counter, status, c->wait_limit); break;
-    case 4: gemm::rs_local_reduce_kernel<4, 4><<<grid, 256, 0, st>>>(q, o, ldo, c->shard_rows, c->n, rank, epoch, c->d_counter, status, c->wait_limit); break;
-    case 8: gemm::rs_local_reduce_kernel<8, 2><<<grid, 256, 0, st>>>(q, o, ldo, c->shard_rows, c->n, rank, epoch, c->d_counter, status, c->wait_limit); break;
-    default:
-      gemm::rs_fp8_reduce_kernel<<<sms * 3, 256, 0, st>>>(q, nullptr, o, ldo, c->shard_rows, c->n, rank, tp, epoch, c->d_counter, status, c->wait_limit);
-  }
-  rc = check_cuda(cudaGetLastError(), "rs reduce launch");
-  if (rc != FTB_OK) return rc;
   // the next call's GEMM overwrites the partial: not before this call's copies have read it
   return check_cuda(cudaStreamWaitEvent(st, c->ev_join, 0), "gemm_rs copy-engine join wait");
 }
@@ -1332,7 +1366,7 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
   if (ok != FTB_OK) return ok;
   if (c->copy_engine) return copy_engine_gemm_rs(c, a, b, out, k_local, lda, ldb, ldo, status, reinterpret_cast<cudaStream_t>(stream));
   if (c->staged) {
-    if (c->form == 1) { set_last_error("ftb_gemm_rs: this context has served fused calls"); return FTB_ERR_INVALID; }
+    if (c->form == 1 || c->form == 3) { set_last_error("ftb_gemm_rs: this context has served calls of another protocol (the flag words differ)"); return FTB_ERR_INVALID; }
     c->form = 2;
     const int n = c->n;
     auto rows = [&](long long row0, int m_rows, __nv_bfloat16* dst) -> int {
@@ -1348,7 +1382,7 @@ extern "C" FTB_API int ftb_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void
     };
     return staged_gemm_rs(c, rows, out, ldo, status, reinterpret_cast<cudaStream_t>(stream));
   }
-  if (c->form == 2) { set_last_error("ftb_gemm_rs: this context serves staged calls (the flag words differ)"); return FTB_ERR_INVALID; }
+  if (c->form == 2 || c->form == 3) { set_last_error("ftb_gemm_rs: this context serves calls of another protocol (the flag words differ)"); return FTB_ERR_INVALID; }
   c->form = 1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   c->epoch += 1;
@@ -1377,7 +1411,7 @@ extern "C" FTB_API int ftb_gemm_rs_fp8(ftb_gemm_rs_ctx* c, const void* a, const 
                                        int64_t a_scale_ld, int64_t b_scale_ld, int64_t ldo, int32_t* status, void* stream) {
   if (!c || !a || !b || !a_scale || !b_scale || !out) { set_last_error("ftb_gemm_rs_fp8: null pointer"); return FTB_ERR_INVALID; }
   if ((ldo % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) { set_last_error("ftb_gemm_rs_fp8: out alignment"); return FTB_ERR_INVALID; }
-  if (c->form == 1) { set_last_error("ftb_gemm_rs_fp8: this context serves fused bf16 calls (the flag words differ)"); return FTB_ERR_INVALID; }
+  if (c->form == 1 || c->form == 3) { set_last_error("ftb_gemm_rs_fp8: this context serves bf16 calls of another protocol (the flag words differ)"); return FTB_ERR_INVALID; }
   if ((c->n % 128) || (k_local % 128)) { set_last_error("ftb_gemm_rs_fp8: n and k_local must be multiples of 128"); return FTB_ERR_INVALID; }
   if (k_local <= 0 || (lda % 16) || (ldb % 16) || (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15)) {
     set_last_error("ftb_gemm_rs_fp8: operands must be 16-byte aligned with leading dimensions that are multiples of 16");
@@ -1409,10 +1443,18 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_set_copy_engine(ftb_gemm_rs_ctx* c, int o
   if (c->epoch != 0) { set_last_error("ftb_gemm_rs_ctx_set_copy_engine: must be called before the first call"); return FTB_ERR_INVALID; }
   if (on && c->part == nullptr) {
     cudaError_t e = cudaMalloc(&c->part, static_cast<size_t>(c->m) * c->n * 2);
-    if (e == cudaSuccess) e = cudaMalloc(&c->d_ready, sizeof(unsigned int) * gemm::MAX_TP);
-    if (e == cudaSuccess) e = cudaMemset(c->d_ready, 0, sizeof(unsigned int) * gemm::MAX_TP);
-    if (e == cudaSuccess) e = cudaMalloc(&c->d_shard_cnt, sizeof(unsigned int) * gemm::MAX_TP);
-    if (e == cudaSuccess) e = cudaMemset(c->d_shard_cnt, 0, sizeof(unsigned int) * gemm::MAX_TP);
+    // A shard leaves in up to four pieces (whole CTA-pair row groups each), as long as the second stream has at
+    // most eight copies per call to issue: the pieces of the shard computed last arrive while the own rows are
+    // still being multiplied.
+    int chunks = 1;
+    for (int cand = 4; cand > 1; cand >>= 1)
+      if ((c->tp - 1) * cand <= 8 && c->blocks_per_shard % (2 * cand) == 0) { chunks = cand; break; }
+    c->ce_chunks = chunks;
+    const size_t words = sizeof(unsigned int) * gemm::MAX_TP * 4;
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_ready, words);
+    if (e == cudaSuccess) e = cudaMemset(c->d_ready, 0, words);
+    if (e == cudaSuccess) e = cudaMalloc(&c->d_shard_cnt, words);
+    if (e == cudaSuccess) e = cudaMemset(c->d_shard_cnt, 0, words);
     if (e == cudaSuccess) e = cudaMalloc(&c->d_epoch_word, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMalloc(&c->d_ce_counter, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(c->d_ce_counter, 0, sizeof(unsigned int));
@@ -1556,24 +1598,28 @@ extern "C" FTB_API int ftb_ag_gemm(ftb_ag_gemm_ctx* c, const void* a_shard, cons
   cudaError_t e = cudaEventRecord(c->ev_fork, st);      // the shard is ready on the caller's stream
   if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm, c->ev_fork, 0);
   if (e != cudaSuccess) return check_cuda(e, "ag_gemm fork");
-  // ---- second stream: own shard into the own gather buffer, then to the peers, rank + 1 first
+  // ---- second stream: the shard goes to the peers, rank + 1 first (the own rows are read where they lie)
   CUresult r = write32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_epoch_word), epoch, CU_STREAM_WRITE_VALUE_DEFAULT);
   if (r != CUDA_SUCCESS) { set_last_error("ftb_ag_gemm: cuStreamWriteValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
-  for (int s = 0; s < tp; ++s) {
+  for (int s = 1; s < tp; ++s) {
     const int d = (rank + s) % tp;
-    // rank d has read the gather buffer of the call before (its word [tp + d] in this rank's flags; for d = rank the
-    // word is written by this rank's own GEMM of that call, which the fork event already covers)
-    if (d != rank && epoch > 1u) {
+    // rank d has read the gather buffer of the call before (its word [tp + d] in this rank's flags)
+    if (epoch > 1u) {
       r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->flags[rank] + tp + d), epoch - 1u, CU_STREAM_WAIT_VALUE_GEQ);
       if (r != CUDA_SUCCESS) { set_last_error("ftb_ag_gemm: cuStreamWaitValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
     }
     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(c->ag[d]) + static_cast<size_t>(rank) * c->shard_rows * c->k;
-    e = cudaMemcpy2DAsync(dst, static_cast<size_t>(c->k) * 2, a_shard, static_cast<size_t>(lda) * 2, static_cast<size_t>(c->k) * 2,
-                          static_cast<size_t>(c->shard_rows), cudaMemcpyDeviceToDevice, c->comm);
+    // A contiguous shard goes as one linear copy, which the copy engines carry out.  (A pitched copy may be run
+    // by a kernel of the driver's; on a GPU whose SMs are held by GEMM CTAs that wait for this very copy such a
+    // kernel has no place to run until the waits give up.)
+    if (lda == c->k)
+      e = cudaMemcpyAsync(dst, a_shard, shard_bytes, cudaMemcpyDeviceToDevice, c->comm);
+    else
+      e = cudaMemcpy2DAsync(dst, static_cast<size_t>(c->k) * 2, a_shard, static_cast<size_t>(lda) * 2, static_cast<size_t>(c->k) * 2,
+                            static_cast<size_t>(c->shard_rows), cudaMemcpyDeviceToDevice, c->comm);
     if (e == cudaSuccess) e = cudaMemcpyAsync(c->flags[d] + rank, c->d_epoch_word, sizeof(unsigned int), cudaMemcpyDeviceToDevice, c->comm);
     if (e != cudaSuccess) return check_cuda(e, "ag_gemm copy");
   }
-  (void)shard_bytes;
   e = cudaEventRecord(c->ev_join, c->comm);
   if (e != cudaSuccess) return check_cuda(e, "ag_gemm join");
   // ---- the GEMM over the gather buffer
@@ -1587,7 +1633,7 @@ extern "C" FTB_API int ftb_ag_gemm(ftb_ag_gemm_ctx* c, const void* a_shard, cons
   p.ag_flags = c->flags[rank];
   p.counter = c->d_counter;
   for (int i = 0; i < tp; ++i) p.flags[i] = c->flags[i];
-  int rc = launch_gemm(c->ag[rank], b, c->m, n_local, c->k, c->k, ldb, p, st);
+  int rc = launch_gemm(c->ag[rank], b, c->m, n_local, c->k, c->k, ldb, p, st, a_shard, c->shard_rows, lda);
   if (rc != FTB_OK) return rc;
   // the caller may overwrite its shard once the copies have read it
   return check_cuda(cudaStreamWaitEvent(st, c->ev_join, 0), "ag_gemm join wait");
