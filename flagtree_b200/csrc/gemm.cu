@@ -1155,83 +1155,6 @@ __global__ void __launch_bounds__(256, 3) rs_fp8_reduce_kernel(RsFp8Ptrs q, cons
 }
 
 
-// Reduce kernel of the copy-engine exchange: every source lies in THIS rank's memory (the peers' partials of the
-// own shard in the receive slots, the own partial in the local partial buffer), so this is one pass over
-// TP x shard bytes at device-memory speed.  Waits (bounded) until every peer's flag shows this call, then each
-// thread sums V 16-byte vectors with all TP x V loads in flight before the first add (fixed source order, fp32).
-// The last CTA tells every peer that their partials of this call have been read.
-template <int TP, int V>
-__global__ void __launch_bounds__(256) rs_local_reduce_kernel(RsFp8Ptrs q, __nv_bfloat16* out, long long ldo, int shard_rows, int n,
-                                                             int rank, unsigned int epoch, unsigned int* counter, int* status,
-                                                             long long wait_limit) {
-  __shared__ int s_abort;
-  if (threadIdx.x == 0) s_abort = (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) ? 1 : 0;
-  __syncthreads();
-  if (threadIdx.x < TP && !s_abort) {
-    const long long t0 = clock64();
-    while (ld_acquire_sys(q.flags[rank] + threadIdx.x) < epoch) {
-      if (clock64() - t0 > wait_limit) {
-        s_abort = 1;
-        if (status != nullptr) atomicCAS(status, 0, FTB_ERR_TIMEOUT);
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  if (!s_abort) {
-    const int vec_per_row = n / 8;
-    const long long total = static_cast<long long>(shard_rows) * vec_per_row;
-    const long long row0 = static_cast<long long>(rank) * shard_rows;
-    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-    for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += stride * V) {
-      uint4 v[TP][V];
-      long long dst[V];
-      bool ok[V];
-#pragma unroll
-      for (int u = 0; u < V; ++u) {
-        const long long i = i0 + u * stride;
-        ok[u] = i < total;
-        const long long r = ok[u] ? i / vec_per_row : 0;
-        const int c8 = ok[u] ? static_cast<int>(i - r * vec_per_row) : 0;
-        const long long off = (row0 + r) * n + c8 * 8;
-        dst[u] = r * ldo + c8 * 8;
-#pragma unroll
-        for (int src = 0; src < TP; ++src)
-          v[src][u] = ok[u] ? __ldcs(reinterpret_cast<const uint4*>(q.recv[src] + off)) : make_uint4(0, 0, 0, 0);
-      }
-#pragma unroll
-      for (int u = 0; u < V; ++u) {
-        float acc[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-#pragma unroll
-        for (int src = 0; src < TP; ++src) {
-          const uint32_t w[4] = {v[src][u].x, v[src][u].y, v[src][u].z, v[src][u].w};
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            acc[2 * k] += __uint_as_float(w[k] << 16);
-            acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
-          }
-        }
-        if (ok[u]) {
-          uint4 o;
-          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-          __stcs(reinterpret_cast<uint4*>(out + dst[u]), o);
-        }
-      }
-    }
-  }
-  __threadfence_system();
-  __syncthreads();
-  __shared__ unsigned int s_last;
-  if (threadIdx.x == 0) s_last = (atomicAdd(counter, 1u) == gridDim.x - 1u) ? 1u : 0u;
-  __syncthreads();
-  if (s_last) {
-    if (threadIdx.x == 0) *counter = 0u;
-    if (threadIdx.x < TP) st_release_sys(q.flags[threadIdx.x] + TP + rank, epoch);
-  }
-}
 
 }  // namespace gemm
 }  // namespace ftb
