@@ -395,7 +395,7 @@ def bench_gemm_rs_fp8(args, dev, rank, world, dist, peaks):
         row = {"m": m, "n": n, "k_local": k_total // world, "flops_per_gpu": flops, "gemm_only_ms": t_gemm,
                "gemm_only_tflops_per_gpu": flops / t_gemm / 1e9}
         if world > 1:
-            ctx = GemmRsContext(m, n, None, dev, "auto", "auto")
+            ctx = GemmRsContext(m, n, None, dev, "auto", "auto", fp8=True)
             out = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)
             t_fused = _timed_collective(lambda: ctx.fp8(case.a, case.a_scale, case.b, case.b_scale, out), iters, flush, dist, sync_word, dev)
             ctx.check()

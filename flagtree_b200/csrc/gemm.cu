@@ -78,8 +78,9 @@ struct Params {
   // (source, piece), and the epilogue of the own rows, which come last, adds them: no separate reduce pass.
   unsigned int* ce_ready;            // [tp * ce_chunks] (NULL = another protocol)
   unsigned int* ce_cnt;              // [tp * ce_chunks] epilogue-warp arrivals per piece, monotonic over calls
-  unsigned int ce_target;            // value ce_cnt[] reaches in this call
-  int ce_chunks;
+  unsigned int ce_target[8];         // value ce_cnt[d * ce_chunks + piece] reaches in this call (pieces may differ in size)
+  int ce_chunks;                     // <= 8
+  int ce_groups, ce_group_blocks;    // row groups per shard, row blocks per group (2 when the shard has an even number)
   // all-gather + GEMM: the rows of A arrive shard by shard (copy engines of the peers); ag_flags[src] takes the
   // call number once rank src's shard is in place.  NULL = A is complete at launch.  The rank's own rows are read
   // from the caller's shard through a tensor map of their own (no copy, no wait).
@@ -491,7 +492,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       const bool ce = !PULL && !ce_own && (p.ce_ready != nullptr || ag);    // tiles stored plainly into c
       const bool remote = !PULL && !ce && !ce_own && p.tp > 1 && dst != p.rank;
       const int blk_in_shard = m_blk - dst * p.blocks_per_shard;
-      const int piece = p.ce_ready != nullptr ? blk_in_shard * p.ce_chunks / p.blocks_per_shard : 0;
+      // row group g of a shard belongs to piece floor(g * pieces / groups)
+      const int piece = p.ce_ready != nullptr ? (blk_in_shard / p.ce_group_blocks) * p.ce_chunks / p.ce_groups : 0;
       if constexpr (PULL) {
         // Before overwriting a row block of the partial buffer make sure its owner has fetched the
         // previous call's sum (the owner's done[] word in this rank's flag buffer).
@@ -534,7 +536,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           if (ce_pending >= 0) {
             __threadfence();
             const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, ce_weight) + ce_weight;
-            if (cnt == p.ce_target) st_release_sys(p.ce_ready + ce_pending, p.epoch);
+            if (cnt == p.ce_target[ce_pending % p.ce_chunks]) st_release_sys(p.ce_ready + ce_pending, p.epoch);
             ce_pending = -1;
           }
           const int blk = m_blk - dst * p.blocks_per_shard;
@@ -674,7 +676,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           // through L2, so device scope is enough.  The last count of a shard publishes "shard complete".
           __threadfence();
           const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, ce_weight) + ce_weight;
-          if (cnt == p.ce_target) st_release_sys(p.ce_ready + ce_pending, p.epoch);
+          if (cnt == p.ce_target[ce_pending % p.ce_chunks]) st_release_sys(p.ce_ready + ce_pending, p.epoch);
           ce_pending = -1;
         }
         __syncwarp();                  // the tensor-memory loads below are warp-collective
@@ -711,7 +713,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     if (lane == 0 && ce_pending >= 0) {
       __threadfence();
       const unsigned int cnt = atomicAdd(p.ce_cnt + ce_pending, ce_weight) + ce_weight;
-      if (cnt == p.ce_target) st_release_sys(p.ce_ready + ce_pending, p.epoch);
+      if (cnt == p.ce_target[ce_pending % p.ce_chunks]) st_release_sys(p.ce_ready + ce_pending, p.epoch);
     }
     if (lane == 0) {
       bulk_wait_all();
@@ -1230,7 +1232,11 @@ static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b,
   const int tp = c->tp, rank = c->rank;
   const int chunks = c->ce_chunks;
   const long long slot = static_cast<long long>(c->shard_rows) * c->n;       // elements of one row shard
-  const long long piece = slot / chunks;                                      // elements of one piece
+  // row groups as the CTA groups take them (pairs of row blocks when the shard has an even number of them); group g
+  // belongs to piece floor(g * chunks / groups), so piece p starts at group ceil(p * groups / chunks)
+  const int rows_per_group = (c->blocks_per_shard % 2 == 0 ? 2 : 1) * gemm::BM;
+  const int groups = c->shard_rows / rows_per_group;
+  auto piece_row0 = [&](int pc) { return ((pc * groups + chunks - 1) / chunks) * rows_per_group; };
   __nv_bfloat16* part = reinterpret_cast<__nv_bfloat16*>(c->part);
   cudaError_t e = cudaEventRecord(c->ev_fork, st);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(c->comm, c->ev_fork, 0);
@@ -1246,6 +1252,8 @@ static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b,
   p.ce_ready = c->d_ready;
   p.ce_cnt = c->d_shard_cnt;
   p.ce_chunks = chunks;
+  p.ce_groups = groups;
+  p.ce_group_blocks = rows_per_group / gemm::BM;
   p.counter = c->d_ce_counter;
   for (int i = 0; i < tp; ++i) {
     p.flags[i] = c->flags[i];
@@ -1253,10 +1261,13 @@ static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b,
   }
   const int n_blocks = (c->n + gemm::BN - 1) / gemm::BN;
   // 4 epilogue warps per tile and row block, a whole tile counts 2
-  p.ce_target = epoch * static_cast<unsigned int>(c->blocks_per_shard / chunks) * static_cast<unsigned int>(n_blocks) * 8u;
+  for (int pc = 0; pc < chunks; ++pc)
+    p.ce_target[pc] = epoch * static_cast<unsigned int>((piece_row0(pc + 1) - piece_row0(pc)) / gemm::BM) * static_cast<unsigned int>(n_blocks) * 8u;
   int rc = launch_gemm(a, b, c->m, c->n, k_local, lda, ldb, p, st);
   if (rc != FTB_OK) return rc;
-  // ---- exchange on the second stream, piece after piece in the order in which they complete
+  // ---- exchange on the second stream, piece after piece in the order in which they complete.  (One stream per
+  // destination and flags raised by stream writes to the peer were measured too: no faster; the copy engines give
+  // a rank about 500 GB/s in copies of this size whatever the number of streams.)
   CUresult r = write32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->d_epoch_word), epoch, CU_STREAM_WRITE_VALUE_DEFAULT);
   if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWriteValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
   for (int s = 1; s < tp; ++s) {
@@ -1267,8 +1278,10 @@ static int copy_engine_gemm_rs(ftb_gemm_rs_ctx* c, const void* a, const void* b,
       if (r == CUDA_SUCCESS && ch == 0 && epoch > 1u)
         r = wait32(reinterpret_cast<CUstream>(c->comm), reinterpret_cast<CUdeviceptr>(c->flags[rank] + tp * chunks + d), epoch - 1u, CU_STREAM_WAIT_VALUE_GEQ);
       if (r != CUDA_SUCCESS) { set_last_error("ftb_gemm_rs: cuStreamWaitValue32 failed (%d)", static_cast<int>(r)); return FTB_ERR_CUDA; }
-      e = cudaMemcpyAsync(reinterpret_cast<__nv_bfloat16*>(c->recv[d]) + rank * slot + ch * piece, part + d * slot + ch * piece,
-                          static_cast<size_t>(piece) * 2, cudaMemcpyDeviceToDevice, c->comm);
+      const long long off = static_cast<long long>(piece_row0(ch)) * c->n;
+      const size_t bytes = static_cast<size_t>(piece_row0(ch + 1) - piece_row0(ch)) * c->n * 2;
+      e = cudaMemcpyAsync(reinterpret_cast<__nv_bfloat16*>(c->recv[d]) + rank * slot + off, part + d * slot + off, bytes,
+                          cudaMemcpyDeviceToDevice, c->comm);
       if (e == cudaSuccess)
         e = cudaMemcpyAsync(c->flags[d] + rank * chunks + ch, c->d_epoch_word, sizeof(unsigned int), cudaMemcpyDeviceToDevice, c->comm);
       if (e != cudaSuccess) return check_cuda(e, "gemm_rs copy-engine copy");
@@ -1369,17 +1382,22 @@ extern "C" FTB_API int ftb_gemm_rs_ctx_set_copy_engine(ftb_gemm_rs_ctx* c, int o
     // A shard leaves in up to four pieces (whole CTA-pair row groups each), as long as the second stream has at
     // most eight copies per call to issue: the pieces of the shard computed last arrive while the own rows are
     // still being multiplied.
-    int chunks = 1;
-    for (int cand = 4; cand > 1; cand >>= 1)
-      if ((c->tp - 1) * cand <= 8 && c->blocks_per_shard % (2 * cand) == 0) { chunks = cand; break; }
+    const int groups = c->blocks_per_shard % 2 == 0 ? c->blocks_per_shard / 2 : c->blocks_per_shard;
+    // measured: tp = 2: 4 pieces (2: +12 %, 3 and 6: +5 %); tp = 4: 2 pieces (1 and 4: +7 %)
+    int chunks = c->tp == 2 ? 4 : c->tp <= 4 ? 2 : 1;
+    if (const char* ev = getenv("FTB_RS_PIECES")) chunks = atoi(ev);      // tuning override
+    if (chunks > 8) chunks = 8;
+    if (chunks > groups) chunks = groups;
+    if (chunks < 1) chunks = 1;
     c->ce_chunks = chunks;
-    const size_t words = sizeof(unsigned int) * gemm::MAX_TP * 4;
+    const size_t words = sizeof(unsigned int) * gemm::MAX_TP * 8;
     if (e == cudaSuccess) e = cudaMalloc(&c->d_ready, words);
     if (e == cudaSuccess) e = cudaMemset(c->d_ready, 0, words);
     if (e == cudaSuccess) e = cudaMalloc(&c->d_shard_cnt, words);
     if (e == cudaSuccess) e = cudaMemset(c->d_shard_cnt, 0, words);
     if (e == cudaSuccess) e = cudaMalloc(&c->d_epoch_word, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMalloc(&c->d_ce_counter, sizeof(unsigned int));
+
     if (e == cudaSuccess) e = cudaMemset(c->d_ce_counter, 0, sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->comm, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);

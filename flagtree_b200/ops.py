@@ -464,11 +464,13 @@ def matmul_fp8_blockscaled(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tens
 class GemmRsContext:
     """Workspace of one (M, N, group) GEMM + reduce-scatter shape: peer-mapped receive slots and flags.
 
-    Creation is collective over `group`.  One call may be in flight per context.
+    Creation is collective over `group`.  One call may be in flight per context.  `fp8=True` announces that the
+    context will serve block-scaled FP8 calls (`fp8()`), which keeps "auto" off the copy-engine protocol: its flag
+    words differ from those of the FP8 form.
     """
 
     def __init__(self, m: int, n: int, group=None, device: Optional[torch.device] = None, provider: str = "auto",
-                 protocol: str = "auto"):
+                 protocol: str = "auto", fp8: bool = False):
         import torch.distributed as dist
         from .symm import SymmetricBuffer
         self.group = group
@@ -492,6 +494,11 @@ class GemmRsContext:
         import torch.distributed as dist
         # measured at the cfg4 per-rank shape: push 0.311 ms against pull 0.36-0.39 at tp = 2, level at tp = 4,
         # pull 0.383-0.390 against push 0.463-0.471 at tp = 8; so "auto" pulls from four ranks on
+        # "auto" for bf16 calls: the copy-engine exchange up to four ranks (0.224 ms against push 0.30 and
+        # GEMM + NCCL 0.35 at tp = 2; 0.333 against pull 0.394 and NCCL 0.378 at tp = 4), the in-switch reduction
+        # beyond (the copy engines of a rank move about 500 GB/s, too little for seven shards)
+        if protocol == "auto" and not fp8 and self.tp <= 4:
+            protocol = "copy"
         want_pull = protocol == "pull" or (protocol == "auto" and self.tp >= 4)
         have_mc = torch.tensor([1 if (self.recv.mc_ptr and want_pull) else 0], device=self.device)
         dist.all_reduce(have_mc, op=dist.ReduceOp.MIN, group=group)
@@ -503,8 +510,8 @@ class GemmRsContext:
         # per-rank shape the staged form is the slowest (0.44 ms at tp = 2, 0.48 ms at tp = 8), so "auto"
         # keeps the fused kernel; the FP8 form always runs staged.
         self.staged = protocol == "staged"
-        # "copy" = one GEMM launch into a local partial, the shards sent by device-to-device copies on a second
-        # stream as they complete (copy engines), one reduce kernel
+        # "copy" = one GEMM launch; the other ranks' row shards leave in pieces by device-to-device copies on a second
+        # stream as they complete (copy engines), the epilogue of the own rows adds the peers' partials
         if protocol == "copy":
             _lib.check(lib.ftb_gemm_rs_ctx_set_copy_engine(ctx, 1), "gemm_rs set_copy_engine")
             self.protocol = "copy"
@@ -538,6 +545,8 @@ class GemmRsContext:
         fp32 scales [(K/tp)/128, N/128]; returns this rank's rows of the sum of the dequantised products as
         bf16.  A context serves either bf16 calls or FP8 calls."""
         _require_cuda(a, a_scale, b, b_scale)
+        if self.protocol == "copy":
+            raise RuntimeError("gemm_rs_fp8: this context runs the copy-engine protocol of the bf16 form; create it with fp8=True")
         for t in (a, b):
             assert t.dtype in (torch.uint8, torch.float8_e4m3fn), "operands must hold e4m3 bytes"
         assert a.shape[0] == self.m and b.shape[1] == self.n and a.shape[1] == b.shape[0], "incompatible dimensions"
@@ -671,7 +680,7 @@ def _rs_context(form: str, m: int, n: int, group, device) -> "GemmRsContext":
     key = (form, m, n, device.index, id(group))
     hit = _RS_CONTEXTS.get(key)
     if hit is None or hit[0] is not group:
-        hit = _RS_CONTEXTS[key] = (group, GemmRsContext(m, n, group, device))
+        hit = _RS_CONTEXTS[key] = (group, GemmRsContext(m, n, group, device, fp8=(form == "fp8")))
     return hit[1]
 
 

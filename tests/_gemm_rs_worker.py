@@ -53,7 +53,8 @@ def main():
         cases = [W.gemm_cfg5(tp=world, rank=r, m=m, n=n, k_total=k_total) for r in range(world)]
         ref = gemm_rs_fp8_ref([c.a for c in cases], [c.a_scale for c in cases], [c.b for c in cases],
                               [c.b_scale for c in cases])[rank]
-        ctx = GemmRsContext(m, n, None, dev, provider, protocol)
+        # a context of the copy-engine protocol serves bf16 calls only: the FP8 form gets its own
+        ctx = GemmRsContext(m, n, None, dev, provider, "auto" if protocol == "copy" else protocol, fp8=True)
         me = cases[rank]
         a, b, a_s, b_s = me.a.to(dev), me.b.to(dev), me.a_scale.to(dev), me.b_scale.to(dev)
         outs = [ctx.fp8(a, a_s, b, b_s).clone() for _ in range(3)]
