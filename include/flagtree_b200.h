@@ -256,10 +256,12 @@ FTB_API int ftb_gemm_rs_ctx_set_multicast(ftb_gemm_rs_ctx* ctx, void* mc_recv_pt
  * shard.  0 = the fused kernel (default).  The FP8 form always works this way. */
 FTB_API int ftb_gemm_rs_ctx_set_staged(ftb_gemm_rs_ctx* ctx, int staged);
 /* Copy-engine exchange for the bf16 calls of a context (before its first call; allocates a local partial of
- * 2 * m * n bytes and a second stream): one GEMM launch stores the partial locally, shard by shard in rotated
- * order; as each shard completes, a second stream copies it into its owner's receive slot with a device-to-device
- * copy (carried out by the copy engines, no SM involved) and raises the owner's flag; a reduce kernel sums the
- * tp partials of the own shard.  The call returns on `stream` as usual; the second stream is joined to it. */
+ * 2 * m * n bytes and a second stream): one GEMM launch stores the other ranks' row shards into the local partial
+ * in rotated order, the own shard last; as pieces of a shard complete, a second stream copies them into the owner's
+ * receive slot with device-to-device copies (carried out by the copy engines, no SM involved) and raises the
+ * owner's flags; the epilogue of the own rows waits (bounded) for the peers' flags and adds their partials in fp32,
+ * so the result is rounded once and there is no reduce pass.  The call returns on `stream` as usual; the second
+ * stream is joined to it.  A context of this protocol serves bf16 calls only. */
 FTB_API int ftb_gemm_rs_ctx_set_copy_engine(ftb_gemm_rs_ctx* ctx, int on);
 /* Longest time, in SM clock cycles, that a kernel of this context waits for another rank before it gives up,
  * sets FTB_ERR_TIMEOUT in the status word and returns (default about one second).  After a timeout the
