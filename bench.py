@@ -394,6 +394,11 @@ def bench_gemm_rs_fp8(args, dev, rank, world, dist, peaks):
                                    iters, flush, dist, sync_word, dev)
         row = {"m": m, "n": n, "k_local": k_total // world, "flops_per_gpu": flops, "gemm_only_ms": t_gemm,
                "gemm_only_tflops_per_gpu": flops / t_gemm / 1e9}
+        # the same product with the weight kept as [N, K] (K contiguous) and passed as its transposed view
+        bt = case.b.t().contiguous()
+        t_km = _timed_collective(lambda: matmul_fp8_blockscaled(case.a, case.a_scale, bt.t(), case.b_scale, out=c_full), iters, flush, dist, sync_word, dev)
+        row.update({"gemm_only_weight_nk_ms": t_km, "gemm_only_weight_nk_tflops_per_gpu": flops / t_km / 1e9})
+        del bt
         if world > 1:
             ctx = GemmRsContext(m, n, None, dev, "auto", "auto", fp8=True)
             out = torch.empty(m // world, n, dtype=torch.bfloat16, device=dev)

@@ -46,7 +46,7 @@ class GemmFp8Args(C.Structure):
     _fields_ = [("a", C.c_void_p), ("b", C.c_void_p), ("c", C.c_void_p), ("a_scale", C.c_void_p), ("b_scale", C.c_void_p),
                 ("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32),
                 ("lda", C.c_int64), ("ldb", C.c_int64), ("ldc", C.c_int64), ("a_scale_ld", C.c_int64), ("b_scale_ld", C.c_int64),
-                ("status", C.c_void_p)]
+                ("status", C.c_void_p), ("b_kmajor", C.c_int32)]
 
 
 class SparseMlaMergeArgs(C.Structure):

@@ -5,8 +5,13 @@
 // 128-deep K block is multiplied on its own (4 tcgen05.mma kind::f8f6f4 of K = 32 into a fresh TMEM
 // accumulator) and four "promotion" warps fold it into fp32 registers with its two scales while the
 // next block is being multiplied (two TMEM accumulators of 128 columns).
-// Tile 128 x 128, K step 128; A stage [128 rows x 128 B] K-major, B stage [128 k-rows x 128 B]
-// (128 columns) used as the MN-major operand; 6 stages of 32 KB filled by TMA.
+// Tile 128 x 128, K step 128; A stage [128 rows x 128 B] K-major; B stage either [128 k-rows x 128 B]
+// (128 columns; B given as [K, N] row-major, the MN-major operand) or [128 columns x 128 B] (B given as the
+// transpose [N, K] row-major, as a linear layer keeps its weight: the K-major operand, same speed, same bits);
+// 6 stages of 32 KB filled by TMA.
+// Measured and not kept (cfg5 shapes, 908 / 1080 / 1090 TFLOP/s with this kernel; the tensor pipe is 32 % busy, L2
+// 37 %): eight promotion warps with packed two-wide adds and the scales fetched a block ahead (-4 %), CTA pairs
+// on 256 x 256 tiles (-20 %).
 // Roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer + TMEM owner, warps 2-5 promotion/epilogue.
 #include <cstring>
 
@@ -46,6 +51,7 @@ struct Bars {
   int abort_flag;
 };
 
+template <bool B_KMAJOR>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -91,13 +97,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
           mbar_arrive_expect_tx(full, STAGE_BYTES);
           const uint32_t a_dst = base + s * STAGE_BYTES;
           tma_load_2d(a_dst, &tm_a, full, kb * BK, m_blk * BM);
-          tma_load_2d(a_dst + A_BYTES, &tm_b, full, n_blk * BN, kb * BK);
+          if constexpr (B_KMAJOR) tma_load_2d(a_dst + A_BYTES, &tm_b, full, kb * BK, n_blk * BN);
+          else tma_load_2d(a_dst + A_BYTES, &tm_b, full, n_blk * BN, kb * BK);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t kIdesc = umma_idesc(kFmtE4M3, BM, BN, 0, 1);
+      constexpr uint32_t kIdesc = umma_idesc(kFmtE4M3, BM, BN, 0, B_KMAJOR ? 0 : 1);
       uint32_t it = 0;   // K blocks issued so far = accumulator uses
       for (int t = blockIdx.x; t < p.n_tiles; t += gridDim.x) {
         for (int kb = 0; kb < p.kb_total; ++kb, ++it) {
@@ -111,7 +118,8 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
             const uint64_t ad = smem_desc_sw128(a_s + k * 32, 16, 1024);          // K-major: 32 B per K step
-            const uint64_t bd = smem_desc_sw128(b_s + k * 4096, B_BYTES, 1024);   // MN-major: 32 k-rows per step
+            const uint64_t bd = B_KMAJOR ? smem_desc_sw128(b_s + k * 32, 16, 1024)            // K-major: 32 B per K step
+                                         : smem_desc_sw128(b_s + k * 4096, B_BYTES, 1024);   // MN-major: 32 k-rows per step
             umma_f8_ss(tmem + acc * BN, ad, bd, kIdesc, k != 0 ? 1u : 0u);
           }
           umma_commit(smem_u32(&bars->empty[s]));
@@ -189,8 +197,10 @@ extern "C" FTB_API int ftb_gemm_fp8_blockscaled(const ftb_gemm_fp8_args* g, void
     return FTB_ERR_INVALID;
   }
   CUtensorMap tm_a, tm_b;
+  const bool bkm = g->b_kmajor != 0;
   if (!make_tmap_2d(&tm_a, g->a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g->m, g->k, g->lda, gemm8::BM, 128) ||
-      !make_tmap_2d(&tm_b, g->b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g->k, g->n, g->ldb, gemm8::BK, 128)) {
+      !(bkm ? make_tmap_2d(&tm_b, g->b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g->n, g->k, g->ldb, gemm8::BN, 128)
+            : make_tmap_2d(&tm_b, g->b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g->k, g->n, g->ldb, gemm8::BK, 128))) {
     set_last_error("ftb_gemm_fp8_blockscaled: cuTensorMapEncodeTiled failed");
     return FTB_ERR_CUDA;
   }
@@ -208,9 +218,10 @@ extern "C" FTB_API int ftb_gemm_fp8_blockscaled(const ftb_gemm_fp8_args* g, void
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  cudaError_t e = cudaFuncSetAttribute(gemm8::gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm8::SMEM_BYTES);
+  auto kern = bkm ? gemm8::gemm_fp8_kernel<true> : gemm8::gemm_fp8_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm8::SMEM_BYTES);
   if (e != cudaSuccess) return check_cuda(e, "cudaFuncSetAttribute(gemm_fp8)");
   const int grid = p.n_tiles < sms ? p.n_tiles : sms;
-  gemm8::gemm_fp8_kernel<<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
+  kern<<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, reinterpret_cast<cudaStream_t>(stream)>>>(tm_a, tm_b, p);
   return check_cuda(cudaGetLastError(), "gemm_fp8 launch");
 }

@@ -446,15 +446,20 @@ def matmul_fp8_blockscaled(a: torch.Tensor, a_scale: torch.Tensor, b: torch.Tens
     assert k % 128 == 0 and n % 128 == 0, "k and n must be multiples of the 128-wide scale blocks"
     assert a_scale.shape == (m, k // 128) and b_scale.shape == (k // 128, n // 128)
     assert a_scale.dtype == torch.float32 and b_scale.dtype == torch.float32
-    assert a.stride(1) == 1 and b.stride(1) == 1 and a_scale.stride(1) == 1 and b_scale.stride(1) == 1
+    assert a.stride(1) == 1 and a_scale.stride(1) == 1 and b_scale.stride(1) == 1
+    # b may be a [K, N] row-major matrix or the transposed view `w.t()` of a weight kept as [N, K] (K contiguous),
+    # which the tensor cores read as the K-major operand
+    b_kmajor = b.stride(1) != 1
+    assert b.stride(1) == 1 or b.stride(0) == 1, "b must be contiguous along N or along K"
     if out is None:
         out = torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
     g = _lib.GemmFp8Args()
     g.a, g.b, g.c, g.a_scale, g.b_scale = a.data_ptr(), b.data_ptr(), out.data_ptr(), a_scale.data_ptr(), b_scale.data_ptr()
     g.m, g.n, g.k = m, n, k
-    g.lda, g.ldb, g.ldc = a.stride(0), b.stride(0), out.stride(0)
+    g.lda, g.ldb, g.ldc = a.stride(0), (b.stride(1) if b_kmajor else b.stride(0)), out.stride(0)
     g.a_scale_ld, g.b_scale_ld = a_scale.stride(0), b_scale.stride(0)
     g.status = None
+    g.b_kmajor = 1 if b_kmajor else 0
     with torch.cuda.device(a.device):
         rc = _lib.load().ftb_gemm_fp8_blockscaled(C.byref(g), C.c_void_p(_stream_ptr(a.device)))
     _lib.check(rc, "matmul_fp8_blockscaled")

@@ -214,13 +214,15 @@ FTB_API int ftb_sizeof_gemm_args(void);
  * ------------------------------------------------------------------------------------------ */
 typedef struct ftb_gemm_fp8_args {
   const void* a;          /* e4m3 [m, k], lda (bytes = elements) */
-  const void* b;          /* e4m3 [k, n], ldb */
+  const void* b;          /* e4m3 [k, n] row-major with ldb, or, when b_kmajor is set, its transpose [n, k] row-major with
+                             ldb (the layout a linear layer keeps its weight in; same speed, same bits) */
   void* c;                /* bf16 [m, n], ldc */
   const float* a_scale;   /* fp32 [m, k/128], row stride a_scale_ld */
   const float* b_scale;   /* fp32 [k/128, n/128], row stride b_scale_ld */
   int32_t m, n, k;
   int64_t lda, ldb, ldc, a_scale_ld, b_scale_ld;
   int32_t* status;
+  int32_t b_kmajor;       /* 0: b is [k, n] row-major; 1: b points at the transpose [n, k] row-major */
 } ftb_gemm_fp8_args;
 
 FTB_API int ftb_gemm_fp8_blockscaled(const ftb_gemm_fp8_args* args, void* stream);

@@ -29,6 +29,17 @@ def test_fp8_blockscaled_matches_oracle(m, n, k):
     assert err <= 2 ** -8 * scale
 
 
+def test_weight_kept_as_n_by_k_gives_the_same_bits():
+    """B passed as the transposed view of an [N, K] weight (the K-major operand of the tensor cores) must give the
+    result of the [K, N] row-major call bit for bit: the same products are summed in the same order."""
+    c = W.gemm_cfg5(tp=1, rank=0, m=384, n=512, k_total=640)
+    a, b, a_s, b_s = c.a.to(DEV), c.b.to(DEV), c.a_scale.to(DEV), c.b_scale.to(DEV)
+    ref = matmul_fp8_blockscaled(a, a_s, b, b_s)
+    w = b.t().contiguous()                      # [N, K]
+    got = matmul_fp8_blockscaled(a, a_s, w.t(), b_s)
+    assert torch.equal(ref, got)
+
+
 def test_fp8_unit_scales_equal_plain_product():
     g = torch.Generator().manual_seed(3)
     a = torch.randint(-8, 9, (256, 256), generator=g).float()
