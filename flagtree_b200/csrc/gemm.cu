@@ -329,8 +329,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     tma_prefetch_desc(&tm_b);
   }
   __syncthreads();
-  // The status word is read before any CTA of this launch can have written it only if an EARLIER
-  // launch failed, so both CTAs of a pair take the same branch here.
+  // An earlier launch on this status word failed: leave at once.  The two CTAs of a pair read the word at
+  // different moments (another group of this launch may report a timeout in between), so the odd CTA takes the
+  // even CTA's reading: a CTA that went on alone would signal barriers in the shared memory of a partner that
+  // has left.
+  if constexpr (NCTA == 2) {
+    cluster_sync_all();
+    uint32_t leave;
+    asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(leave) : "r"(mapa_shared(smem_u32(&bars->abort_flag), 0)) : "memory");
+    cluster_sync_all();        // the even CTA keeps its flag until its partner has read it
+    if (tid == 0) bars->abort_flag = leave != 0u ? 1 : 0;
+    __syncthreads();
+  }
   if (bars->abort_flag) {
     // copy-engine exchange: the second stream waits for the ready words whatever became of this launch
     if (p.ce_ready != nullptr && blockIdx.x == 0 && tid < p.tp * p.ce_chunks) st_release_sys(p.ce_ready + tid, p.epoch);
