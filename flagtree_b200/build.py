@@ -9,7 +9,7 @@ import sys
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libflagtree_b200.so")
-SOURCES = ["abi.cu", "sparse_mla.cu", "sparse_mla_ring.cu", "gemm.cu", "gemm_fp8.cu", "kv_cache.cu", "topk.cu"]
+SOURCES = ["abi.cu", "sparse_mla.cu", "sparse_mla_ring.cu", "sparse_mla_few.cu", "gemm.cu", "gemm_fp8.cu", "kv_cache.cu", "topk.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

@@ -65,10 +65,11 @@ typedef struct ftb_sparse_mla_args {
   int64_t lse_stride_token;
   float sm_scale;
   int32_t lse_base2;        /* 0: lse = log sum exp(s);  1: log2 sum 2^(s*log2 e)            */
-  int32_t algo_id;          /* 0 = default = 5; 1 = one CTA per (token, output half); 5 = persistent
-                               role-split CTA pairs that walk through the tokens (scores in one
-                               CTA, values in the other); 6 = paged FP8 form only: dequantise the
-                               selected rows, then the persistent kernel                     */
+  int32_t algo_id;          /* 0 = default = 5; 1 = one CTA per (token, output half); 2 = few heads
+                               (h <= 32, bf16 form without splits): one CTA per token, scores
+                               transposed; 5 = persistent role-split CTA pairs that walk through the
+                               tokens (scores in one CTA, values in the other); 6 = paged FP8 form
+                               only: dequantise the selected rows, then the persistent kernel    */
   int32_t* status;          /* optional device int32: kernels OR-in a non-zero FTB_ERR_* code */
   /* Paged FP8 form (kv_is_fp8 != 0): physical row = block_table[seq, p / page] * page + p % page,
    * the rule of test_accuracy_musa_vllm_mla.py:278-283.  Query token t belongs to sequence
