@@ -483,6 +483,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     unsigned int* pending_flag = nullptr;            // lane 0: counter of the last remote tile, not yet released
     int ce_pending = -1;                             // lane 0, copy-engine exchange: row shard of the tile stored last, not yet counted
     unsigned int ce_weight = 0;                      // what that tile counts: 2 for a whole tile, 1 for a half
+    int pull_pending_blk = -1;                       // lane 0, pull protocol: row block of the tile stored last, not yet counted
+    unsigned int* pull_pending_flag = nullptr;       // the owner's word for that row block
     // the accumulator-free barrier the MMA issuer waits on lives in the even CTA
     const uint32_t acc_empty_addr[2] = {
         NCTA == 1 ? smem_u32(&bars->acc_empty[0]) : mapa_shared(smem_u32(&bars->acc_empty[0]), 0),
@@ -573,6 +575,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         // partial tile -> this rank's own symmetric buffer (row-major [m, n] bf16), then count the row block
         if (!__all_sync(0xffffffffu, mbar_wait(smem_u32(&bars->acc_full[acc]), (local >> 1) & 1u, abort_flag))) break;   // a wait ran out
         tc_fence_after();
+        if (lane == 0 && pull_pending_blk >= 0) {
+          // Count the tile stored BEFORE this one for its row block: its stores left a whole tile ago, so the fence
+          // that orders them before the count returns at once (a system-scope fence right behind the stores of
+          // every tile held the epilogue, and with it the MMAs, back).  The last count of a row block on this rank
+          // tells the owner, with the one system-scope release that the peers' reads need.
+          __threadfence();
+          const unsigned int cnt = atomicAdd(p.blk_counter + pull_pending_blk, 1u) + 1u;
+          if (cnt == p.flag_target) {
+            __threadfence_system();
+            st_release_sys(pull_pending_flag, p.epoch);
+          }
+          pull_pending_blk = -1;
+        }
+        __syncwarp();                  // the tensor-memory loads below are warp-collective
         __nv_bfloat16* orow = p.recv[p.rank] + static_cast<long long>(row) * p.n + n_blk * BN;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -594,15 +610,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         tc_fence_before();
         __syncwarp();                  // orders the 32 lanes' stores before lane 0's fence below
         if (lane == 0) {
-          release_acc(acc);            // the MMAs of the next tile do not wait for the fence
-          __threadfence_system();      // the warp's stores are visible to peers before the count
-          const unsigned int cnt = atomicAdd(p.blk_counter + m_blk, 1u) + 1u;
-          if (cnt == p.flag_target) {
-            // last warp of the row block on this rank: tell the owner (one 4-byte remote store)
-            __threadfence_system();
-            const int blk = m_blk - dst * p.blocks_per_shard;
-            st_release_sys(p.flags[dst] + p.rank * p.blocks_per_shard + blk, p.epoch);
-          }
+          release_acc(acc);
+          const int blk = m_blk - dst * p.blocks_per_shard;
+          pull_pending_blk = m_blk;    // counted one tile late, see above
+          pull_pending_flag = p.flags[dst] + p.rank * p.blocks_per_shard + blk;
         }
         __syncwarp();
       } else if (remote) {
@@ -718,6 +729,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
           release_acc(acc);
           if (ce && !ag) { ce_pending = dst * p.ce_chunks + piece; ce_weight = stp.width == BN ? 2u : 1u; }   // counted one tile late, see above
         }
+      }
+    }
+    if (lane == 0 && pull_pending_blk >= 0) {
+      __threadfence();
+      const unsigned int cnt = atomicAdd(p.blk_counter + pull_pending_blk, 1u) + 1u;
+      if (cnt == p.flag_target) {
+        __threadfence_system();
+        st_release_sys(pull_pending_flag, p.epoch);
       }
     }
     if (lane == 0 && ce_pending >= 0) {
