@@ -499,10 +499,10 @@ class GemmRsContext:
         import torch.distributed as dist
         # measured at the cfg4 per-rank shape: push 0.311 ms against pull 0.36-0.39 at tp = 2, level at tp = 4,
         # pull 0.383-0.390 against push 0.463-0.471 at tp = 8; so "auto" pulls from four ranks on
-        # "auto" for bf16 calls: the copy-engine exchange up to four ranks (0.224 ms against push 0.30 and
-        # GEMM + NCCL 0.35 at tp = 2; 0.333 against pull 0.394 and NCCL 0.378 at tp = 4), the in-switch reduction
-        # beyond (the copy engines of a rank move about 500 GB/s, too little for seven shards)
-        if protocol == "auto" and not fp8 and self.tp <= 4:
+        # "auto" for bf16 calls: the copy-engine exchange at two ranks (0.230 ms against pull 0.317, push 0.30 and
+        # GEMM + NCCL 0.358), the in-switch reduction from four ranks on (0.320 ms against copy 0.341 and NCCL 0.379
+        # at tp = 4: the copy engines of a rank move about 500 GB/s, too little for three or seven shards)
+        if protocol == "auto" and not fp8 and self.tp <= 2:
             protocol = "copy"
         want_pull = protocol == "pull" or (protocol == "auto" and self.tp >= 4)
         have_mc = torch.tensor([1 if (self.recv.mc_ptr and want_pull) else 0], device=self.device)

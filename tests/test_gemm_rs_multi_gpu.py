@@ -23,7 +23,7 @@ def _run(world, provider, protocol):
 @pytest.mark.parametrize("provider,protocol", [("auto", "auto"), ("auto", "pull"), ("auto", "staged"), ("auto", "push"),
                                                ("cuda_ipc", "push"), ("cuda_ipc", "staged"), ("auto", "copy"), ("cuda_ipc", "copy")])
 def test_gemm_rs_matches_oracle(provider, protocol):
-    """auto/auto = the copy-engine exchange up to four ranks, beyond that the fused kernel with the pull protocol
+    """auto/auto = the copy-engine exchange at two ranks, from four ranks on the fused kernel with the pull protocol
     (in-switch reduction) when the box offers NVSwitch multicast, else push; cuda_ipc/staged = the staged protocol with plain peer loads.  The worker also runs
     the FP8 form, which is always staged, in every combination."""
     _run(min(torch.cuda.device_count(), 8), provider, protocol)
